@@ -1,0 +1,374 @@
+"""Benchmark of the QR hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one pass of the hot path over one batch: reduced QR of BATCH float32
+32 x 32 N(0,1) matrices per GPU (the shape the headline metric is quoted on, at a
+batch that saturates the GPU and is larger than L2: 1 GiB in, 2 GiB out per GPU).
+The batch axis is sharded over the GPUs with no collective; per-GPU work is fixed
+as N grows (weak scaling). Rank 0 prints one JSON line.
+
+  value      matrices/s with the inputs resident in HBM: K launches of the C-ABI
+             call on device pointers, timed with CUDA events, max over ranks
+  e2e        the same through the C-ABI call on HOST (pinned) buffers: the
+             host-to-device copy of the inputs and the device-to-host copy of Q
+             and R are inside the timed region
+  roofline   the small-matrix kernel against the measured HBM copy bandwidth
+  cpu_baseline  the reference's own CPU path (src/qr_cpu.mm compiled into
+             oracle/_ref; all host cores) on a bounded sample of the same workload
+  others     (1 GPU only) the remaining benchmark configurations, each timed the same way
+
+--impl reference times the reference's CPU path alone, on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [os.path.join(ROOT, "metal-linalg_b200")]
+
+METRIC = "fp32 QR matrices/s (32x32 batch)"
+UNIT = "matrices/s"
+ROWS = COLS = 32
+BATCH = 262144                       # per GPU
+BYTES_PER_MATRIX = 3 * ROWS * COLS * 4   # A read, Q and R written
+# DRAM bytes per matrix of the small kernel from the ncu capture summarised in
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over one launch / matrices); None until captured.
+MEASURED_TRAFFIC_PER_MATRIX = None
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": FALLBACK_HBM_GBS}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference(sample_batch, reps):
+    """The reference's CPU QR on `sample_batch` 32 x 32 matrices: (matrices/s, cores, kind)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+
+    import harness
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((sample_batch, ROWS, COLS)).astype(np.float32)
+    if harness.load_ref() is not None:
+        run, kind, cores = (lambda: harness.ref_qr(a)), "reference", int(harness.load_ref().ref_cpu_threads())
+    else:
+        run, kind, cores = (lambda: harness.oracle_qr(a)), "port", os.cpu_count() or 1
+    run()
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        run()
+        best = min(best, time.perf_counter() - t0)
+    return sample_batch / best, cores, kind, best
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    t_all = time.perf_counter()
+    # calibrate the sample so that one step is about a second of CPU work
+    rate, cores, kind, _ = cpu_reference(4096, 1)
+    sample = int(min(BATCH, max(4096, rate * 1.0)))
+    for _ in range(args.warmup):
+        cpu_reference(sample, 1)
+    times = []
+    for _ in range(args.steps):
+        _, _, _, t = cpu_reference(sample, 1)
+        times.append(t)
+    value = sample * len(times) / sum(times)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"reduced QR of {ROWS}x{COLS} float32 N(0,1) matrices, batch {BATCH} per GPU; "
+                               f"the CPU arm times a sample of {sample} matrices per step on the host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{sample} matrices per step, {args.steps} steps"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t_all,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_config(torch, mlt, _lib, a, mode, steps, warmup, flush):
+    """Seconds per launch of the C-ABI call on device tensor `a`, CUDA events on the launching stream."""
+    b, m, n = a.shape
+    k = min(m, n)
+    qc = {"reduced": k, "complete": m, "r": 0}[mode]
+    rr = m if mode == "complete" else k
+    q = torch.empty(b, m, qc, device=a.device) if qc else None
+    r = torch.empty(b, rr, n, device=a.device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        _lib.qr(a.data_ptr(), b, m, n, q.data_ptr() if qc else None, r.data_ptr(), mode, stream)
+
+    for _ in range(warmup):
+        call()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1.0)            # rewrites a buffer larger than L2 between iterations
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        call()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1) * 1e-3
+    return total / steps, (q, r)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+
+    import metal_linalg_torch as mlt
+    from metal_linalg_torch import _lib, workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: this library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    t_all = time.perf_counter()
+
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    a = torch.randn(BATCH, ROWS, COLS, generator=g, device="cuda", dtype=torch.float32)
+    q = torch.empty(BATCH, ROWS, COLS, device="cuda")
+    r = torch.empty(BATCH, ROWS, COLS, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        _lib.qr(a.data_ptr(), BATCH, ROWS, COLS, q.data_ptr(), r.data_ptr(), "reduced", stream)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    seconds = e0.elapsed_time(e1) * 1e-3
+    # keep the sampler running over a few more launches so that short timed regions still get samples
+    if rank == 0:
+        t_end = time.perf_counter() + 0.6
+        while time.perf_counter() < t_end:
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    seconds = t.item()
+
+    # correctness of what was timed: a sample against float64 products on the GPU
+    sl = slice(0, 4096)
+    a64, q64, r64 = a[sl].double(), q[sl].double(), r[sl].double()
+    recon = (torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)).max().item()
+    orth = torch.linalg.matrix_norm(q64.mT @ q64 - torch.eye(COLS, device="cuda", dtype=torch.float64)).max().item()
+
+    # end to end: host (pinned) buffers through the C-ABI call, copies inside the timed region
+    e2e_steps = max(1, min(args.steps, 3))
+    ha = torch.empty(BATCH, ROWS, COLS, dtype=torch.float32).pin_memory()
+    ha.copy_(a)
+    hq = torch.empty(BATCH, ROWS, COLS, dtype=torch.float32).pin_memory()
+    hr = torch.empty(BATCH, ROWS, COLS, dtype=torch.float32).pin_memory()
+    _lib.lib.metal_linalg_set_device(local_rank)
+
+    def host_step():
+        _lib.qr(ha.data_ptr(), BATCH, ROWS, COLS, hq.data_ptr(), hr.data_ptr(), "reduced")
+
+    host_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_step()
+    e2e_seconds = time.perf_counter() - t0
+    t = torch.tensor([e2e_seconds], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_seconds = t.item()
+    e2e_ok = bool(torch.equal(hq[:64], q[:64].cpu()) and torch.equal(hr[:64], r[:64].cpu()))
+    del ha, hq, hr
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    per_launch = seconds / args.steps
+    achieved = BATCH * BYTES_PER_MATRIX / per_launch / 1e9
+    line = {
+        "metric": METRIC, "value": world * BATCH * args.steps / seconds, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * per_launch,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"reduced QR of {BATCH} float32 {ROWS}x{COLS} N(0,1) matrices per GPU (the first "
+                               f"benchmark configuration's shape at a batch that saturates the GPU)",
+                   "batch_per_gpu": BATCH, "rows": ROWS, "cols": COLS, "mode": "reduced",
+                   "sharding": f"batch axis over {world} GPU(s), no collective",
+                   "l2": "inputs and outputs (3 GiB per GPU) are larger than L2; no flush needed",
+                   "kernel": mlt.qr_kernel(ROWS, COLS, BATCH)},
+        "e2e": {"value": world * BATCH * e2e_steps / e2e_seconds, "unit": UNIT,
+                "h2d_bytes_per_step": BATCH * ROWS * COLS * 4, "d2h_bytes_per_step": 2 * BATCH * ROWS * COLS * 4,
+                "steps": e2e_steps, "ms_per_step": 1e3 * e2e_seconds / e2e_steps,
+                "path": "metal_linalg_qr_with_mode on pinned host pointers (staged in chunks)",
+                "matches_device_path": e2e_ok},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "of": peak_kind,
+                     "traffic": (MEASURED_TRAFFIC_PER_MATRIX * BATCH if MEASURED_TRAFFIC_PER_MATRIX else None),
+                     "kernel": "qr_small_kernel<32,32>", "algorithmic_bytes_per_launch": BATCH * BYTES_PER_MATRIX},
+        "clocks": clocks,
+        "check": {"recon_max": recon, "orth_max": orth, "tolerance": workloads.tolerance(COLS)},
+    }
+
+    if world == 1 and not args.headline_only:
+        line["others"] = other_configs(torch, mlt, _lib, workloads, args)
+        rate, cores, kind, best = cpu_reference(4096, 1)
+        sample = int(min(BATCH, max(4096, rate * 3.0)))
+        rate, cores, kind, best = cpu_reference(sample, 3)
+        line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": kind,
+                                "sample": f"{sample} of the {BATCH} matrices, best of 3 ({best:.2f} s each)"}
+    line["wall_s"] = time.perf_counter() - t_all
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def other_configs(torch, mlt, _lib, workloads, args):
+    """The remaining benchmark configurations on one GPU: seconds per launch, matrices/s, GFLOP/s and
+    GB/s from the algorithmic counts. Inputs are drawn on the GPU with the configurations' shapes and
+    distributions (the seeded CPU generators are what the parity tests use)."""
+    out = []
+    flush = torch.zeros(64 << 20, device="cuda")      # 256 MiB, larger than L2
+
+    def add(name, a, mode, need_flush, steps=None):
+        b, m, n = a.shape
+        try:
+            kernel = mlt.qr_kernel(m, n, b, mode)
+            sec, (q, r) = time_config(torch, mlt, _lib, a, mode, steps or args.steps, max(3, min(args.warmup, 3)),
+                                      flush if need_flush else None)
+            s = slice(0, min(b, 2))
+            a64, q64, r64 = a[s].double(), q[s].double(), r[s].double()
+            recon = (torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)).max().item()
+            out.append({"config": name, "mode": mode, "kernel": kernel, "batch": b, "rows": m, "cols": n,
+                        "ms": sec * 1e3, "matrices_per_s": b / sec,
+                        "gflops": b * workloads.qr_flops(m, n, mode) / sec / 1e9,
+                        "gbs": b * workloads.qr_bytes(m, n, mode) / sec / 1e9,
+                        "l2_flush": bool(need_flush), "recon_max": recon})
+        except Exception as e:   # a configuration whose kernel is not built yet is reported, not hidden
+            out.append({"config": name, "mode": mode, "error": f"{type(e).__name__}: {e}"})
+        torch.cuda.synchronize()
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    add("c1_32x32 (batch 1024)", torch.randn(1024, 32, 32, generator=g, device="cuda"), "reduced", True)
+    a = torch.randn(262144, 16, 16, generator=g, device="cuda")
+    u = torch.rand(262144, generator=g, device="cuda", dtype=torch.float64) * 67.0 - 30.0
+    a = (a.double() * torch.pow(torch.tensor(10.0, device="cuda", dtype=torch.float64), u)[:, None, None]).float()
+    add("c2_16x16_magnitudes", a, "reduced", False)
+    del a
+    try:
+        uu = torch.linalg.qr(torch.randn(4096, 256, 256, generator=g, device="cuda"))[0]
+        vv = torch.linalg.qr(torch.randn(4096, 256, 256, generator=g, device="cuda"))[0]
+        s = torch.logspace(0.0, -7.0, 256, device="cuda")
+        s[224:] = 0.0
+        a = (uu * s) @ vv.mT
+        del uu, vv
+        add("c3_256x256_rank224", a, "reduced", False)
+        add("c3_256x256_rank224", a, "complete", False)
+        del a
+    except Exception as e:
+        out.append({"config": "c3_256x256_rank224", "error": f"{type(e).__name__}: {e}"})
+    add("c4_65536x64_tall", torch.randn(64, 65536, 64, generator=g, device="cuda"), "reduced", False)
+    add("c5a_4096x4096", torch.rand(1, 4096, 4096, generator=g, device="cuda") * 2 - 1, "reduced", False,
+        steps=min(args.steps, 5))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--headline-only", action="store_true", help="skip the other configurations and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

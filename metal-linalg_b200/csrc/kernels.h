@@ -1,0 +1,53 @@
+#pragma once
+// The QR kernel families and their launchers. Every pointer is a device pointer
+// on ctx.device; everything is enqueued on `stream` and nothing waits.
+#include "runtime.h"
+
+#include <cstdint>
+
+namespace mlb {
+
+enum QrModeInt { kReduced = 0, kROnly = 1, kComplete = 2 };
+
+struct QrProblem {
+    const float* a;      // [batch, m, n] row-major
+    float*       q;      // [batch, m, qc] or null when qc == 0
+    float*       r;      // [batch, rr, n]
+    uint32_t     batch, m, n;
+    uint32_t     qc;     // Q's columns: K, 0 (R alone) or m
+    uint32_t     rr;     // R's rows: K or m
+};
+
+inline uint32_t qr_k(const QrProblem& p) { return p.m < p.n ? p.m : p.n; }
+
+// A matrix in one warp's registers (or a part of a warp's): m, n, qc <= 32.
+bool qr_small_fits(uint32_t m, uint32_t n, uint32_t qc);
+void launch_qr_small(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
+
+// A matrix to a thread block: panels of 32 columns factored in shared memory,
+// the trailing matrix streamed through a per-block scratch copy that stays in L2.
+bool   qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n);
+void   launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
+// The same on `count` independent matrices read with a row stride and scaled on
+// load or not; used by the TSQR tree for its row blocks. See qr_mid.cu.
+struct MidOptions {
+    uint32_t lda      = 0;      // row stride of a (0: n)
+    uint64_t a_stride = 0;      // floats between matrices of a (0: m * lda)
+    uint64_t q_stride = 0;      // floats between matrices of q (0: m * qc)
+    uint64_t r_stride = 0;      // floats between matrices of r (0: rr * n)
+    bool     scale    = true;   // scan and scale each matrix by a power of two; NaN-fill non-finite ones
+};
+void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p, const MidOptions& o);
+
+// A tall thin matrix as a tree of row blocks (explicit Q).
+bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc);
+void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
+
+// Blocked compact-WY QR over the whole grid, any shape.
+bool qr_blocked_fits(uint32_t m, uint32_t n);
+void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
+
+// Small utilities shared by the launchers.
+void launch_fill_identity(cudaStream_t stream, float* q, uint32_t batch, uint32_t m, uint32_t cols);
+
+} // namespace mlb

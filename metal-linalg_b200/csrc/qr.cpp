@@ -1,0 +1,351 @@
+// The QR router and the buffer-core entry point core::qr: policy resolution
+// (reference: src/qr.mm:114-209), kernel choice (reference: src/qr.mm:231-286,
+// src/qr_householder.mm:263-275,387-391), pointer placement, and the staged
+// pipeline for host pointers.
+#include <metal_linalg/core.h>
+
+#include "kernels.h"
+#include "runtime.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+namespace metal_linalg {
+
+using core::Matrices;
+using core::QrKernel;
+using core::QrMode;
+
+// ---------------------------------------------------------------------------
+// Policy
+// ---------------------------------------------------------------------------
+namespace {
+
+struct ResolvedPolicy {
+    QrPolicy    policy;
+    std::string source;
+};
+
+// The one measured row: thresholds found on an NVIDIA B200 (148 multiprocessors).
+// k from which one matrix is better spread over the grid than given to one block.
+struct TunedRow {
+    const char* device;
+    unsigned    cores;
+    unsigned    crossover_small_batch, crossover_large_batch, batch_threshold;
+    unsigned    large_min_k, large_max_batch;
+};
+constexpr TunedRow kTuned[] = {
+    {"NVIDIA B200", 148, 384, 1024, 64, 1024, 0},
+};
+
+bool env_value(const char* name, unsigned& out) {
+    const char* s = std::getenv(name);
+    if (!s || !*s) return false;
+    char* end = nullptr;
+    const long long v = std::strtoll(s, &end, 10);
+    if (end == s || v < 0) return false;
+    out = v > 0xFFFFFFFFll ? kQrNoLimit : (unsigned)v;
+    return true;
+}
+
+ResolvedPolicy resolve() {
+    ResolvedPolicy r;
+    const std::string name = device_name();
+    r.policy.gpu_cores = gpu_core_count();
+    r.policy.concurrent_matrices = 2 * r.policy.gpu_cores;
+    for (const auto& e : kTuned) {
+        if (name == e.device && r.policy.gpu_cores == e.cores) {
+            r.policy.m_crossover_small_batch = e.crossover_small_batch;
+            r.policy.m_crossover_large_batch = e.crossover_large_batch;
+            r.policy.batch_threshold         = e.batch_threshold;
+            r.policy.gpu_large_min_k         = e.large_min_k;
+            r.policy.gpu_large_max_batch     = e.large_max_batch;
+            r.source = "tuned:" + name;
+        }
+    }
+    if (r.source.empty()) r.source = "default:untuned-device" + (name.empty() ? "" : " (" + name + ")");
+
+    std::string env;
+    unsigned crossover = 0;
+    if (env_value("QR_M_CROSSOVER", crossover) && crossover > 0) {
+        r.policy.m_crossover_small_batch = crossover;
+        r.policy.m_crossover_large_batch = crossover;
+        env = "QR_M_CROSSOVER";
+    }
+    auto over = [&](const char* n, unsigned& field) {
+        if (env_value(n, field)) env += (env.empty() ? "" : ",") + std::string(n);
+    };
+    over("QR_GPU_MAX_K", r.policy.gpu_max_k);
+    over("QR_GPU_MIN_BATCH_TIMES_K", r.policy.gpu_min_batch_times_k);
+    over("QR_GPU_MIN_BATCH", r.policy.gpu_min_batch);
+    over("QR_GPU_MIN_K", r.policy.gpu_min_k);
+    over("QR_GPU_LARGE_MIN_K", r.policy.gpu_large_min_k);
+    over("QR_GPU_LARGE_MAX_BATCH", r.policy.gpu_large_max_batch);
+    over("QR_SHARE_MIN_BATCH", r.policy.share_min_batch);
+    if (!env.empty()) r.source = "env:" + env;
+    return r;
+}
+
+std::mutex g_policy_mutex;
+ResolvedPolicy& state() {
+    static ResolvedPolicy s = resolve();
+    return s;
+}
+
+} // namespace
+
+QrPolicy qr_policy() {
+    std::lock_guard<std::mutex> lock(g_policy_mutex);
+    return state().policy;
+}
+const char* qr_policy_source() {
+    std::lock_guard<std::mutex> lock(g_policy_mutex);
+    return state().source.c_str();
+}
+void set_qr_policy(const QrPolicy& p) {
+    std::lock_guard<std::mutex> lock(g_policy_mutex);
+    const unsigned cores = state().policy.gpu_cores, conc = state().policy.concurrent_matrices;
+    state().policy = p;
+    state().policy.gpu_cores = cores;             // informational, ignored when setting
+    state().policy.concurrent_matrices = conc;
+    state().source = "user";
+}
+
+QrBackend qr_gpu_backend(unsigned m, unsigned n, unsigned batch) {
+    const QrPolicy p = qr_policy();
+    const unsigned k = std::min(m, n);
+    const unsigned crossover = batch < p.batch_threshold ? p.m_crossover_small_batch : p.m_crossover_large_batch;
+    if (k >= crossover) return QrBackend::streaming_reduced;
+    const unsigned long long L = p.gpu_large_min_k;
+    if (L && (unsigned long long)m * k >= L * L && (p.gpu_large_max_batch == 0 || batch <= p.gpu_large_max_batch))
+        return QrBackend::streaming_reduced;
+    return QrBackend::unblocked;
+}
+QrBackend qr_backend(unsigned m, unsigned n, unsigned batch) { return qr_gpu_backend(m, n, batch); }
+bool      qr_uses_gpu(unsigned, unsigned, unsigned) { return true; }
+bool      qr_shares_batch(unsigned, unsigned, unsigned) { return false; }
+
+// ---------------------------------------------------------------------------
+// Kernel choice
+// ---------------------------------------------------------------------------
+namespace {
+
+mlb::QrProblem problem(const Matrices& a, float* q, float* r, QrMode mode) {
+    mlb::QrProblem p{};
+    p.a = a.data; p.q = q; p.r = r;
+    p.batch = a.batch; p.m = a.rows; p.n = a.cols;
+    p.qc = core::qr_q_cols(mode, a.rows, a.cols);
+    p.rr = core::qr_r_rows(mode, a.rows, a.cols);
+    if (!p.qc) p.q = nullptr;
+    return p;
+}
+
+// A forced kernel, for tuning: QR_KERNEL=small|mid|tsqr|blocked (ignored where it does not fit).
+int forced_kernel() {
+    const char* e = std::getenv("QR_KERNEL");
+    if (!e) return -1;
+    if (!std::strcmp(e, "small")) return (int)QrKernel::small;
+    if (!std::strcmp(e, "mid")) return (int)QrKernel::mid;
+    if (!std::strcmp(e, "tsqr")) return (int)QrKernel::tsqr;
+    if (!std::strcmp(e, "blocked")) return (int)QrKernel::blocked;
+    return -1;
+}
+
+QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, QrMode mode) {
+    const uint32_t qc = core::qr_q_cols(mode, m, n);
+    const bool small = mlb::qr_small_fits(m, n, qc), mid = mlb::qr_mid_fits(ctx, m, n),
+               tsqr = mlb::qr_tsqr_fits(ctx, m, n, qc);
+    switch (forced_kernel()) {
+        case (int)QrKernel::small:   if (small) return QrKernel::small; break;
+        case (int)QrKernel::mid:     if (mid) return QrKernel::mid; break;
+        case (int)QrKernel::tsqr:    if (tsqr) return QrKernel::tsqr; break;
+        case (int)QrKernel::blocked: return QrKernel::blocked;
+        default: break;
+    }
+    if (small) return QrKernel::small;
+    const bool spread = qr_gpu_backend(m, n, batch) == QrBackend::streaming_reduced;
+    if (mid && !spread) return QrKernel::mid;
+    if (tsqr) return QrKernel::tsqr;
+    if (mid && !mlb::qr_blocked_fits(m, n)) return QrKernel::mid;
+    return QrKernel::blocked;
+}
+
+void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices& a, float* q, float* r, QrMode mode,
+                   int forced /* -1: route */) {
+    const mlb::QrProblem p = problem(a, q, r, mode);
+    const QrKernel k = forced >= 0 ? (QrKernel)forced : choose(ctx, a.rows, a.cols, a.batch, mode);
+    switch (k) {
+        case QrKernel::small:   mlb::launch_qr_small(ctx, stream, p); break;
+        case QrKernel::mid:     mlb::launch_qr_mid(ctx, stream, p); break;
+        case QrKernel::tsqr:    mlb::launch_qr_tsqr(ctx, stream, p); break;
+        case QrKernel::blocked: mlb::launch_qr_blocked(ctx, stream, p); break;
+    }
+}
+
+// Host pointers: the batch in chunks through two sets of device buffers, the
+// copy in of chunk i+1 and the copy out of chunk i-1 running beside the
+// kernels of chunk i on the context's three streams.
+void run_staged(mlb::DeviceContext& ctx, const Matrices& a, float* q, float* r, QrMode mode, int forced) {
+    const uint32_t m = a.rows, n = a.cols;
+    const size_t qc = core::qr_q_cols(mode, m, n), rr = core::qr_r_rows(mode, m, n);
+    const size_t fa = (size_t)m * n, fq = (size_t)m * qc, fr = rr * n;
+    const size_t per = (fa + fq + fr) * sizeof(float);
+    // chunks of about 64 MB of traffic, at least one matrix, at most the batch
+    size_t chunk = std::max<size_t>(1, ((size_t)64 << 20) / std::max<size_t>(per, 1));
+    chunk = std::min<size_t>(chunk, a.batch);
+    const size_t align = 64;   // floats; keeps every buffer 256-byte aligned
+    auto up = [&](size_t f) { return (f + align - 1) / align * align; };
+    const size_t set_floats = up(chunk * fa) + up(chunk * fq) + up(chunk * fr);
+
+    mlb::DeviceGuard guard(ctx.device);
+    std::lock_guard<std::mutex> lock(ctx.mutex);
+    // the staging buffers belong to the copy-in stream's workspace; the kernels'
+    // own scratch to the compute stream's
+    float* base = static_cast<float*>(ctx.workspace(ctx.copy_in, 2 * set_floats * sizeof(float)));
+    float* da[2], *dq[2], *dr[2];
+    for (int s = 0; s < 2; ++s) {
+        da[s] = base + s * set_floats;
+        dq[s] = da[s] + up(chunk * fa);
+        dr[s] = dq[s] + up(chunk * fq);
+    }
+    size_t done = 0;
+    for (size_t i = 0; done < a.batch; ++i) {
+        const int s = (int)(i & 1);
+        const uint32_t count = (uint32_t)std::min<size_t>(chunk, a.batch - done);
+        // the set is free once its previous copy out has finished
+        if (i >= 2) mlb::cuda_check(cudaStreamWaitEvent(ctx.copy_in, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
+        mlb::cuda_check(cudaMemcpyAsync(da[s], a.data + done * fa, count * fa * sizeof(float),
+                                        cudaMemcpyHostToDevice, ctx.copy_in), "copy in");
+        mlb::cuda_check(cudaEventRecord(ctx.ev_in[s], ctx.copy_in), "cudaEventRecord");
+        mlb::cuda_check(cudaStreamWaitEvent(ctx.compute, ctx.ev_in[s], 0), "cudaStreamWaitEvent");
+        if (i >= 2) mlb::cuda_check(cudaStreamWaitEvent(ctx.compute, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
+        run_on_device(ctx, ctx.compute, {da[s], count, m, n}, dq[s], dr[s], mode, forced);
+        mlb::cuda_check(cudaEventRecord(ctx.ev_done[s], ctx.compute), "cudaEventRecord");
+        mlb::cuda_check(cudaStreamWaitEvent(ctx.copy_out, ctx.ev_done[s], 0), "cudaStreamWaitEvent");
+        if (fq)
+            mlb::cuda_check(cudaMemcpyAsync(q + done * fq, dq[s], count * fq * sizeof(float),
+                                            cudaMemcpyDeviceToHost, ctx.copy_out), "copy out");
+        mlb::cuda_check(cudaMemcpyAsync(r + done * fr, dr[s], count * fr * sizeof(float),
+                                        cudaMemcpyDeviceToHost, ctx.copy_out), "copy out");
+        mlb::cuda_check(cudaEventRecord(ctx.ev_out[s], ctx.copy_out), "cudaEventRecord");
+        done += count;
+    }
+    mlb::cuda_check(cudaStreamSynchronize(ctx.copy_out), "cudaStreamSynchronize");
+    mlb::cuda_check(cudaStreamSynchronize(ctx.compute), "cudaStreamSynchronize");
+}
+
+void run(const Matrices& a, float* q, float* r, QrMode mode, int forced) {
+    const uint32_t M = a.rows, N = a.cols, K = std::min(M, N);
+    const size_t qc = core::qr_q_cols(mode, M, N), rr = core::qr_r_rows(mode, M, N);
+    if (!qc) q = nullptr;
+    if (cpu_only())
+        throw std::runtime_error("[qr] this thread is set CPU-only, and this build has no CPU path");
+    const bool has_q = q != nullptr && (size_t)a.batch * M * qc > 0;
+    const bool has_r = (size_t)a.batch * rr * N > 0;
+    const bool has_a = (size_t)a.batch * M * N > 0;
+    // where the buffers live: all on one GPU, or all on the host
+    int where = -2;
+    auto place = [&](const void* p, bool used) {
+        if (!used || !p) return;
+        const int d = mlb::pointer_device(p);
+        if (where == -2) where = d;
+        else if (where != d)
+            throw std::invalid_argument("[qr] a, q and r must all be host pointers or all device pointers on one GPU");
+    };
+    place(a.data, has_a);
+    place(q, has_q);
+    place(r, has_r);
+    if (where == -2) return;   // nothing to read or write
+
+    // Nothing to factor: the complete Q is the identity (reference: src/qr.mm:312-317)
+    if (K == 0 || a.batch == 0) {
+        if (mode == QrMode::complete && N == 0 && has_q) {
+            if (where < 0) {
+                std::fill(q, q + (size_t)a.batch * M * M, 0.0f);
+                for (size_t i = 0; i < (size_t)a.batch * M; ++i) q[i * M + i % M] = 1.0f;
+            } else {
+                mlb::DeviceContext& ctx = mlb::context(where);
+                mlb::DeviceGuard guard(where);
+                mlb::launch_fill_identity(mlb::thread_stream(), q, a.batch, M, M);
+            }
+        }
+        return;
+    }
+    if (where >= 0) {
+        mlb::DeviceContext& ctx = mlb::context(where);
+        mlb::DeviceGuard guard(where);
+        std::lock_guard<std::mutex> lock(ctx.mutex);
+        run_on_device(ctx, mlb::thread_stream(), a, q, r, mode, forced);
+    } else {
+        run_staged(mlb::context(mlb::thread_device()), a, q, r, mode, forced);
+    }
+}
+
+} // namespace
+
+namespace core {
+
+QrKernel qr_kernel(uint32_t m, uint32_t n, uint32_t batch, QrMode mode) {
+    return choose(mlb::context(mlb::thread_device()), m, n, batch, mode);
+}
+const char* qr_kernel_name(QrKernel k) {
+    switch (k) {
+        case QrKernel::small: return "small";
+        case QrKernel::mid:   return "mid";
+        case QrKernel::tsqr:  return "tsqr";
+        default:              return "blocked";
+    }
+}
+
+void qr(const Matrices& a, float* q, float* r, QrMode mode) { run(a, q, r, mode, -1); }
+void qr(const Matrices& a, float* q, float* r) { run(a, q, r, QrMode::reduced, -1); }
+
+namespace detail {
+
+bool qr_householder_fits(uint32_t m, uint32_t n) {
+    return m > 0 && n > 0 && mlb::qr_mid_fits(mlb::context(mlb::thread_device()), m, n);
+}
+bool qr_blocked_fits(uint32_t m, uint32_t n) { return mlb::qr_blocked_fits(m, n); }
+bool qr_tsqr_fits(uint32_t m, uint32_t n, QrMode mode) {
+    return mlb::qr_tsqr_fits(mlb::context(mlb::thread_device()), m, n, core::qr_q_cols(mode, m, n));
+}
+
+void qr_householder(const Matrices& a, float* q, float* r, QrMode mode) {
+    if (std::min(a.rows, a.cols) == 0 || a.batch == 0) return run(a, q, r, mode, -1);
+    const uint32_t qc = core::qr_q_cols(mode, a.rows, a.cols);
+    if (mlb::qr_small_fits(a.rows, a.cols, qc)) return run(a, q, r, mode, (int)QrKernel::small);
+    if (!qr_householder_fits(a.rows, a.cols))
+        throw std::invalid_argument("[qr_householder] a matrix of " + std::to_string(a.rows) + " x " +
+                                    std::to_string(a.cols) + " does not fit a thread block");
+    run(a, q, r, mode, (int)QrKernel::mid);
+}
+void qr_unblocked(const Matrices& a, float* q, float* r, QrMode mode) {
+    if (std::min(a.rows, a.cols) == 0 || a.batch == 0) return run(a, q, r, mode, -1);
+    const uint32_t qc = core::qr_q_cols(mode, a.rows, a.cols);
+    if (mlb::qr_small_fits(a.rows, a.cols, qc) || qr_householder_fits(a.rows, a.cols))
+        return qr_householder(a, q, r, mode);
+    qr_blocked(a, q, r, mode);
+}
+void qr_blocked(const Matrices& a, float* q, float* r, QrMode mode) {
+    if (std::min(a.rows, a.cols) == 0 || a.batch == 0) return run(a, q, r, mode, -1);
+    if (!mlb::qr_blocked_fits(a.rows, a.cols))
+        throw std::invalid_argument("[qr_blocked] a matrix of " + std::to_string(a.rows) + " x " +
+                                    std::to_string(a.cols) + " is beyond the blocked QR");
+    run(a, q, r, mode, (int)QrKernel::blocked);
+}
+void qr_tsqr(const Matrices& a, float* q, float* r, QrMode mode) {
+    if (std::min(a.rows, a.cols) == 0 || a.batch == 0) return run(a, q, r, mode, -1);
+    if (!qr_tsqr_fits(a.rows, a.cols, mode))
+        throw std::invalid_argument("[qr_tsqr] takes tall matrices of at most 64 columns, reduced or R alone");
+    run(a, q, r, mode, (int)QrKernel::tsqr);
+}
+void qr_streaming_amx_reduced(const Matrices& a, float* q, float* r, QrMode mode) { qr_blocked(a, q, r, mode); }
+
+} // namespace detail
+} // namespace core
+} // namespace metal_linalg

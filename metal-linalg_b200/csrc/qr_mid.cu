@@ -1,0 +1,510 @@
+// The mid-size kernel: one thread block per matrix, up to 1024 rows and any
+// number of columns; LAPACK's blocked method (sgeqrf + sorgqr with compact-WY
+// block reflectors, panels of 32 columns).
+//
+// It takes the place of the reference's threadgroup-per-matrix kernel
+// qr_householder_wy (shaders/QR_Householder.metal:665-847; host side
+// src/qr_householder.mm:128-164,293-381) and keeps its contract: scan + power-
+// of-two scaling per matrix, non-finite matrix -> NaN outputs, slarfg signs, R
+// with exact zeros below the diagonal, Q formed backward from [I; 0].
+//
+// Layout. The grid is persistent: gridDim.x blocks (as many as are resident at
+// once) each loop over matrices, and each owns one scratch slot in global
+// memory holding its current matrix (row-major, in the scaled domain) and the
+// panels' T factors. A slot is rewritten for every matrix a block takes, so the
+// slots (a few hundred KB each) live in the 126 MB L2 and the HBM traffic of a
+// matrix is its input once and its outputs once.
+//
+// Per panel: the panel's rows are brought into shared memory column-major
+// (leading dimension = 4 mod 32 floats, so that four consecutive rows of a
+// column are one aligned 16-byte word and eight columns' words tile the 32
+// banks), factored there one column per step with one barrier a step (a warp
+// owns the columns it updates, so a dot product and its update need no
+// barrier between them), T is built from the Gram matrix V^T V, and the
+// trailing columns are updated tile by tile (32 columns x up to 256 rows in
+// shared memory) as C -= V (T^T (V^T C)) with register-tiled FP32 FMA loops
+// reading 16-byte words. Q formation runs the same tile update backward over
+// the panels on the output buffer itself.
+#include "common.cuh"
+#include "kernels.h"
+
+#include <algorithm>
+
+namespace mlb {
+
+namespace {
+
+constexpr int NT  = 256;    // threads per block
+constexpr int JB  = 32;     // panel width
+constexpr int RC  = 256;    // rows of a trailing tile held in shared memory at once
+constexpr int LDC = RC + 4; // its leading dimension
+constexpr int LDZ = 36;     // leading dimension of the 32 x 32 blocks (T, Z, W)
+
+struct MidParams {
+    const float* a;
+    float*       q;
+    float*       r;
+    float*       ws;            // gridDim.x slots of slot_floats
+    uint32_t     batch;
+    int          m, n, K, qc, rr;
+    int          lda;
+    unsigned long long a_stride, q_stride, r_stride, slot_floats;
+    int          scale;
+    int          ldv;
+    int          npanels;
+};
+
+struct Smem {
+    float* Vs;      // [32][ldv]   the panel / V, column-major
+    float* Cs;      // [32][LDC]   a trailing tile, column-major
+    float* Zp;      // [4][32][LDZ] partial V^T C of the four row groups
+    float* Zs;      // [32][LDZ]   V^T C
+    float* Ws;      // [32][LDZ]   op(T) V^T C
+    float* Ts;      // [32][LDZ]   T
+    float* taus;    // [32]
+    float* scs;     // [32]
+    float* betas;   // [32]
+    float* colss;   // [32]
+    float* red;     // [32] reductions
+};
+
+__device__ __forceinline__ Smem carve(float* base, int ldv) {
+    Smem s;
+    s.Vs = base;
+    s.Cs = s.Vs + JB * ldv;
+    s.Zp = s.Cs + 32 * LDC;
+    s.Zs = s.Zp + 4 * 32 * LDZ;
+    s.Ws = s.Zs + 32 * LDZ;
+    s.Ts = s.Ws + 32 * LDZ;
+    s.taus = s.Ts + 32 * LDZ;
+    s.scs = s.taus + 32;
+    s.betas = s.scs + 32;
+    s.colss = s.betas + 32;
+    s.red = s.colss + 32;
+    return s;
+}
+
+size_t smem_bytes(int ldv) {
+    return (size_t)(JB * ldv + 32 * LDC + 4 * 32 * LDZ + 3 * 32 * LDZ + 5 * 32) * sizeof(float);
+}
+
+// How an element read from global memory enters shared memory.
+struct LoadPlain {
+    __device__ __forceinline__ float operator()(float v, int, int) const { return v; }
+};
+struct LoadScaled {
+    Pow2 down;
+    __device__ __forceinline__ float operator()(float v, int, int) const { return down(v); }
+};
+
+// Rows [row0, row0 + nrows) x columns [col0, col0 + ncols) of a row-major matrix
+// into dst[c * lds + r], all 32 columns and rows up to the next multiple of four
+// written (zeros outside). A warp reads 32 consecutive floats of four rows and
+// writes one 16-byte word a lane.
+template <class F>
+__device__ __forceinline__ void load_tile(float* dst, int lds, const float* src, size_t ld, int row0, int nrows,
+                                          int col0, int ncols, const F& f) {
+    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+    const int nq = (nrows + 3) >> 2;
+    for (int rq = warp; rq < nq; rq += NT / 32) {
+        const int r = rq * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < ncols) {
+            const float* s = src + (size_t)(row0 + r) * ld + col0 + c;
+            if (r + 0 < nrows) v.x = f(s[0], r + 0, c);
+            if (r + 1 < nrows) v.y = f(s[ld], r + 1, c);
+            if (r + 2 < nrows) v.z = f(s[2 * ld], r + 2, c);
+            if (r + 3 < nrows) v.w = f(s[3 * ld], r + 3, c);
+        }
+        *reinterpret_cast<float4*>(dst + c * lds + r) = v;
+    }
+}
+
+// The reverse: src[c * lds + r] to rows [row0, row0 + nrows) x columns [col0, col0 + ncols).
+__device__ __forceinline__ void store_tile(const float* src, int lds, float* dst, size_t ld, int row0, int nrows,
+                                           int col0, int ncols) {
+    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+    const int nq = (nrows + 3) >> 2;
+    if (c >= ncols) return;
+    for (int rq = warp; rq < nq; rq += NT / 32) {
+        const int r = rq * 4;
+        const float4 v = *reinterpret_cast<const float4*>(src + c * lds + r);
+        float* d = dst + (size_t)(row0 + r) * ld + col0 + c;
+        if (r + 0 < nrows) d[0] = v.x;
+        if (r + 1 < nrows) d[ld] = v.y;
+        if (r + 2 < nrows) d[2 * ld] = v.z;
+        if (r + 3 < nrows) d[3 * ld] = v.w;
+    }
+}
+
+// acc[a][b] += sum over the rows of this thread's row group of V[i][r] C[c][r],
+// i = ti + 8a, c = tc + 8b. V rows start at vbase (already offset to the tile's
+// first row), C at cbase; nq row quads.
+__device__ __forceinline__ void gemm_vtc(float (&acc)[4][4], const float* vbase, int ldv, const float* cbase,
+                                         int ldc, int nq) {
+    const int ti = threadIdx.x & 7, tc = (threadIdx.x >> 3) & 7, tr = threadIdx.x >> 6;
+    for (int rq = tr; rq < nq; rq += 4) {
+        float4 v[4], c[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) v[a] = *reinterpret_cast<const float4*>(vbase + (ti + 8 * a) * ldv + 4 * rq);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) c[b] = *reinterpret_cast<const float4*>(cbase + (tc + 8 * b) * ldc + 4 * rq);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                acc[a][b] = fmaf(v[a].x, c[b].x, acc[a][b]);
+                acc[a][b] = fmaf(v[a].y, c[b].y, acc[a][b]);
+                acc[a][b] = fmaf(v[a].z, c[b].z, acc[a][b]);
+                acc[a][b] = fmaf(v[a].w, c[b].w, acc[a][b]);
+            }
+    }
+}
+
+// The four row groups' partial sums into Zp, then (after the caller's barrier)
+// summed into Zs.
+__device__ __forceinline__ void put_partials(const float (&acc)[4][4], float* Zp) {
+    const int ti = threadIdx.x & 7, tc = (threadIdx.x >> 3) & 7, tr = threadIdx.x >> 6;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) Zp[(tr * 32 + ti + 8 * a) * LDZ + tc + 8 * b] = acc[a][b];
+}
+__device__ __forceinline__ void sum_partials(const float* Zp, float* Zs) {
+    const int i = threadIdx.x >> 3, cq = threadIdx.x & 7;
+    float4 s = *reinterpret_cast<const float4*>(Zp + i * LDZ + 4 * cq);
+#pragma unroll
+    for (int g = 1; g < 4; ++g) {
+        const float4 t = *reinterpret_cast<const float4*>(Zp + (g * 32 + i) * LDZ + 4 * cq);
+        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    *reinterpret_cast<float4*>(Zs + i * LDZ + 4 * cq) = s;
+}
+
+// Ws = T^T Zs (transposed) or T Zs.
+__device__ __forceinline__ void apply_t(const float* Ts, const float* Zs, float* Ws, bool transposed) {
+    const int i = threadIdx.x >> 3, cq = threadIdx.x & 7;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+        const float t = transposed ? Ts[k * LDZ + i] : Ts[i * LDZ + k];
+        const float4 z = *reinterpret_cast<const float4*>(Zs + k * LDZ + 4 * cq);
+        s.x = fmaf(t, z.x, s.x); s.y = fmaf(t, z.y, s.y); s.z = fmaf(t, z.z, s.z); s.w = fmaf(t, z.w, s.w);
+    }
+    *reinterpret_cast<float4*>(Ws + i * LDZ + 4 * cq) = s;
+}
+
+// C[c][r] -= sum_i V[i][r] W[i][c] on nq row quads, in place in shared memory.
+__device__ __forceinline__ void gemm_vw(const float* vbase, int ldv, const float* Ws, float* cbase, int ldc, int nq) {
+    const int trq = threadIdx.x & 7;
+    const int tcq = ((threadIdx.x >> 3) & 3) + 4 * ((threadIdx.x >> 5) & 1);
+    const int trb = threadIdx.x >> 6;
+    for (int rq = trq + 8 * trb; rq < nq; rq += 32) {
+        float4 c[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) c[b] = *reinterpret_cast<const float4*>(cbase + (4 * tcq + b) * ldc + 4 * rq);
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const float4 v = *reinterpret_cast<const float4*>(vbase + i * ldv + 4 * rq);
+            const float4 w = *reinterpret_cast<const float4*>(Ws + i * LDZ + 4 * tcq);
+            c[0].x = fmaf(-v.x, w.x, c[0].x); c[0].y = fmaf(-v.y, w.x, c[0].y);
+            c[0].z = fmaf(-v.z, w.x, c[0].z); c[0].w = fmaf(-v.w, w.x, c[0].w);
+            c[1].x = fmaf(-v.x, w.y, c[1].x); c[1].y = fmaf(-v.y, w.y, c[1].y);
+            c[1].z = fmaf(-v.z, w.y, c[1].z); c[1].w = fmaf(-v.w, w.y, c[1].w);
+            c[2].x = fmaf(-v.x, w.z, c[2].x); c[2].y = fmaf(-v.y, w.z, c[2].y);
+            c[2].z = fmaf(-v.z, w.z, c[2].z); c[2].w = fmaf(-v.w, w.z, c[2].w);
+            c[3].x = fmaf(-v.x, w.w, c[3].x); c[3].y = fmaf(-v.y, w.w, c[3].y);
+            c[3].z = fmaf(-v.z, w.w, c[3].z); c[3].w = fmaf(-v.w, w.w, c[3].w);
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) *reinterpret_cast<float4*>(cbase + (4 * tcq + b) * ldc + 4 * rq) = c[b];
+    }
+}
+
+// dst[row0 + r][c] (columns [col_begin, col_end), rows row0 .. row0 + mp) <-
+// (I - V op(T) V^T) src[same], 32 columns at a time. V is in s.Vs (mp rows), T
+// in s.Ts. src and dst may be the same matrix.
+template <class F>
+__device__ void update_columns(const Smem& s, int ldv, const float* src, size_t lds, const F& f, float* dst,
+                               size_t ldd, int row0, int mp, int col_begin, int col_end, bool transposed) {
+    for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+        const int tw = min(32, col_end - c0);
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+        const bool single = mp <= RC;
+        for (int r0 = 0; r0 < mp; r0 += RC) {
+            const int nr = min(RC, mp - r0);
+            __syncthreads();   // the tile buffer is free
+            load_tile(s.Cs, LDC, src, lds, row0 + r0, nr, c0, tw, f);
+            __syncthreads();
+            gemm_vtc(acc, s.Vs + r0, ldv, s.Cs, LDC, (nr + 3) >> 2);
+        }
+        put_partials(acc, s.Zp);
+        __syncthreads();
+        sum_partials(s.Zp, s.Zs);
+        __syncthreads();
+        apply_t(s.Ts, s.Zs, s.Ws, transposed);
+        __syncthreads();
+        for (int r0 = 0; r0 < mp; r0 += RC) {
+            const int nr = min(RC, mp - r0);
+            if (!single) {
+                __syncthreads();
+                load_tile(s.Cs, LDC, src, lds, row0 + r0, nr, c0, tw, f);
+                __syncthreads();
+            }
+            gemm_vw(s.Vs + r0, ldv, s.Ws, s.Cs, LDC, (nr + 3) >> 2);
+            __syncthreads();
+            store_tile(s.Cs, LDC, dst, ldd, row0 + r0, nr, c0, tw);
+        }
+    }
+    __syncthreads();
+}
+
+// Factors the panel in s.Vs (mp rows, jb columns) in place: afterwards column c
+// holds R's entries above the diagonal, the reflector's unscaled tail below it;
+// betas, taus, scs per column.
+__device__ void factor_panel(const Smem& s, int ldv, int mp, int jb) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        float ss = 0.0f;
+        for (int r = 1 + lane; r < mp; r += 32) ss = fmaf(s.Vs[r], s.Vs[r], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) s.colss[0] = ss;
+    }
+    if (threadIdx.x < 32) {
+        s.taus[threadIdx.x] = 0.0f;
+        s.scs[threadIdx.x] = 0.0f;
+        s.betas[threadIdx.x] = 0.0f;
+    }
+    __syncthreads();
+    for (int j = 0; j < jb; ++j) {
+        const float* vj = s.Vs + j * ldv;
+        float beta, tau, sc;
+        reflector(vj[j], s.colss[j], beta, tau, sc);
+        if (threadIdx.x == 0) {
+            s.taus[j] = tau;
+            s.scs[j] = sc;
+            s.betas[j] = beta;
+        }
+        for (int c = j + 1 + warp; c < jb; c += NT / 32) {
+            float* xc = s.Vs + c * ldv;
+            float  d = 0.0f;
+            for (int r = j + 1 + lane; r < mp; r += 32) d = fmaf(vj[r], xc[r], d);
+            d = warp_sum(d);
+            const float head = xc[j];
+            const float w = tau * fmaf(sc, d, head);
+            const float ws = w * sc;
+            float ss = 0.0f;
+            for (int r = j + 1 + lane; r < mp; r += 32) {
+                const float x = fmaf(-ws, vj[r], xc[r]);
+                xc[r] = x;
+                if (r > j + 1) ss = fmaf(x, x, ss);
+            }
+            __syncwarp();
+            if (lane == 0) xc[j] = head - w;
+            if (c == j + 1) {
+                ss = warp_sum(ss);
+                if (lane == 0) s.colss[j + 1] = ss;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// After factor_panel: writes the factored panel to the scratch matrix (R above
+// the diagonal, beta on it, the scaled reflector below) and leaves the clean V
+// (unit diagonal, zeros above, columns from jb on zero) in s.Vs.
+__device__ void finish_panel(const Smem& s, int ldv, int mp, int jb, float* W, size_t ldw, int k0) {
+    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+    const int nq = (mp + 3) >> 2;
+    const float sc = s.scs[c], beta = s.betas[c];
+    for (int rq = warp; rq < nq; rq += NT / 32) {
+        const int r = rq * 4;
+        float4 v = *reinterpret_cast<const float4*>(s.Vs + c * ldv + r);
+        float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int rr = r + t;
+            const float g = rr < c ? e[t] : (rr == c ? beta : e[t] * sc);
+            if (c < jb && rr < mp) W[(size_t)(k0 + rr) * ldw + k0 + c] = g;
+            e[t] = (c < jb && rr < mp) ? (rr < c ? 0.0f : (rr == c ? 1.0f : g)) : 0.0f;
+        }
+        *reinterpret_cast<float4*>(s.Vs + c * ldv + r) = make_float4(e[0], e[1], e[2], e[3]);
+    }
+    __syncthreads();
+}
+
+// T of the panel from its clean V in s.Vs: the Gram matrix into s.Zs, then
+// slarft's forward recurrence by one warp, a row of T per lane.
+__device__ void build_t(const Smem& s, int ldv, int mp) {
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+    gemm_vtc(acc, s.Vs, ldv, s.Vs, ldv, (mp + 3) >> 2);
+    put_partials(acc, s.Zp);
+    __syncthreads();
+    sum_partials(s.Zp, s.Zs);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int i = threadIdx.x;
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float tau = s.taus[j];
+            float a = 0.0f;
+#pragma unroll
+            for (int k = 0; k < j; ++k) a = fmaf(t[k], s.Zs[k * LDZ + j], a);
+            t[j] = i < j ? -tau * a : (i == j ? tau : 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s.Ts[i * LDZ + j] = t[j];
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
+    extern __shared__ __align__(16) float smem_raw[];
+    const Smem s = carve(smem_raw, p.ldv);
+    const int m = p.m, n = p.n, K = p.K, ldv = p.ldv;
+    float* W  = p.ws + (size_t)blockIdx.x * p.slot_floats;
+    float* Tg = W + (((size_t)m * n + 3) & ~(size_t)3);
+
+    for (uint32_t mat = blockIdx.x; mat < p.batch; mat += gridDim.x) {
+        const float* A = p.a + (size_t)mat * p.a_stride;
+        float*       Q = p.qc ? p.q + (size_t)mat * p.q_stride : nullptr;
+        float*       R = p.r + (size_t)mat * p.r_stride;
+
+        // 0. scan: largest magnitude, non-finite entries
+        int expo = 0;
+        if (p.scale) {
+            float amax = 0.0f;
+            int   bad = 0;
+            for (int i = threadIdx.x / 32; i < m; i += NT / 32)
+                for (int j = threadIdx.x & 31; j < n; j += 32) {
+                    const float v = A[(size_t)i * p.lda + j];
+                    amax = fmaxf(amax, fabsf(v));
+                    bad |= nonfinite(v);
+                }
+            amax = warp_max(amax);
+            bad = __any_sync(0xffffffffu, bad);
+            __syncthreads();   // s.red is free (previous matrix done)
+            if ((threadIdx.x & 31) == 0) s.red[threadIdx.x >> 5] = bad ? -1.0f : amax;
+            __syncthreads();
+            amax = 0.0f;
+            bad = 0;
+            for (int w = 0; w < NT / 32; ++w) {
+                const float v = s.red[w];
+                if (v < 0.0f) bad = 1; else amax = fmaxf(amax, v);
+            }
+            if (bad) {
+                for (size_t i = threadIdx.x; i < (size_t)m * p.qc; i += NT) Q[i] = qnan();
+                for (size_t i = threadIdx.x; i < (size_t)p.rr * n; i += NT) R[i] = qnan();
+                continue;
+            }
+            expo = amax_exponent(amax);
+        }
+        const LoadScaled from_a{Pow2(-expo)};
+
+        // 1. factor, panel by panel
+        for (int pi = 0; pi < p.npanels; ++pi) {
+            const int k0 = pi * JB, jb = min(JB, K - k0), mp = m - k0;
+            __syncthreads();
+            if (pi == 0) load_tile(s.Vs, ldv, A, p.lda, 0, mp, 0, jb, from_a);
+            else         load_tile(s.Vs, ldv, W, n, k0, mp, k0, jb, LoadPlain{});
+            __syncthreads();
+            factor_panel(s, ldv, mp, jb);
+            finish_panel(s, ldv, mp, jb, W, n, k0);
+            build_t(s, ldv, mp);
+            for (int i = threadIdx.x; i < 32 * 32; i += NT) Tg[(size_t)pi * 1024 + i] = s.Ts[(i >> 5) * LDZ + (i & 31)];
+            if (k0 + jb < n) {
+                if (pi == 0) update_columns(s, ldv, A, p.lda, from_a, W, n, 0, mp, jb, n, true);
+                else         update_columns(s, ldv, W, n, LoadPlain{}, W, n, k0, mp, k0 + jb, n, true);
+            }
+        }
+        __syncthreads();
+
+        // 2. R, back in the caller's scale
+        {
+            const Pow2 up(expo);
+            for (int i = threadIdx.x / 32; i < p.rr; i += NT / 32)
+                for (int j = threadIdx.x & 31; j < n; j += 32)
+                    R[(size_t)i * n + j] = (i < K && j >= i) ? up(W[(size_t)i * n + j]) : 0.0f;
+        }
+        if (!p.qc) continue;
+
+        // 3. Q = H_0 ... H_{K-1} [I; 0], block reflectors applied backward
+        const int qc = p.qc;
+        for (int i = threadIdx.x / 32; i < m; i += NT / 32)
+            for (int j = threadIdx.x & 31; j < qc; j += 32) Q[(size_t)i * qc + j] = i == j ? 1.0f : 0.0f;
+        __syncthreads();
+        for (int pi = p.npanels - 1; pi >= 0; --pi) {
+            const int k0 = pi * JB, jb = min(JB, K - k0), mp = m - k0;
+            __syncthreads();
+            {   // the reflectors back from the scratch matrix: rows relative to the panel
+                const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+                const int nq = (mp + 3) >> 2;
+                for (int rq = warp; rq < nq; rq += NT / 32) {
+                    const int r = rq * 4;
+                    float e[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (c < jb) {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const int rr = r + t;
+                            if (rr < mp) e[t] = rr > c ? W[(size_t)(k0 + rr) * n + k0 + c] : (rr == c ? 1.0f : 0.0f);
+                        }
+                    }
+                    *reinterpret_cast<float4*>(s.Vs + c * ldv + r) = make_float4(e[0], e[1], e[2], e[3]);
+                }
+            }
+            for (int i = threadIdx.x; i < 32 * 32; i += NT) s.Ts[(i >> 5) * LDZ + (i & 31)] = Tg[(size_t)pi * 1024 + i];
+            __syncthreads();
+            update_columns(s, ldv, Q, qc, LoadPlain{}, Q, qc, k0, mp, k0, qc, false);
+        }
+    }
+}
+
+} // namespace
+
+bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
+    if (m == 0 || n == 0 || m > 1024) return false;
+    const int ldv = (int)((m + 31) / 32) * 32 + 4;
+    return smem_bytes(ldv) <= ctx.smem_optin && (uint64_t)m * n < ((uint64_t)1 << 31);
+}
+
+void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr, const MidOptions& o) {
+    if (pr.batch == 0) return;
+    MidParams p{};
+    p.a = pr.a; p.q = pr.q; p.r = pr.r;
+    p.batch = pr.batch;
+    p.m = (int)pr.m; p.n = (int)pr.n; p.K = (int)qr_k(pr); p.qc = (int)pr.qc; p.rr = (int)pr.rr;
+    p.lda = o.lda ? (int)o.lda : (int)pr.n;
+    p.a_stride = o.a_stride ? o.a_stride : (uint64_t)pr.m * p.lda;
+    p.q_stride = o.q_stride ? o.q_stride : (uint64_t)pr.m * pr.qc;
+    p.r_stride = o.r_stride ? o.r_stride : (uint64_t)pr.rr * pr.n;
+    p.scale = o.scale ? 1 : 0;
+    p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
+    p.npanels = (p.K + JB - 1) / JB;
+    p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
+
+    const size_t smem = smem_bytes(p.ldv);
+    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+               "qr_mid shared memory");
+    int per_sm = 0;
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    if (per_sm < 1) throw std::runtime_error("qr_mid: the matrix does not fit a thread block");
+    const uint32_t slots = (uint32_t)std::min<uint64_t>(pr.batch, (uint64_t)per_sm * ctx.sm_count);
+    p.ws = static_cast<float*>(ctx.workspace(stream, (size_t)slots * p.slot_floats * sizeof(float)));
+    qr_mid_kernel<<<slots, NT, smem, stream>>>(p);
+    cuda_check(cudaGetLastError(), "qr_mid launch");
+}
+
+void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p) {
+    launch_qr_mid(ctx, stream, p, MidOptions{});
+}
+
+} // namespace mlb

@@ -1,0 +1,105 @@
+// Per-GPU contexts, the calling thread's stream and device, workspaces.
+#include "runtime.h"
+
+#include <memory>
+#include <new>
+#include <vector>
+
+namespace mlb {
+
+void cuda_check(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return;
+    cudaGetLastError();   // clear the sticky-less error so the next call starts clean
+    if (e == cudaErrorMemoryAllocation) throw std::bad_alloc();
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int device_count() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+DeviceGuard::DeviceGuard(int device) {
+    cuda_check(cudaGetDevice(&previous_), "cudaGetDevice");
+    if (device != previous_) cuda_check(cudaSetDevice(device), "cudaSetDevice");
+    else previous_ = -1;
+}
+DeviceGuard::~DeviceGuard() {
+    if (previous_ >= 0) cudaSetDevice(previous_);
+}
+
+namespace {
+std::mutex g_contexts_mutex;
+std::vector<std::unique_ptr<DeviceContext>> g_contexts;
+
+thread_local cudaStream_t t_stream = nullptr;
+thread_local int          t_device = 0;
+}
+
+DeviceContext& context(int device) {
+    std::lock_guard<std::mutex> lock(g_contexts_mutex);
+    const int n = device_count();
+    if (n == 0) throw std::runtime_error("no CUDA device: this library has no CPU path");
+    if (device < 0 || device >= n) throw std::invalid_argument("no such CUDA device: " + std::to_string(device));
+    if (g_contexts.size() < (size_t)n) g_contexts.resize(n);
+    if (!g_contexts[device]) {
+        auto c = std::make_unique<DeviceContext>();
+        c->device = device;
+        cudaDeviceProp prop{};
+        cuda_check(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+        c->sm_count   = prop.multiProcessorCount;
+        c->smem_optin = prop.sharedMemPerBlockOptin;
+        c->name       = prop.name;
+        DeviceGuard guard(device);
+        cuda_check(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking), "cudaStreamCreate");
+        for (int i = 0; i < 2; ++i) {
+            cuda_check(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming), "cudaEventCreate");
+            cuda_check(cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming), "cudaEventCreate");
+            cuda_check(cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming), "cudaEventCreate");
+        }
+        g_contexts[device] = std::move(c);
+    }
+    return *g_contexts[device];
+}
+
+void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) {
+    Workspace& w = workspaces[stream];
+    if (w.bytes < bytes) {
+        DeviceGuard guard(device);
+        if (w.data) cuda_check(cudaFree(w.data), "cudaFree");   // waits for the work that may still use it
+        w.data = nullptr;
+        w.bytes = 0;
+        const size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+        cuda_check(cudaMalloc(&w.data, want), "cudaMalloc");
+        w.bytes = want;
+    }
+    return w.data;
+}
+
+cudaStream_t thread_stream() { return t_stream; }
+void         set_thread_stream(cudaStream_t s) { t_stream = s; }
+int          thread_device() { return t_device; }
+void         set_thread_device(int device) {
+    if (device < 0 || device >= device_count())
+        throw std::invalid_argument("no such CUDA device: " + std::to_string(device));
+    t_device = device;
+}
+
+int pointer_device(const void* p) {
+    if (!p) return -1;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return attr.device;
+    return -1;
+}
+
+} // namespace mlb

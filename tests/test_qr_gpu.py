@@ -1,0 +1,457 @@
+"""Parity of the CUDA QR with the CPU oracle, through the C ABI, on a B200.
+
+The checks restate the reference's own suites: tests/test_qr.cpp (edge shapes,
+identity/zero/constant matrices, non-finite isolation, modes, magnitudes, nearly
+dependent columns), tests/test_core.cpp:134-167,407-437 (buffers), tests/
+test_c_api.c:29-81,201-206 (C API) and python-torch/tests/test_torch.py (the
+binding), with the tolerances of the benchmark definition: ||A - QR||_F / ||A||_F
+and ||Q^T Q - I||_F at most 10 n eps (eps = 2^-23), R within 1e-4 relative of
+the oracle's after sign normalisation, R's strict lower triangle exactly zero.
+"""
+import ctypes
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import harness
+import metal_linalg_torch as mlt
+from metal_linalg_torch import _lib, workloads
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import make_golden  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qr_golden.npz"))
+
+
+def gpu_qr(a, mode="reduced", kernel=None):
+    """numpy in, numpy out, through the C ABI on device pointers (the torch binding)."""
+    t = torch.as_tensor(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+    if kernel:
+        os.environ["QR_KERNEL"] = kernel
+    try:
+        q, r = mlt.qr(t, mode)
+    finally:
+        os.environ.pop("QR_KERNEL", None)
+    torch.cuda.synchronize()
+    return (q.cpu().numpy() if q.numel() else None), r.cpu().numpy()
+
+
+def check(a, q, r, mode, r_ref=None, tol_scale=1.0):
+    *lead, m, n = a.shape
+    k = min(m, n)
+    tol = workloads.tolerance(n) * tol_scale
+    rr = m if mode == "complete" else k
+    assert r.shape == (*lead, rr, n)
+    assert np.isfinite(r).all()
+    if rr > 1:
+        assert np.abs(np.tril(r, -1)).max() == 0.0, "R is not exactly upper triangular"
+    if mode == "complete" and m > k:
+        assert np.abs(r[..., k:, :]).max() == 0.0, "rows below K are not exactly zero"
+    if mode != "r":
+        qc = m if mode == "complete" else k
+        assert q.shape == (*lead, m, qc)
+        recon, orth, _ = harness.metrics(a, q, r)
+        assert recon.max() <= tol, f"reconstruction {recon.max():.3e} > {tol:.3e}"
+        assert orth.max() <= tol, f"orthogonality {orth.max():.3e} > {tol:.3e}"
+    if r_ref is not None:
+        par = harness.r_parity(r, r_ref)
+        assert par <= 1e-4, f"R differs from the oracle's by {par:.3e}"
+
+
+# ---------------------------------------------------------------------------
+# Shapes, modes, kernels
+# ---------------------------------------------------------------------------
+
+SMALL = [(1, 1), (1, 5), (5, 1), (2, 2), (3, 2), (2, 3), (7, 7), (8, 8), (9, 16), (16, 16), (16, 9), (17, 9),
+         (31, 32), (32, 31), (32, 32), (32, 8), (8, 32), (20, 13), (13, 20)]
+MID = [(33, 33), (40, 40), (64, 64), (64, 16), (16, 64), (100, 37), (37, 100), (96, 80), (128, 128), (129, 65),
+       (65, 129), (200, 200), (256, 256), (300, 40), (520, 520), (600, 64), (1024, 16), (1000, 130), (64, 2048),
+       (1024, 1024)]
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("shape", SMALL)
+def test_small_kernel_shapes(shape, mode):
+    m, n = shape
+    rng = np.random.default_rng(m * 100 + n)
+    a = rng.standard_normal((37, m, n)).astype(np.float32)     # 37: groups and warps only partly filled
+    assert mlt.qr_kernel(m, n, 37, mode) == "small"
+    q, r = gpu_qr(a, mode)
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("shape", MID)
+def test_mid_kernel_shapes(shape, mode):
+    m, n = shape
+    if mode == "complete" and m * m > 1 << 21:
+        batch = 1
+    else:
+        batch = 3
+    rng = np.random.default_rng(m * 100 + n)
+    a = rng.standard_normal((batch, m, n)).astype(np.float32)
+    q, r = gpu_qr(a, mode, kernel="mid")
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+def test_mid_kernel_on_small_shapes_agrees_with_small_kernel():
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((50, 24, 18)).astype(np.float32)
+    q1, r1 = gpu_qr(a, "reduced", kernel="small")
+    q2, r2 = gpu_qr(a, "reduced", kernel="mid")
+    assert np.abs(r1 - r2).max() <= 1e-5 * np.abs(r1).max()
+    assert np.abs(q1 - q2).max() <= 1e-5
+
+
+def test_large_batch_persistent_loop():
+    """More matrices than resident thread blocks: every slot is reused many times."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((1500, 48, 40)).astype(np.float32)
+    q, r = gpu_qr(a, "reduced")
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
+# ---------------------------------------------------------------------------
+# Golden vectors of the reference's own CPU path
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name,mode", [(n, md) for n, (_, mds) in make_golden.CASES.items() for md in mds])
+def test_against_reference_fixtures(name, mode):
+    a = make_golden.case_input(name)
+    q, r = gpu_qr(a, mode)
+    check(a, q, r, mode, GOLDEN[f"{name}/{mode}/r"])
+    if mode != "r" and name not in ("c3_256x256_rank224", "doc_3x3"):
+        qn, _ = harness.sign_normalise(q, r)
+        qr_, _ = harness.sign_normalise(GOLDEN[f"{name}/{mode}/q"], GOLDEN[f"{name}/{mode}/r"])
+        k = min(a.shape[-2:])
+        assert np.abs(qn[..., :k] - qr_[..., :k]).max() <= 1e-4
+
+
+def test_lapack_signs_in_small_and_mid_kernels():
+    """R's diagonal has LAPACK's signs (not just up to sign) where a matrix goes to a
+    warp or a thread block (reference: docs/qr.md:457-470)."""
+    rng = np.random.default_rng(2)
+    for shape in [(20, 16, 16), (5, 80, 72)]:
+        a = rng.standard_normal(shape).astype(np.float32)
+        _, r = gpu_qr(a, "r")
+        _, r_ref = harness.oracle_qr(a, "r")
+        d, d_ref = np.diagonal(r, axis1=-2, axis2=-1), np.diagonal(r_ref, axis1=-2, axis2=-1)
+        assert np.array_equal(np.sign(d), np.sign(d_ref))
+        assert np.abs(r - r_ref).max() <= 1e-4 * np.abs(r_ref).max()
+
+
+# ---------------------------------------------------------------------------
+# Special matrices (tests/test_qr.cpp:252-281,372-400)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(16, 16), (32, 20), (64, 64), (200, 100), (600, 64)])
+def test_identity_zero_constant(shape):
+    m, n = shape
+    eye = np.zeros((m, n), np.float32)
+    eye[np.arange(min(m, n)), np.arange(min(m, n))] = 1.0
+    a = np.stack([eye, np.zeros((m, n), np.float32), np.full((m, n), 3.25, np.float32),
+                  np.full((m, n), -1e-3, np.float32)])
+    q, r = gpu_qr(a, "reduced")
+    assert np.isfinite(q).all() and np.isfinite(r).all()
+    recon, orth, low = harness.metrics(a, q, r)
+    tol = workloads.tolerance(n)
+    assert recon.max() <= tol and low.max() == 0.0
+    # Q of the identity and of the constant matrices is orthonormal; the zero matrix's Q is I's columns
+    assert orth.max() <= tol
+    assert np.abs(r[1]).max() == 0.0
+
+
+@pytest.mark.parametrize("shape", [(12, 12), (32, 32), (70, 50), (300, 64)])
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+def test_nonfinite_isolation(shape, mode):
+    m, n = shape
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((5, m, n)).astype(np.float32)
+    a[1, m // 2, n // 3] = np.nan
+    a[3, m - 1, n - 1] = -np.inf
+    q, r = gpu_qr(a, mode)
+    for b in (1, 3):
+        assert np.isnan(r[b]).all()
+        if q is not None:
+            assert np.isnan(q[b]).all()
+    good = [0, 2, 4]
+    _, r_ref = harness.oracle_qr(a[good], mode)
+    check(a[good], None if q is None else q[good], r[good], mode, r_ref)
+
+
+@pytest.mark.parametrize("scale", [1e-3, 1e-5, 1e-20, 1e-30, 1e18, 1e30, 1e37])
+@pytest.mark.parametrize("shape", [(16, 16), (32, 32), (100, 60)])
+def test_magnitudes(shape, scale):
+    """tests/test_qr.cpp:557-603: accuracy is that of the unit-scale problem."""
+    m, n = shape
+    rng = np.random.default_rng(4)
+    unit = rng.standard_normal((4, m, n)).astype(np.float32)
+    unit /= np.abs(unit).max() * 1.5
+    a = (unit.astype(np.float64) * scale).astype(np.float32)
+    q, r = gpu_qr(a)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
+def test_mixed_magnitudes_in_one_batch():
+    rng = np.random.default_rng(6)
+    unit = rng.standard_normal((6, 24, 24)).astype(np.float64)
+    scales = np.array([1e-30, 1.0, 1e30, 1e-12, 1e37 / 8, 1e-38])
+    a = (unit * scales[:, None, None]).astype(np.float32)
+    q, r = gpu_qr(a)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
+@pytest.mark.parametrize("shape", [(32, 32), (128, 96)])
+def test_nearly_dependent_columns(shape):
+    """tests/test_qr.cpp:611-652: columns that differ by 1e-6 keep Q orthonormal."""
+    m, n = shape
+    rng = np.random.default_rng(8)
+    base = rng.standard_normal((3, m, 1))
+    a = (base + 1e-6 * rng.standard_normal((3, m, n))).astype(np.float32)
+    q, r = gpu_qr(a)
+    check(a, q, r, "reduced")
+
+
+def test_modes_agree():
+    """tests/test_qr.cpp:132-190: R alone equals the reduced R; the complete Q starts
+    with the reduced Q; rows below K are exactly zero."""
+    rng = np.random.default_rng(10)
+    for shape in [(6, 20, 12), (4, 90, 50), (4, 12, 20)]:
+        a = rng.standard_normal(shape).astype(np.float32)
+        q, r = gpu_qr(a, "reduced")
+        _, r1 = gpu_qr(a, "r")
+        qc, rc = gpu_qr(a, "complete")
+        k = min(shape[1:])
+        assert np.abs(r1 - r).max() <= 1e-5 * np.abs(r).max()
+        assert np.abs(qc[..., :k] - q).max() <= 1e-5
+        assert np.abs(rc[..., :k, :] - r).max() <= 1e-5 * np.abs(r).max()
+
+
+# ---------------------------------------------------------------------------
+# The benchmark configurations (full size where a CPU check is affordable)
+# ---------------------------------------------------------------------------
+
+def test_config1_full():
+    a = workloads.generate("c1_32x32").numpy()
+    q, r = gpu_qr(a)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
+def test_config2_full_magnitudes():
+    a = workloads.generate("c2_16x16_magnitudes")
+    t = a.cuda()
+    q, r = mlt.qr(t)
+    torch.cuda.synchronize()
+    # properties on the GPU in float64, on the unit-scale problem, for the whole batch
+    s = torch.as_tensor(harness.unit_scale(a.numpy()), device="cuda")
+    a64, r64, q64 = t.double() / s, r.double() / s, q.double()
+    tol = workloads.tolerance(16)
+    recon = torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)
+    orth = torch.linalg.matrix_norm(q64.mT @ q64 - torch.eye(16, device="cuda", dtype=torch.float64))
+    assert recon.max().item() <= tol and orth.max().item() <= tol
+    assert torch.count_nonzero(torch.tril(r, -1)).item() == 0
+    # R against the oracle on a sample across the batch
+    idx = np.arange(0, a.shape[0], 64)
+    sample = a.numpy()[idx]
+    _, r_ref = harness.oracle_qr(sample)
+    assert harness.r_parity(r[idx].cpu().numpy(), r_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete"])
+def test_config3_rank_deficient(mode):
+    a = workloads.generate("c3_256x256_rank224", batch=24).numpy()
+    q, r = gpu_qr(a, mode)
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+# ---------------------------------------------------------------------------
+# The C API on host and device pointers (tests/test_c_api.c of the reference)
+# ---------------------------------------------------------------------------
+
+def test_capi_host_pointers_known_answers():
+    lib = _lib.lib
+    a = np.array([1, 2, 3, 4, 5, 6, 2, 0, 0, 3, 1, 1], np.float32)
+    q, r = np.zeros(12, np.float32), np.zeros(8, np.float32)
+    assert lib.metal_linalg_qr(a.ctypes.data, 2, 3, 2, q.ctypes.data, r.ctypes.data) == _lib.OK, _lib.last_error()
+    A, Q, R = a.reshape(2, 3, 2), q.reshape(2, 3, 2), r.reshape(2, 2, 2)
+    assert R[0, 1, 0] == 0.0 and R[1, 1, 0] == 0.0
+    assert np.allclose(Q @ R, A, rtol=1e-5, atol=1e-5)
+    r_alone = np.zeros(8, np.float32)
+    assert lib.metal_linalg_qr_with_mode(a.ctypes.data, 2, 3, 2, 1, None, r_alone.ctypes.data) == _lib.OK
+    assert np.allclose(r_alone, r, rtol=1e-5, atol=1e-6)
+    qc, rc = np.zeros(18, np.float32), np.zeros(12, np.float32)
+    assert lib.metal_linalg_qr_with_mode(a.ctypes.data, 2, 3, 2, 2, qc.ctypes.data, rc.ctypes.data) == _lib.OK
+    QC, RC = qc.reshape(2, 3, 3), rc.reshape(2, 3, 2)
+    assert np.all(RC[:, 2, :] == 0.0)
+    assert np.allclose(np.swapaxes(QC, -1, -2) @ QC, np.eye(3), atol=1e-5)
+    assert np.allclose(QC @ RC, A, rtol=1e-5, atol=1e-5)
+    assert np.allclose(QC[:, :, :2], Q, atol=1e-5)
+    # an error, then a success (tests/test_c_api.c:201-206)
+    assert lib.metal_linalg_qr(None, 1, 2, 2, q.ctypes.data, r.ctypes.data) == _lib.INVALID_ARGUMENT
+    eye = np.eye(2, dtype=np.float32)
+    assert lib.metal_linalg_qr(eye.ctypes.data, 1, 2, 2, q.ctypes.data, r.ctypes.data) == _lib.OK
+    # an unaligned host pointer (tests/test_core.cpp:407-417)
+    buf = np.zeros(1 + 5 * 7 * 3, np.float32)
+    rng = np.random.default_rng(1)
+    buf[1:] = rng.standard_normal(5 * 7 * 3).astype(np.float32)
+    qq, rr = np.zeros(5 * 7 * 3, np.float32), np.zeros(5 * 3 * 3, np.float32)
+    assert lib.metal_linalg_qr(buf.ctypes.data + 4, 5, 7, 3, qq.ctypes.data, rr.ctypes.data) == _lib.OK
+    check(buf[1:].reshape(5, 7, 3), qq.reshape(5, 7, 3), rr.reshape(5, 3, 3), "reduced")
+
+
+def test_capi_host_pointers_staged_in_chunks():
+    """A host batch larger than one staging chunk: several chunks through both buffer sets."""
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((40000, 32, 32)).astype(np.float32)          # 160 MB in, 320 MB out
+    q, r = np.empty_like(a), np.empty_like(a)
+    assert _lib.lib.metal_linalg_qr(a.ctypes.data, a.shape[0], 32, 32, q.ctypes.data, r.ctypes.data) == _lib.OK
+    idx = np.arange(0, a.shape[0], 997)
+    _, r_ref = harness.oracle_qr(a[idx])
+    check(a[idx], q[idx], r[idx], "reduced", r_ref)
+    qd, rd = gpu_qr(a[-5:])
+    assert np.array_equal(qd, q[-5:]) and np.array_equal(rd, r[-5:])
+
+
+def test_capi_mixed_pointers_rejected():
+    a = torch.randn(2, 8, 8, device="cuda")
+    q = np.zeros((2, 8, 8), np.float32)
+    r = torch.empty(2, 8, 8, device="cuda")
+    status = _lib.lib.metal_linalg_qr(a.data_ptr(), 2, 8, 8, q.ctypes.data, r.data_ptr())
+    assert status == _lib.INVALID_ARGUMENT and "device" in _lib.last_error()
+
+
+def test_capi_device_pointers_on_a_side_stream():
+    a = torch.randn(64, 32, 32, device="cuda")
+    q, r = torch.empty_like(a), torch.empty_like(a)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    _lib.qr(a.data_ptr(), 64, 32, 32, q.data_ptr(), r.data_ptr(), "reduced", s.cuda_stream)
+    assert _lib.lib.metal_linalg_stream() == s.cuda_stream
+    assert _lib.lib.metal_linalg_synchronize() == _lib.OK
+    _lib.lib.metal_linalg_set_stream(None)
+    check(a.cpu().numpy(), q.cpu().numpy(), r.cpu().numpy(), "reduced")
+
+
+def test_device_queries():
+    assert "B200" in mlt.device_name()
+    assert mlt.gpu_core_count() == 148
+    assert mlt.qr_policy_source().startswith(("tuned:", "env:", "user"))
+    assert mlt.calibration_status() == ""
+    assert mlt.qr_kernel(32, 32, 1000) == "small" and mlt.qr_kernel(256, 256, 4096) == "mid"
+
+
+# ---------------------------------------------------------------------------
+# The torch binding (python-torch/tests/test_torch.py of the reference)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("lead", [(), (3,), (2, 3)])
+@pytest.mark.parametrize("shape", [(8, 8), (40, 24), (24, 40)])
+def test_binding_shapes_and_lead_dims(lead, shape):
+    a = torch.randn(*lead, *shape, device="cuda")
+    q, r = mlt.qr(a)
+    k = min(shape)
+    assert q.shape == (*lead, shape[0], k) and r.shape == (*lead, k, shape[1])
+    assert q.device == a.device and q.dtype == torch.float32
+    assert torch.count_nonzero(torch.tril(r, -1)).item() == 0
+    assert (q @ r - a).abs().max().item() < 2e-5 * max(1.0, a.abs().max().item()) * shape[1]
+    res = mlt.qr(a)
+    assert type(res).__name__ == "linalg_qr" and torch.equal(res.Q, q)
+
+
+def test_binding_dtypes_and_views():
+    a64 = torch.randn(4, 20, 20, device="cuda", dtype=torch.float64)
+    q, r = mlt.qr(a64)
+    assert q.dtype == torch.float32
+    assert (q.double() @ r.double() - a64).abs().max().item() < 1e-4
+    ai = torch.arange(12, device="cuda").reshape(3, 4) % 5
+    q, r = mlt.qr(ai)
+    assert (q @ r - ai.float()).abs().max().item() < 1e-5
+    base = torch.randn(6, 30, 50, device="cuda")
+    view = base[::2, :, ::2].mT                    # non-contiguous
+    q, r = mlt.qr(view)
+    assert (q @ r - view).abs().max().item() < 1e-4
+    qh, rh = mlt.qr(base[0].cpu())                 # a CPU tensor is staged through the GPU
+    assert qh.device.type == "cpu" and (qh @ rh - base[0].cpu()).abs().max().item() < 1e-4
+
+
+def test_binding_outputs_usable_at_once_on_the_stream():
+    a = torch.randn(256, 32, 32, device="cuda")
+    q, r = mlt.qr(a)
+    err = (q @ r - a).abs().max()                  # enqueued behind the QR on the same stream, no sync
+    assert err.item() < 1e-4
+
+
+@pytest.mark.parametrize("shape,mode", [((3, 10, 6), "reduced"), ((3, 6, 6), "complete"), ((2, 5, 9), "reduced"),
+                                        ((3, 10, 6), "r")])
+def test_binding_gradients_match_torch(shape, mode):
+    torch.manual_seed(3)
+    b, m, n = shape
+    a = torch.randn(*shape, device="cuda", dtype=torch.float32)
+    w0 = torch.randn(b, m, n, device="cuda", dtype=torch.float64)
+    w1 = torch.randn(b, m, m, device="cuda", dtype=torch.float64)
+    w2 = torch.randn(b, n, n, device="cuda", dtype=torch.float64)
+
+    def loss(q, r):
+        # invariant to the sign freedom of QR: R^T R, Q R and the projector Q Q^T
+        out = ((r.mT @ r).double() * w2).sum()
+        if mode != "r":
+            out = out + ((q @ r).double() * w0).sum() + ((q @ q.mT).double() * w1).sum()
+        return out
+
+    x = a.clone().requires_grad_(True)
+    q, r = mlt.qr(x, mode)
+    loss(q, r).backward()
+    y = a.double().clone().requires_grad_(True)
+    q2, r2 = torch.linalg.qr(y, mode="reduced" if mode == "r" else mode)
+    loss(q2, r2).backward()
+    assert (x.grad.double() - y.grad).abs().max().item() <= 2e-4 * max(1.0, y.grad.abs().max().item())
+
+
+def test_binding_opcheck_and_compile():
+    a = torch.randn(3, 12, 8, device="cuda")
+    torch.library.opcheck(torch.ops.metal_linalg.qr, (a, "reduced"),
+                          test_utils=("test_schema", "test_faketensor"))
+
+    @torch.compile(backend="aot_eager", fullgraph=True)
+    def f(x):
+        q, r = mlt.qr(x)
+        return q @ r
+
+    assert (f(a) - a).abs().max().item() < 1e-4
+
+
+def test_binding_threads():
+    import threading
+    a = torch.randn(128, 32, 32, device="cuda")
+    q0, r0 = mlt.qr(a)
+    torch.cuda.synchronize()
+    errors = []
+
+    def work():
+        try:
+            for _ in range(5):
+                q, r = mlt.qr(a)
+                torch.cuda.synchronize()
+                if not (torch.equal(q, q0) and torch.equal(r, r0)):
+                    errors.append("mismatch")
+        except Exception as e:   # pragma: no cover
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=work) for _ in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
