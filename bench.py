@@ -352,6 +352,30 @@ def other_configs(torch, mlt, _lib, workloads, args):
     return out
 
 
+PROFILE_CASES = {
+    # name: (batch, rows, cols, mode): small enough for an ncu capture to end by itself, larger than L2
+    "small32": (65536, 32, 32, "reduced"),
+    "small16": (262144, 16, 16, "reduced"),
+    "mid256": (592, 256, 256, "reduced"),
+    "tsqr": (8, 65536, 64, "reduced"),
+    "blocked4096": (1, 4096, 4096, "reduced"),
+}
+
+
+def run_profile_case(name, launches):
+    """A few launches of one configuration and nothing else: the target of the ncu captures."""
+    import torch
+
+    import metal_linalg_torch as mlt
+    from metal_linalg_torch import _lib
+    b, m, n, mode = PROFILE_CASES[name]
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn(b, m, n, generator=g, device="cuda")
+    sec, _ = time_config(torch, mlt, _lib, a, mode, launches, 1, None)
+    print(json.dumps({"profile_case": name, "kernel": mlt.qr_kernel(m, n, b, mode), "batch": b, "rows": m, "cols": n,
+                      "ms_per_launch": sec * 1e3}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -359,7 +383,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--headline-only", action="store_true", help="skip the other configurations and the CPU baseline")
+    ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), help="run a few launches of one small case and exit")
+    ap.add_argument("--launches", type=int, default=3)
     args = ap.parse_args()
+    if args.profile_case:
+        return run_profile_case(args.profile_case, args.launches)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
