@@ -23,6 +23,8 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <cstdlib>
+
 namespace mlb {
 
 namespace {
@@ -37,7 +39,7 @@ struct SmallParams {
 
 // R: rows held per lane (row capacity). G: lanes per matrix (column capacity).
 template <int R, int G>
-__global__ void __launch_bounds__(128) qr_small_kernel(const SmallParams p) {
+__global__ void __launch_bounds__(512) qr_small_kernel(const SmallParams p) {
     constexpr int kSteps = R < G ? R : G;
     const int lane  = threadIdx.x & 31;
     const int l     = lane % G;          // this lane's column
@@ -162,7 +164,12 @@ __global__ void __launch_bounds__(128) qr_small_kernel(const SmallParams p) {
 
 template <int R, int G>
 void launch(cudaStream_t stream, const SmallParams& p) {
-    constexpr int per_warp = 32 / G, warps_per_block = 4;
+    constexpr int per_warp = 32 / G;
+    static const int warps_per_block = [] {
+        const char* e = std::getenv("QR_SMALL_WARPS");
+        const int w = e ? std::atoi(e) : 8;
+        return w >= 1 && w <= 16 ? w : 8;
+    }();
     const uint32_t per_block = per_warp * warps_per_block;
     const uint32_t blocks = (p.batch + per_block - 1) / per_block;
     qr_small_kernel<R, G><<<blocks, 32 * warps_per_block, 0, stream>>>(p);
