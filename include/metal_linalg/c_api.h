@@ -65,6 +65,34 @@ typedef enum metal_linalg_qr_mode {
 metal_linalg_status metal_linalg_qr_with_mode(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
                                               metal_linalg_qr_mode mode, float* q, float* r);
 
+/* No counterpart in the reference. The QR for callers that must not allocate
+ * device memory at call time, or trigger the device-wide stall of a cudaFree:
+ * a request loop with a latency budget, or a process whose framework has
+ * already taken the GPU's memory for its own pool so that a library's
+ * cudaMalloc may fail. metal_linalg_qr_with_mode keeps the scratch memory of
+ * its block-per-matrix kernel in a workspace that grows on demand; this entry
+ * point runs the same kernel on a scratch array built into the library image
+ * instead (metal_linalg_qr_no_alloc_scratch_bytes() bytes, 32 MiB, held by every
+ * GPU that loads the library until the process exits). It calls no cudaMalloc,
+ * no cudaFree and no allocating library routine.
+ *
+ * a, q and r as metal_linalg_qr_with_mode's, but CUDA device pointers on one
+ * GPU only; the work is enqueued on the calling thread's stream. Limits: at most
+ * 1024 rows, and one matrix's scratch, 4 * (rows * cols + 1024 * ceil(min(rows,
+ * cols) / 32)) bytes, must fit the array; beyond either the call fails with
+ * METAL_LINALG_INVALID_ARGUMENT and a message that says which. Batches of any
+ * size are fine: fewer matrices are in flight at once when the array holds
+ * fewer slots.
+ *
+ * The first call on a GPU looks up the array's device address (once per GPU);
+ * make that call before any stream capture. Every call on a GPU shares the one
+ * array: each slot is rewritten in full before it is read, so nothing from an
+ * earlier call leaks into a later one, but two calls that overlap on the GPU
+ * (different streams or threads) race on it. Serialise them. */
+metal_linalg_status metal_linalg_qr_no_alloc(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
+                                             metal_linalg_qr_mode mode, float* q, float* r);
+uint64_t            metal_linalg_qr_no_alloc_scratch_bytes(void);
+
 /* ---------------------------------------------------------------------------
  * CUDA placement (no counterpart in the reference, whose memory is unified)
  * ------------------------------------------------------------------------- */

@@ -4,6 +4,9 @@
 #include <metal_linalg/c_api.h>
 #include <metal_linalg/core.h>
 
+#include "kernels.h"
+#include "runtime.h"
+
 #include <algorithm>
 #include <new>
 #include <stdexcept>
@@ -78,6 +81,28 @@ metal_linalg_status metal_linalg_qr_with_mode(const float* a, uint32_t batch, ui
         core::qr({a, batch, rows, cols}, qc ? q : nullptr, r, m);
     });
 }
+
+metal_linalg_status metal_linalg_qr_no_alloc(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
+                                             metal_linalg_qr_mode mode, float* q, float* r) {
+    return guarded([&] {
+        const core::QrMode m = mode_of(mode);
+        const uint32_t qc = core::qr_q_cols(m, rows, cols), rr = core::qr_r_rows(m, rows, cols);
+        require(present(a, (uint64_t)batch * rows * cols), "[qr_no_alloc] a is NULL");
+        if (qc) require(present(q, (uint64_t)batch * rows * qc), "[qr_no_alloc] q is NULL");
+        require(present(r, (uint64_t)batch * rr * cols), "[qr_no_alloc] r is NULL");
+        if (batch == 0 || rows == 0 || cols == 0) return;   // nothing to factor (and nothing to allocate for it)
+        const int device = mlb::pointer_device(a);
+        require(device >= 0, "[qr_no_alloc] takes CUDA device pointers only (staging host memory would allocate)");
+        require(mlb::pointer_device(r) == device && (!qc || mlb::pointer_device(q) == device),
+                "[qr_no_alloc] a, q and r must be device pointers on one GPU");
+        mlb::QrProblem p{};
+        p.a = a; p.q = qc ? q : nullptr; p.r = r;
+        p.batch = batch; p.m = rows; p.n = cols; p.qc = qc; p.rr = rr;
+        mlb::launch_qr_mid_static(device, mlb::thread_stream(), p);
+    });
+}
+
+uint64_t metal_linalg_qr_no_alloc_scratch_bytes(void) { return mlb::qr_mid_static_capacity_bytes(); }
 
 void  metal_linalg_set_stream(void* cuda_stream) { set_stream(cuda_stream); }
 void* metal_linalg_stream(void) { return stream(); }

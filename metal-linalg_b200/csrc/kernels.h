@@ -39,6 +39,13 @@ struct MidOptions {
 };
 void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p, const MidOptions& o);
 
+// The block-per-matrix kernel on scratch slots that are part of the library
+// image instead of the workspace: allocates and frees nothing. Device pointers
+// on `device`; throws std::invalid_argument beyond 1024 rows or when one matrix
+// needs more scratch than qr_mid_static_capacity_bytes().
+void   launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& p);
+size_t qr_mid_static_capacity_bytes();
+
 // A tall thin matrix as a tree of row blocks (explicit Q).
 bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc);
 void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);

@@ -29,6 +29,8 @@
 #include "kernels.h"
 
 #include <algorithm>
+#include <mutex>
+#include <string>
 
 namespace mlb {
 
@@ -500,6 +502,91 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr,
     const uint32_t slots = (uint32_t)std::min<uint64_t>(pr.batch, (uint64_t)per_sm * ctx.sm_count);
     p.ws = static_cast<float*>(ctx.workspace(stream, (size_t)slots * p.slot_floats * sizeof(float)));
     qr_mid_kernel<<<slots, NT, smem, stream>>>(p);
+    cuda_check(cudaGetLastError(), "qr_mid launch");
+}
+
+// ---------------------------------------------------------------------------
+// The same kernel on scratch memory that is part of the library image
+// ---------------------------------------------------------------------------
+// launch_qr_mid above takes its per-block scratch slots from a workspace that
+// it grows with cudaMalloc (and cudaFree, which stalls the whole GPU) when a
+// call needs more than any call before it. Some callers must never trigger
+// that: a serving loop with a latency budget, where one implicit device-wide
+// synchronisation is a missed deadline, and a process whose framework has
+// already claimed the GPU's memory for its own pool (PyTorch's caching
+// allocator at its cap, say), where a raw cudaMalloc from a library can simply
+// fail. For them the slots can live in the array below instead: it is part of
+// the loaded module, so every GPU that loads the library holds these 32 MiB
+// from load to exit, and nothing is allocated or freed at call time.
+//
+// Host code cannot pass `g_static_scratch` to a kernel: in host code that name
+// is only a handle for the runtime, not a device address. The address is
+// looked up once per GPU with cudaGetSymbolAddress, with that GPU current, on
+// the first call that runs there.
+constexpr size_t kStaticScratchFloats = (size_t)8 << 20;   // 32 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float*     g_static_address[kMaxDevices] = {};
+int        g_static_sms[kMaxDevices] = {};
+int        g_static_smem[kMaxDevices] = {};
+}
+
+size_t qr_mid_static_capacity_bytes() { return kStaticScratchFloats * sizeof(float); }
+
+void launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& pr) {
+    if (pr.batch == 0 || pr.m == 0 || pr.n == 0) return;
+    if (device < 0 || device >= kMaxDevices) throw std::invalid_argument("[qr_no_alloc] no such CUDA device");
+    DeviceGuard guard(device);
+    float* scratch = nullptr;
+    int sms = 0, smem_optin = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_address[device]) {   // first call on this GPU: the one-time set-up
+            float* address = nullptr;
+            cuda_check(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch),
+                       "cudaGetSymbolAddress(static scratch)");
+            cuda_check(cudaDeviceGetAttribute(&g_static_sms[device], cudaDevAttrMultiProcessorCount, device),
+                       "cudaDeviceGetAttribute");
+            cuda_check(cudaDeviceGetAttribute(&g_static_smem[device], cudaDevAttrMaxSharedMemoryPerBlockOptin, device),
+                       "cudaDeviceGetAttribute");
+            g_static_address[device] = address;
+        }
+        scratch = g_static_address[device];
+        sms = g_static_sms[device];
+        smem_optin = g_static_smem[device];
+    }
+    MidParams p{};
+    p.a = pr.a; p.q = pr.q; p.r = pr.r;
+    p.batch = pr.batch;
+    p.m = (int)pr.m; p.n = (int)pr.n; p.K = (int)qr_k(pr); p.qc = (int)pr.qc; p.rr = (int)pr.rr;
+    p.lda = (int)pr.n;
+    p.a_stride = (uint64_t)pr.m * pr.n;
+    p.q_stride = (uint64_t)pr.m * pr.qc;
+    p.r_stride = (uint64_t)pr.rr * pr.n;
+    p.scale = 1;
+    p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
+    p.npanels = (p.K + JB - 1) / JB;
+    p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
+    const size_t smem = smem_bytes(p.ldv);
+    if (pr.m > 1024 || smem > (size_t)smem_optin)
+        throw std::invalid_argument("[qr_no_alloc] takes matrices of at most 1024 rows, got " + std::to_string(pr.m));
+    if (p.slot_floats > kStaticScratchFloats)
+        throw std::invalid_argument("[qr_no_alloc] one " + std::to_string(pr.m) + " x " + std::to_string(pr.n) +
+                                    " matrix needs " + std::to_string(p.slot_floats * sizeof(float)) +
+                                    " bytes of scratch; the built-in scratch holds " +
+                                    std::to_string(kStaticScratchFloats * sizeof(float)));
+    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+               "qr_mid shared memory");
+    int per_sm = 0;
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    if (per_sm < 1) throw std::runtime_error("[qr_no_alloc] the matrix does not fit a thread block");
+    uint64_t slots = std::min<uint64_t>(pr.batch, (uint64_t)per_sm * sms);
+    slots = std::min<uint64_t>(slots, kStaticScratchFloats / p.slot_floats);   // fewer blocks, each looping longer
+    p.ws = scratch;
+    qr_mid_kernel<<<(unsigned)slots, NT, smem, stream>>>(p);
     cuda_check(cudaGetLastError(), "qr_mid launch");
 }
 

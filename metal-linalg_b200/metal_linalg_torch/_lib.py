@@ -38,6 +38,8 @@ def _load():
         "metal_linalg_last_error": (ctypes.c_char_p, []),
         "metal_linalg_qr": (ctypes.c_int, [_ptr, _u32, _u32, _u32, _ptr, _ptr]),
         "metal_linalg_qr_with_mode": (ctypes.c_int, [_ptr, _u32, _u32, _u32, ctypes.c_int, _ptr, _ptr]),
+        "metal_linalg_qr_no_alloc": (ctypes.c_int, [_ptr, _u32, _u32, _u32, ctypes.c_int, _ptr, _ptr]),
+        "metal_linalg_qr_no_alloc_scratch_bytes": (ctypes.c_uint64, []),
         "metal_linalg_set_stream": (None, [_ptr]),
         "metal_linalg_stream": (_ptr, []),
         "metal_linalg_set_device": (ctypes.c_int, [ctypes.c_int]),
