@@ -36,7 +36,13 @@ struct MidOptions {
     uint64_t q_stride = 0;      // floats between matrices of q (0: m * qc)
     uint64_t r_stride = 0;      // floats between matrices of r (0: rr * n)
     bool     scale    = true;   // scan and scale each matrix by a power of two; NaN-fill non-finite ones
+    // two-level indexing: with inner_count > 0, matrix i starts at (i / inner_count) * *_outer +
+    // (i % inner_count) * *_stride (row blocks of several tall matrices in one launch)
+    uint32_t inner_count = 0;
+    uint64_t a_outer = 0, q_outer = 0, r_outer = 0;
+    float*   ws       = nullptr;   // scratch of at least qr_mid_workspace_floats(...) floats (null: the stream's workspace)
 };
+size_t qr_mid_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch);
 void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p, const MidOptions& o);
 
 // The block-per-matrix kernel on scratch slots that are part of the library

@@ -54,6 +54,10 @@ struct MidParams {
     int          scale;
     int          ldv;
     int          npanels;
+    // matrix index -> (outer, inner) = (mat / inner_count, mat % inner_count) when inner_count > 0:
+    // the matrix's buffers then start at outer * *_outer + inner * *_stride
+    unsigned     inner_count;
+    unsigned long long a_outer, q_outer, r_outer;
 };
 
 struct Smem {
@@ -377,9 +381,16 @@ __global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
     float* Tg = W + (((size_t)m * n + 3) & ~(size_t)3);
 
     for (uint32_t mat = blockIdx.x; mat < p.batch; mat += gridDim.x) {
-        const float* A = p.a + (size_t)mat * p.a_stride;
-        float*       Q = p.qc ? p.q + (size_t)mat * p.q_stride : nullptr;
-        float*       R = p.r + (size_t)mat * p.r_stride;
+        size_t oa = (size_t)mat * p.a_stride, oq = (size_t)mat * p.q_stride, orr = (size_t)mat * p.r_stride;
+        if (p.inner_count) {
+            const size_t outer = mat / p.inner_count, inner = mat % p.inner_count;
+            oa = outer * p.a_outer + inner * p.a_stride;
+            oq = outer * p.q_outer + inner * p.q_stride;
+            orr = outer * p.r_outer + inner * p.r_stride;
+        }
+        const float* A = p.a + oa;
+        float*       Q = p.qc ? p.q + oq : nullptr;
+        float*       R = p.r + orr;
 
         // 0. scan: largest magnitude, non-finite entries
         int expo = 0;
@@ -478,9 +489,32 @@ bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
     return smem_bytes(ldv) <= ctx.smem_optin && (uint64_t)m * n < ((uint64_t)1 << 31);
 }
 
+namespace {
+uint64_t slot_floats_of(uint32_t m, uint32_t n) {
+    const uint32_t K = m < n ? m : n;
+    return (((uint64_t)m * n + 3) & ~(uint64_t)3) + (uint64_t)((K + JB - 1) / JB) * 1024;
+}
+uint32_t slots_of(const DeviceContext& ctx, uint32_t m, uint32_t batch) {
+    const size_t smem = smem_bytes((int)((m + 31) / 32) * 32 + 4);
+    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+               "qr_mid shared memory");
+    int per_sm = 0;
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    if (per_sm < 1) throw std::runtime_error("qr_mid: the matrix does not fit a thread block");
+    return (uint32_t)std::min<uint64_t>(batch, (uint64_t)per_sm * ctx.sm_count);
+}
+}
+
+size_t qr_mid_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch) {
+    if (batch == 0) return 0;
+    return (size_t)slots_of(ctx, m, batch) * slot_floats_of(m, n);
+}
+
 void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr, const MidOptions& o) {
     if (pr.batch == 0) return;
     MidParams p{};
+    p.inner_count = o.inner_count;
+    p.a_outer = o.a_outer; p.q_outer = o.q_outer; p.r_outer = o.r_outer;
     p.a = pr.a; p.q = pr.q; p.r = pr.r;
     p.batch = pr.batch;
     p.m = (int)pr.m; p.n = (int)pr.n; p.K = (int)qr_k(pr); p.qc = (int)pr.qc; p.rr = (int)pr.rr;
@@ -500,7 +534,7 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr,
     cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
     if (per_sm < 1) throw std::runtime_error("qr_mid: the matrix does not fit a thread block");
     const uint32_t slots = (uint32_t)std::min<uint64_t>(pr.batch, (uint64_t)per_sm * ctx.sm_count);
-    p.ws = static_cast<float*>(ctx.workspace(stream, (size_t)slots * p.slot_floats * sizeof(float)));
+    p.ws = o.ws ? o.ws : static_cast<float*>(ctx.workspace(stream, (size_t)slots * p.slot_floats * sizeof(float)));
     qr_mid_kernel<<<slots, NT, smem, stream>>>(p);
     cuda_check(cudaGetLastError(), "qr_mid launch");
 }

@@ -1,6 +1,229 @@
-// placeholder
+// TSQR: a tall thin matrix (m >> n, n <= 128) as a tree of row blocks, for the
+// reduced factorisation and for R alone.
+//
+// It takes the place of the reference's TSQR panel kernels bd_tsqr_leaf /
+// bd_tsqr_top / bd_tsqr_rebuild (shaders/Svd_Bidiag.metal:583-869; host side
+// src/band_reduce.mm:196-251), which the reference reaches for every matrix
+// taller than a threadgroup holds (src/qr_householder.mm:387-391). The
+// reference reconstructs Householder vectors from the tree because its caller
+// needs them for a trailing update; a tall thin QR has no trailing matrix, so
+// here the tree's Q is formed explicitly and no reconstruction is needed:
+//
+//   level 0   the matrix is cut into blocks of `c` rows; each block is factored
+//             by the block-per-matrix kernel (qr_mid.cu), its Q written in place
+//             into the output Q and its n x n R onto a stack;
+//   level l   the stack of R's (itself a tall matrix, c/n times shorter) is cut
+//             and factored the same way, until at most 1024 rows remain, which
+//             one block factors: its R is the matrix's R;
+//   down      Q's blocks are multiplied from the right by the n x n blocks of
+//             the level above, level by level (tsqr_apply_kernel below).
+//
+// Algorithmic traffic is A read once, Q and R written once; this scheme reads A,
+// writes Q, reads and rewrites Q once more on the way down, and the stacks are a
+// fraction n/c of that. R's diagonal has the signs of the top-level factorisation,
+// which need not be LAPACK's for the whole matrix (the reference's TSQR likewise).
+// A block holding a NaN or an infinity gives NaN R for that block, so the stack,
+// the top-level Q and with it every entry of the matrix's Q and R are NaN.
+#include "common.cuh"
 #include "kernels.h"
+
+#include <algorithm>
+#include <vector>
+
 namespace mlb {
-bool qr_tsqr_fits(const DeviceContext&, uint32_t, uint32_t, uint32_t) { return false; }
-void launch_qr_tsqr(DeviceContext&, cudaStream_t, const QrProblem&) { throw std::runtime_error("qr_tsqr: not built"); }
+
+namespace {
+
+constexpr int TR = 64;          // rows of Q per thread block of the apply kernel
+constexpr int LDX = TR + 4;     // leading dimension of the transposed tile
+
+struct ApplyParams {
+    float*       q;             // blocks of rows: block i of matrix b at b * q_outer + i * q_stride
+    const float* up;            // n x n factors: that block's at (b * blocks + i) * n * n
+    unsigned     blocks;        // row blocks per matrix
+    unsigned     rows, last_rows;   // rows of a block, and of a matrix's last block
+    unsigned     tiles;         // ceil(max(rows, last_rows) / TR)
+    int          n, np;         // columns, and columns rounded up to 64
+    unsigned long long q_outer, q_stride;
+    unsigned long long total;   // matrices * blocks * tiles
+};
+
+// Q_block <- Q_block * B in place: TR rows at a time, the tile transposed in
+// shared memory so that four rows of a column are one 16-byte word, B row-major.
+__global__ void __launch_bounds__(256) tsqr_apply_kernel(const ApplyParams p) {
+    extern __shared__ __align__(16) float sm[];
+    float* Xs = sm;                      // [n][LDX]
+    float* Bs = sm + (size_t)p.n * LDX;  // [n][np]
+    const int n = p.n, np = p.np;
+    const int rg = threadIdx.x >> 4, cg = threadIdx.x & 15;   // 16 row quads x 16 column quads (per 64 columns)
+    for (unsigned long long work = blockIdx.x; work < p.total; work += gridDim.x) {
+        const unsigned tile = (unsigned)(work % p.tiles);
+        const unsigned long long blk = work / p.tiles;
+        const unsigned i = (unsigned)(blk % p.blocks);
+        const unsigned long long b = blk / p.blocks;
+        const unsigned rows = i + 1 == p.blocks ? p.last_rows : p.rows;
+        const unsigned r0 = tile * TR;
+        if (r0 >= rows) continue;
+        const unsigned nr = min((unsigned)TR, rows - r0);
+        float* Q = p.q + b * p.q_outer + (unsigned long long)i * p.q_stride + (size_t)r0 * n;
+        const float* B = p.up + blk * (unsigned long long)n * n;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * np; idx += 256) {
+            const int k = idx / np, c = idx % np;
+            Bs[idx] = c < n ? B[(size_t)k * n + c] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < TR * n; idx += 256) {
+            const int r = idx / n, k = idx % n;
+            Xs[k * LDX + r] = (unsigned)r < nr ? Q[(size_t)r * n + k] : 0.0f;
+        }
+        __syncthreads();
+        for (int c0 = 0; c0 < np; c0 += 64) {
+            float acc[4][4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[a][e] = 0.0f;
+#pragma unroll 4
+            for (int k = 0; k < n; ++k) {
+                const float4 x = *reinterpret_cast<const float4*>(Xs + k * LDX + 4 * rg);
+                const float4 w = *reinterpret_cast<const float4*>(Bs + k * np + c0 + 4 * cg);
+                const float xv[4] = {x.x, x.y, x.z, x.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[a][e] = fmaf(xv[a], wv[e], acc[a][e]);
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const unsigned r = 4 * rg + a;
+                if (r < nr) {
+                    const int c = c0 + 4 * cg;
+                    if ((n & 3) == 0 && c < n) {   // rows of Q are 16-byte aligned: one word a thread
+                        *reinterpret_cast<float4*>(Q + (size_t)r * n + c) =
+                            make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (c + e < n) Q[(size_t)r * n + c + e] = acc[a][e];
+                    }
+                }
+            }
+        }
+    }
 }
+
+struct Level {
+    uint32_t rows;        // rows of this level's matrix (per input matrix)
+    uint32_t c;           // rows of a block
+    uint32_t blocks;      // blocks per matrix; the last has rows - (blocks - 1) * c
+    uint32_t last_rows;
+};
+
+uint32_t block_rows(uint32_t n) { return n <= 64 ? 256 : 512; }
+
+// The levels below the top: each cuts `rows` into blocks of c (the last takes the remainder, < 2c).
+std::vector<Level> plan(uint32_t m, uint32_t n) {
+    std::vector<Level> levels;
+    const uint32_t c = block_rows(n);
+    uint32_t rows = m;
+    while (rows > 1024) {
+        Level L{rows, c, rows / c, 0};
+        L.last_rows = rows - (L.blocks - 1) * c;
+        levels.push_back(L);
+        rows = L.blocks * n;
+    }
+    return levels;
+}
+
+} // namespace
+
+bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc) {
+    // reduced or R alone (Q of n columns or none), at most 128 columns, at least two levels' worth of rows
+    return n >= 1 && n <= 128 && m > 1024 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
+}
+
+void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr) {
+    if (pr.batch == 0) return;
+    const uint32_t m = pr.m, n = pr.n, batch = pr.batch;
+    const bool want_q = pr.qc != 0;
+    const std::vector<Level> levels = plan(m, n);
+    const size_t nl = levels.size();
+    const uint32_t top_rows = levels.back().blocks * n;
+
+    // workspace: per level l >= 1 the stack S_l (its input) and, with Q wanted, Q_l of the same
+    // shape; the top's Q; the scratch slots of the largest qr_mid launch
+    auto up64 = [](size_t f) { return (f + 63) & ~(size_t)63; };
+    std::vector<size_t> s_off(nl + 1, 0), q_off(nl + 1, 0);
+    size_t total = 0;
+    for (size_t l = 1; l <= nl; ++l) {
+        const size_t floats = (size_t)batch * levels[l - 1].blocks * n * n;   // S_l: blocks of level l-1, n x n each
+        s_off[l] = total; total += up64(floats);
+        if (want_q) { q_off[l] = total; total += up64(floats); }
+    }
+    size_t mid_floats = qr_mid_workspace_floats(ctx, top_rows, n, batch);
+    for (const Level& L : levels) {
+        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, L.c, n, batch * (L.blocks - 1)));
+        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, L.last_rows, n, batch));
+    }
+    const size_t mid_off = total;
+    total += up64(mid_floats);
+    float* ws = static_cast<float*>(ctx.workspace(stream, total * sizeof(float)));
+
+    // up the tree
+    for (size_t l = 0; l < nl; ++l) {
+        const Level& L = levels[l];
+        const float* in = l == 0 ? pr.a : ws + s_off[l];
+        float* qout = !want_q ? nullptr : (l == 0 ? pr.q : ws + q_off[l]);
+        float* rout = ws + s_off[l + 1];
+        const uint64_t in_outer = (uint64_t)L.rows * n, r_outer = (uint64_t)L.blocks * n * n;
+        MidOptions o;
+        o.ws = ws + mid_off;
+        o.a_stride = (uint64_t)L.c * n; o.q_stride = (uint64_t)L.c * n; o.r_stride = (uint64_t)n * n;
+        o.a_outer = in_outer; o.q_outer = in_outer; o.r_outer = r_outer;
+        if (L.blocks > 1) {   // the full blocks of every matrix in one launch
+            QrProblem p{in, qout, rout, batch * (L.blocks - 1), L.c, n, want_q ? n : 0, n};
+            o.inner_count = L.blocks - 1;
+            launch_qr_mid(ctx, stream, p, o);
+        }
+        {   // each matrix's last block (c rows plus the remainder)
+            const uint64_t skip = (uint64_t)(L.blocks - 1);
+            QrProblem p{in + skip * L.c * n, qout ? qout + skip * L.c * n : nullptr, rout + skip * n * n, batch,
+                        L.last_rows, n, want_q ? n : 0, n};
+            o.inner_count = 1;
+            launch_qr_mid(ctx, stream, p, o);
+        }
+    }
+    // the top: one block per matrix; its R is the matrix's R
+    {
+        MidOptions o;
+        o.ws = ws + mid_off;
+        QrProblem p{ws + s_off[nl], want_q ? ws + q_off[nl] : nullptr, pr.r, batch, top_rows, n, want_q ? n : 0, n};
+        launch_qr_mid(ctx, stream, p, o);
+    }
+    if (!want_q) return;
+
+    // down the tree: level l's Q blocks times the n x n blocks of level l+1's Q
+    const int np = (int)((n + 63) / 64 * 64);
+    const size_t smem = ((size_t)n * LDX + (size_t)n * np) * sizeof(float);
+    cuda_check(cudaFuncSetAttribute(tsqr_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+               "tsqr_apply shared memory");
+    for (size_t l = nl; l-- > 0;) {
+        const Level& L = levels[l];
+        ApplyParams a{};
+        a.q = l == 0 ? pr.q : ws + q_off[l];
+        a.up = ws + q_off[l + 1];
+        a.blocks = L.blocks;
+        a.rows = L.c;
+        a.last_rows = L.last_rows;
+        a.tiles = (std::max(L.c, L.last_rows) + TR - 1) / TR;
+        a.n = (int)n; a.np = np;
+        a.q_outer = (uint64_t)L.rows * n;
+        a.q_stride = (uint64_t)L.c * n;
+        a.total = (uint64_t)batch * L.blocks * a.tiles;
+        const unsigned grid = (unsigned)std::min<uint64_t>(a.total, (uint64_t)ctx.sm_count * 8);
+        tsqr_apply_kernel<<<grid, 256, smem, stream>>>(a);
+        cuda_check(cudaGetLastError(), "tsqr_apply launch");
+    }
+}
+
+} // namespace mlb

@@ -101,6 +101,43 @@ def test_mid_kernel_shapes(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
+TALL = [(1025, 8), (1500, 64), (2048, 64), (4096, 16), (5000, 33), (20000, 40), (17000, 24), (9000, 128), (70000, 5)]
+
+
+@pytest.mark.parametrize("mode", ["reduced", "r"])
+@pytest.mark.parametrize("shape", TALL)
+def test_tsqr_shapes(shape, mode):
+    """Tall thin matrices through the tree of row blocks (the reference's TSQR depth cases,
+    tests/test_qr.cpp:364-367, among them)."""
+    m, n = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((2, m, n)).astype(np.float32)
+    assert mlt.qr_kernel(m, n, 2, mode) == "tsqr"
+    q, r = gpu_qr(a, mode)
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+def test_tsqr_nonfinite_and_constant():
+    rng = np.random.default_rng(14)
+    a = rng.standard_normal((4, 3000, 48)).astype(np.float32)
+    a[1, 2999, 47] = np.nan
+    a[2] = 2.5                                   # constant: rank one
+    q, r = gpu_qr(a)
+    assert np.isnan(q[1]).all() and np.isnan(r[1]).all()
+    good = [0, 2, 3]
+    check(a[good], q[good], r[good], "reduced")
+    _, r_ref = harness.oracle_qr(a[[0, 3]])
+    assert harness.r_parity(r[[0, 3]], r_ref) <= 1e-4
+
+
+def test_config4_tall_shrunk_batch():
+    a = workloads.generate("c4_65536x64_tall", batch=2).numpy()
+    q, r = gpu_qr(a)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
 def test_mid_kernel_on_small_shapes_agrees_with_small_kernel():
     rng = np.random.default_rng(5)
     a = rng.standard_normal((50, 24, 18)).astype(np.float32)
