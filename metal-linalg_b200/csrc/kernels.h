@@ -56,6 +56,17 @@ size_t qr_mid_static_capacity_bytes();
 bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc);
 void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
 
+// The tree on strided input with caller-provided scratch (the blocked QR's panels use it): thin QR of
+// `batch` m x n matrices (n <= 128, m >= n) read with row stride lda and matrix stride a_outer; q
+// [batch][m][n] contiguous or null (R alone); r n x n per matrix at stride r_outer.
+size_t tsqr_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, bool want_q);
+void   tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m,
+                 uint32_t n, uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws);
+// out_block = q_block * factor for row blocks of n columns (see qr_tsqr.cu).
+void   launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q, uint64_t q_outer, uint64_t q_stride,
+                         float* out, uint64_t out_outer, uint64_t out_stride, uint64_t out_ld, const float* up,
+                         bool shared_up, uint32_t batch, uint32_t blocks, uint32_t rows, uint32_t last_rows, uint32_t n);
+
 // Blocked compact-WY QR over the whole grid, any shape.
 bool qr_blocked_fits(uint32_t m, uint32_t n);
 void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);

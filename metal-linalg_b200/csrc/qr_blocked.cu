@@ -1,6 +1,405 @@
-// placeholder
+// The blocked compact-WY QR: one matrix spread over the whole grid, any shape.
+//
+// It takes the place of the reference's qr_blocked (src/qr_blocked.mm:56-302 with
+// src/band_reduce.mm:196-507 and the panel kernels of shaders/Svd_Bidiag.metal:
+// 428-886,1125-1279): a scaled working copy of the matrix, panels factored by
+// TSQR with Householder reconstruction, the trailing matrix updated by a block
+// reflector per panel, R read off the working copy, Q formed backward from
+// [I; 0] by the same block reflectors.
+//
+// Per panel of 32 columns (rows k0..m, columns k0..k0+jb of the working copy W):
+//
+//   1. thin QR of the panel by the tree of row blocks (tsqr_core: the
+//      block-per-matrix kernel on blocks of 256 rows, then on the stack of their
+//      R's): explicit Qp (mp x jb) and Rp;
+//   2. Householder reconstruction (Ballard, Demmel, Grigori, Jacquelin, Nguyen,
+//      Solomonik, "Reconstructing Householder vectors from TSQR", 2014; the
+//      reference does the same in bd_tsqr_top, shaders/Svd_Bidiag.metal:757-802):
+//      LU without pivoting of Qp - [S; 0] with the signs S = -sgn(pivot) chosen on
+//      the way, so that every pivot is at least 1 in magnitude: L is the unit lower
+//      trapezoidal Y of the compact-WY form, T = -U S L1^-T, and the panel's R is
+//      S Rp. Only the top jb x jb block takes part in the elimination
+//      (reconstruct_kernel, one warp); the rows below are Qp U^-1, a product;
+//   3. the block reflector applied to the columns right of the panel:
+//      C -= Y (T^T (Y^T C)) as Zp = Y^T C by row chunks (ytc_kernel), the chunks
+//      summed and multiplied by T^T (reduce_t_kernel), C -= Y Z (yz_kernel).
+//
+// Y is kept apart from W (clean: unit diagonal, zeros above) so that the products
+// read it as a plain matrix. The products here are register-tiled FP32 FMA
+// kernels reading 16-byte words from shared memory.
+#include "common.cuh"
 #include "kernels.h"
+
+#include <algorithm>
+#include <vector>
+
 namespace mlb {
-bool qr_blocked_fits(uint32_t, uint32_t) { return false; }
-void launch_qr_blocked(DeviceContext&, cudaStream_t, const QrProblem&) { throw std::runtime_error("qr_blocked: not built"); }
+
+namespace {
+
+constexpr int NB  = 32;     // panel width
+constexpr int RCH = 256;    // rows per chunk of the Y^T C partial sums
+
+struct MatInfo {            // per matrix, written by the scan
+    unsigned amax_bits;     // bit pattern of the largest magnitude (non-negative floats order as integers)
+    unsigned bad;           // a NaN or an infinity was seen
+};
+
+__global__ void scan_kernel(const float* a, size_t count, MatInfo* info) {
+    float amax = 0.0f;
+    int   bad = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = a[i];
+        amax = fmaxf(amax, fabsf(v));
+        bad |= nonfinite(v);
+    }
+    amax = warp_max(amax);
+    bad = __any_sync(0xffffffffu, bad);
+    if ((threadIdx.x & 31) == 0) {
+        if (bad) atomicOr(&info->bad, 1u);
+        else atomicMax(&info->amax_bits, __float_as_uint(amax));
+    }
 }
+
+__device__ __forceinline__ int info_exponent(const MatInfo* info) {
+    return info->bad ? 0 : amax_exponent(__uint_as_float(info->amax_bits));
+}
+
+// W (ld ldw) = A * 2^-e
+__global__ void scale_copy_kernel(const float* a, float* w, uint32_t m, uint32_t n, uint32_t ldw, const MatInfo* info) {
+    const Pow2 down(-info_exponent(info));
+    const size_t total = (size_t)m * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / n, c = i % n;
+        w[r * ldw + c] = down(a[i]);
+    }
+}
+
+// R [rr][n] = the upper trapezoid of W's first K rows * 2^e, zeros elsewhere; NaN for a non-finite matrix
+__global__ void r_out_kernel(const float* w, uint32_t ldw, float* r, uint32_t rr, uint32_t n, uint32_t K,
+                             const MatInfo* info) {
+    const Pow2 up(info_exponent(info));
+    const bool bad = info->bad != 0;
+    const size_t total = (size_t)rr * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / n, c = i % n;
+        float v = (row < K && c >= row) ? up(w[row * ldw + c]) : 0.0f;
+        r[i] = bad ? qnan() : v;
+    }
+}
+
+__global__ void nan_fill_kernel(float* q, size_t count, const MatInfo* info) {
+    if (!info->bad) return;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        q[i] = qnan();
+}
+
+// ---------------------------------------------------------------------------
+// Householder reconstruction of one panel (one warp)
+// ---------------------------------------------------------------------------
+struct ReconParams {
+    const float* qp;        // [mp][jb] explicit thin Q of the panel
+    const float* rp;        // [jb][jb] its R
+    float*       w;         // the working copy: the panel's R (S Rp) goes to rows/cols k0..
+    float*       y;         // Y: the unit lower triangular top block goes to rows k0..k0+jb, columns k0..
+    float*       t;         // [32][32] T, zero padded
+    float*       uinv;      // [jb][jb] U^-1, for the rows below the top block
+    uint32_t     ldw, ldy, k0, jb;
+};
+
+__global__ void __launch_bounds__(32) reconstruct_kernel(const ReconParams p) {
+    __shared__ float M[32][33], Ui[32][33], Tm[32][33];
+    __shared__ float sgn[32];
+    const int i = threadIdx.x, jb = (int)p.jb;
+    for (int c = 0; c < 32; ++c) {
+        M[i][c] = (i < jb && c < jb) ? p.qp[(size_t)i * jb + c] : (i == c ? 1.0f : 0.0f);
+        Ui[i][c] = 0.0f;
+        Tm[i][c] = 0.0f;
+    }
+    __syncwarp();
+    // LU of Q1 - S, S = -sgn(pivot) chosen at each step: every pivot has magnitude >= 1
+    for (int j = 0; j < jb; ++j) {
+        const float d = M[j][j];
+        const float s = d >= 0.0f ? -1.0f : 1.0f;
+        const float piv = d - s;
+        __syncwarp();
+        if (i == j) {
+            M[j][j] = piv;
+            sgn[j] = s;
+        }
+        float l = 0.0f;
+        if (i > j && i < jb) {
+            l = M[i][j] / piv;
+            M[i][j] = l;
+        }
+        __syncwarp();
+        if (i > j && i < jb)
+            for (int c = j + 1; c < jb; ++c) M[i][c] = fmaf(-l, M[j][c], M[i][c]);
+        __syncwarp();
+    }
+    // U^-1, a column per lane: U x = e_c by back substitution
+    if (i < jb) {
+        const int c = i;
+        float x[32];
+#pragma unroll
+        for (int r = 31; r >= 0; --r) {
+            float v = 0.0f;
+            if (r <= c && r < jb) {
+                float acc = r == c ? 1.0f : 0.0f;
+#pragma unroll
+                for (int k = r + 1; k < 32; ++k)
+                    if (k <= c) acc = fmaf(-M[r][k], x[k], acc);
+                v = acc / M[r][r];
+            }
+            x[r] = v;
+        }
+#pragma unroll
+        for (int r = 0; r < 32; ++r)
+            if (r < jb) Ui[r][c] = x[r];
+    }
+    __syncwarp();
+    // T = -U S L1^-T: row i of T from T L1^T = -U S, forward over the columns
+    if (i < jb) {
+        float t[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float v = 0.0f;
+            if (c >= i && c < jb) {
+                float acc = -M[i][c] * sgn[c];
+#pragma unroll
+                for (int k = 0; k < c; ++k)
+                    if (k >= i) acc = fmaf(-t[k], M[c][k], acc);   // L1[c][k], k < c
+                v = acc;
+            }
+            t[c] = v;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) Tm[i][c] = t[c];
+    }
+    __syncwarp();
+    for (int c = 0; c < 32; ++c) p.t[i * 32 + c] = Tm[i][c];
+    if (i < jb) {
+        for (int c = 0; c < jb; ++c) {
+            p.uinv[(size_t)i * jb + c] = Ui[i][c];
+            // Y's top block: unit lower triangular L1
+            p.y[(size_t)(p.k0 + i) * p.ldy + p.k0 + c] = c < i ? M[i][c] : (c == i ? 1.0f : 0.0f);
+            // the panel's R: S Rp, upper triangular (the part of W below it is never read)
+            if (c >= i) p.w[(size_t)(p.k0 + i) * p.ldw + p.k0 + c] = sgn[i] * p.rp[(size_t)i * jb + c];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Block reflector application: three kernels
+// ---------------------------------------------------------------------------
+
+// Zp[chunk][i][j] = sum over the chunk's rows r of Y[r][i] C[r][j]; i < 32 (columns of Y from jb on
+// read as zero), j < nc. Grid (ceil(nc / 128), chunks). A thread accumulates 4 x 4.
+__global__ void __launch_bounds__(256) ytc_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ C,
+                                                  size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* Zp,
+                                                  uint32_t ncp) {
+    __shared__ __align__(16) float Ys[32][36];
+    __shared__ __align__(16) float Cs[32][132];
+    const int ti = threadIdx.x & 7, tj = threadIdx.x >> 3;
+    const uint32_t j0 = blockIdx.x * 128;
+    const uint32_t r_begin = blockIdx.y * RCH, r_end = min(mp, r_begin + RCH);
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+    for (uint32_t r0 = r_begin; r0 < r_end; r0 += 32) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 32 * 32; idx += 256) {
+            const uint32_t r = r0 + (idx >> 5), i = idx & 31;
+            Ys[idx >> 5][i] = (r < r_end && i < jb) ? Y[(size_t)r * ldy + i] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < 32 * 128; idx += 256) {
+            const uint32_t r = r0 + (idx >> 7), j = j0 + (idx & 127);
+            Cs[idx >> 7][idx & 127] = (r < r_end && j < nc) ? C[(size_t)r * ldc + j] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int r = 0; r < 32; ++r) {
+            const float4 y = *reinterpret_cast<const float4*>(&Ys[r][4 * ti]);
+            const float4 c = *reinterpret_cast<const float4*>(&Cs[r][4 * tj]);
+            const float yv[4] = {y.x, y.y, y.z, y.w}, cv[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(yv[a], cv[b], acc[a][b]);
+        }
+    }
+    float* out = Zp + (size_t)blockIdx.y * 32 * ncp;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t j = j0 + 4 * tj + b;
+            if (j < nc) out[(size_t)(4 * ti + a) * ncp + j] = acc[a][b];
+        }
+}
+
+// Z[i][j] = sum_k op(T)[i][k] (sum_chunks Zp[chunk][k][j]); op = transpose (the factorisation) or not (Q).
+// Grid ceil(nc / 64).
+__global__ void __launch_bounds__(256) reduce_t_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
+                                                       uint32_t ncp, const float* __restrict__ T, int transposed,
+                                                       float* Z) {
+    __shared__ float Ts[32][33];
+    __shared__ float Zs[32][65];
+    const uint32_t j0 = blockIdx.x * 64;
+    for (int idx = threadIdx.x; idx < 1024; idx += 256) Ts[idx >> 5][idx & 31] = T[idx];
+    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+        const uint32_t k = idx >> 6, j = j0 + (idx & 63);
+        float s = 0.0f;
+        if (j < nc)
+            for (uint32_t ch = 0; ch < chunks; ++ch) s += Zp[((size_t)ch * 32 + k) * ncp + j];
+        Zs[k][idx & 63] = s;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+        const uint32_t i = idx >> 6, jj = idx & 63;
+        float s = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) s = fmaf(transposed ? Ts[k][i] : Ts[i][k], Zs[k][jj], s);
+        if (j0 + jj < nc) Z[(size_t)i * ncp + j0 + jj] = s;
+    }
+}
+
+// C[r][j] -= sum_k Y[r][k] Z[k][j], k < 32. Grid (ceil(nc / 128), ceil(mp / 128)); a thread owns 8 x 8.
+__global__ void __launch_bounds__(256) yz_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ Z,
+                                                 uint32_t ncp, float* C, size_t ldc, uint32_t mp, uint32_t jb,
+                                                 uint32_t nc) {
+    __shared__ __align__(16) float Ys[32][132];   // [k][row]
+    __shared__ __align__(16) float Zs[32][128];   // [k][col]
+    const uint32_t j0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+        const uint32_t r = idx >> 5, k = idx & 31;
+        Ys[k][r] = (r0 + r < mp && k < jb) ? Y[(size_t)(r0 + r) * ldy + k] : 0.0f;
+    }
+    for (int idx = threadIdx.x; idx < 32 * 128; idx += 256) {
+        const uint32_t k = idx >> 7, j = idx & 127;
+        Zs[k][j] = (j0 + j < nc) ? Z[(size_t)k * ncp + j0 + j] : 0.0f;
+    }
+    __syncthreads();
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+#pragma unroll 4
+    for (int k = 0; k < 32; ++k) {
+        const float4 y0 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr]);
+        const float4 y1 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr + 4]);
+        const float4 z0 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc]);
+        const float4 z1 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc + 4]);
+        const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+        const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(yv[a], zv[b], acc[a][b]);
+    }
+    const bool vec = (ldc & 3) == 0 && (reinterpret_cast<size_t>(C) & 15) == 0 && j0 + 8 * tc + 8 <= nc;
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+        const uint32_t r = r0 + 8 * tr + a;
+        if (r >= mp) continue;
+        float* row = C + (size_t)r * ldc + j0 + 8 * tc;
+        if (vec) {
+            float4 c0 = *reinterpret_cast<float4*>(row), c1 = *reinterpret_cast<float4*>(row + 4);
+            c0.x -= acc[a][0]; c0.y -= acc[a][1]; c0.z -= acc[a][2]; c0.w -= acc[a][3];
+            c1.x -= acc[a][4]; c1.y -= acc[a][5]; c1.z -= acc[a][6]; c1.w -= acc[a][7];
+            *reinterpret_cast<float4*>(row) = c0;
+            *reinterpret_cast<float4*>(row + 4) = c1;
+        } else {
+#pragma unroll
+            for (int b = 0; b < 8; ++b)
+                if (j0 + 8 * tc + b < nc) row[b] -= acc[a][b];
+        }
+    }
+}
+
+unsigned grid_for(size_t count) { return (unsigned)std::min<size_t>((count + 255) / 256, 148 * 8); }
+
+// C (mp rows from C's first row, nc columns) <- (I - Y op(T) Y^T) C
+void apply_block_reflector(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
+                           size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* zp, float* z) {
+    if (nc == 0 || mp == 0) return;
+    const uint32_t chunks = (mp + RCH - 1) / RCH, ncp = (nc + 3) & ~3u;
+    ytc_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, jb, nc, zp, ncp);
+    reduce_t_kernel<<<(nc + 63) / 64, 256, 0, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    yz_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, jb, nc);
+    cuda_check(cudaGetLastError(), "block reflector launch");
+}
+
+} // namespace
+
+bool qr_blocked_fits(uint32_t m, uint32_t n) {
+    return m > 0 && n > 0 && (uint64_t)m * n < ((uint64_t)1 << 31) && (uint64_t)m * std::min(m, n) < ((uint64_t)1 << 31);
+}
+
+void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr) {
+    if (pr.batch == 0) return;
+    const uint32_t m = pr.m, n = pr.n, K = qr_k(pr), qc = pr.qc, rr = pr.rr;
+    const uint32_t ldw = (n + 3) & ~3u, ldy = (K + 3) & ~3u;
+    const uint32_t npanels = (K + NB - 1) / NB;
+    const uint32_t wide = std::max(n, qc);                       // the widest matrix a reflector is applied to
+    const uint32_t chunks = (m + RCH - 1) / RCH, ncp = (wide + 3) & ~3u;
+
+    // workspace (floats), shared by the matrices of the batch, which are factored one after another
+    auto up64 = [](size_t f) { return (f + 63) & ~(size_t)63; };
+    size_t off = 0;
+    auto take = [&](size_t floats) { const size_t o = off; off += up64(floats); return o; };
+    const size_t o_w = take((size_t)m * ldw), o_y = take((size_t)m * ldy), o_t = take((size_t)npanels * 1024);
+    const size_t o_qp = take((size_t)m * NB), o_rp = take(NB * NB), o_ui = take(NB * NB);
+    const size_t o_zp = take((size_t)chunks * 32 * ncp), o_z = take((size_t)32 * ncp);
+    const size_t o_info = take(64);
+    size_t tsqr_floats = 0;
+    for (uint32_t k0 = 0; k0 < K; k0 += NB)
+        tsqr_floats = std::max(tsqr_floats, tsqr_workspace_floats(ctx, m - k0, std::min<uint32_t>(NB, K - k0), 1, true));
+    const size_t o_ts = take(tsqr_floats);
+    float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
+    float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
+    float *Zp = ws + o_zp, *Z = ws + o_z, *ts = ws + o_ts;
+    MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
+
+    for (uint32_t b = 0; b < pr.batch; ++b) {
+        const float* A = pr.a + (size_t)b * m * n;
+        float* Q = qc ? pr.q + (size_t)b * m * qc : nullptr;
+        float* R = pr.r + (size_t)b * rr * n;
+
+        cuda_check(cudaMemsetAsync(info, 0, sizeof(MatInfo), stream), "cudaMemsetAsync");
+        scan_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, (size_t)m * n, info);
+        scale_copy_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, W, m, n, ldw, info);
+
+        // forward: panels and trailing updates
+        for (uint32_t pi = 0; pi < npanels; ++pi) {
+            const uint32_t k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
+            tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
+            ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
+            reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
+            if (mp > jb)   // the rows below the top block: Qp U^-1
+                launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0, ldy, Ui,
+                                  true, 1, 1, mp - jb, mp - jb, jb);
+            if (k0 + jb < n)
+                apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, true,
+                                      W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, n - k0 - jb, Zp, Z);
+        }
+        r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
+        if (!qc) continue;
+
+        // backward: Q = H_0 ... H_{K-1} [I; 0]
+        launch_fill_identity(stream, Q, 1, m, qc);
+        for (uint32_t pi = npanels; pi-- > 0;) {
+            const uint32_t k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
+            apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, false,
+                                  Q + (size_t)k0 * qc + k0, qc, mp, jb, qc - k0, Zp, Z);
+        }
+        nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);
+    }
+    cuda_check(cudaGetLastError(), "qr_blocked launch");
+}
+
+} // namespace mlb

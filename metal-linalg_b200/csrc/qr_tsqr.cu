@@ -38,13 +38,15 @@ constexpr int TR = 64;          // rows of Q per thread block of the apply kerne
 constexpr int LDX = TR + 4;     // leading dimension of the transposed tile
 
 struct ApplyParams {
-    float*       q;             // blocks of rows: block i of matrix b at b * q_outer + i * q_stride
-    const float* up;            // n x n factors: that block's at (b * blocks + i) * n * n
+    const float* q;             // blocks of rows (ld n): block i of matrix b at b * q_outer + i * q_stride
+    float*       out;           // where the products go: block i of matrix b at b * out_outer + i * out_stride, ld out_ld
+    const float* up;            // n x n factors: that block's at (b * blocks + i) * n * n, or one per matrix
+    unsigned     shared_up;     // 1: every block of matrix b uses the factor at b * n * n
     unsigned     blocks;        // row blocks per matrix
     unsigned     rows, last_rows;   // rows of a block, and of a matrix's last block
     unsigned     tiles;         // ceil(max(rows, last_rows) / TR)
     int          n, np;         // columns, and columns rounded up to 64
-    unsigned long long q_outer, q_stride;
+    unsigned long long q_outer, q_stride, out_outer, out_stride, out_ld;
     unsigned long long total;   // matrices * blocks * tiles
 };
 
@@ -65,8 +67,11 @@ __global__ void __launch_bounds__(256) tsqr_apply_kernel(const ApplyParams p) {
         const unsigned r0 = tile * TR;
         if (r0 >= rows) continue;
         const unsigned nr = min((unsigned)TR, rows - r0);
-        float* Q = p.q + b * p.q_outer + (unsigned long long)i * p.q_stride + (size_t)r0 * n;
-        const float* B = p.up + blk * (unsigned long long)n * n;
+        const float* Q = p.q + b * p.q_outer + (unsigned long long)i * p.q_stride + (size_t)r0 * n;
+        float* O = p.out + b * p.out_outer + (unsigned long long)i * p.out_stride + (size_t)r0 * p.out_ld;
+        const size_t ldo = (size_t)p.out_ld;
+        const bool vec = (ldo & 3) == 0 && (reinterpret_cast<size_t>(O) & 15) == 0;
+        const float* B = p.up + (p.shared_up ? b : blk) * (unsigned long long)n * n;
         __syncthreads();
         for (int idx = threadIdx.x; idx < n * np; idx += 256) {
             const int k = idx / np, c = idx % np;
@@ -98,13 +103,13 @@ __global__ void __launch_bounds__(256) tsqr_apply_kernel(const ApplyParams p) {
                 const unsigned r = 4 * rg + a;
                 if (r < nr) {
                     const int c = c0 + 4 * cg;
-                    if ((n & 3) == 0 && c < n) {   // rows of Q are 16-byte aligned: one word a thread
-                        *reinterpret_cast<float4*>(Q + (size_t)r * n + c) =
+                    if (vec && c + 3 < n) {   // the rows are 16-byte aligned: one word a thread
+                        *reinterpret_cast<float4*>(O + (size_t)r * ldo + c) =
                             make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
                     } else {
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
-                            if (c + e < n) Q[(size_t)r * n + c + e] = acc[a][e];
+                            if (c + e < n) O[(size_t)r * ldo + c + e] = acc[a][e];
                     }
                 }
             }
@@ -137,58 +142,98 @@ std::vector<Level> plan(uint32_t m, uint32_t n) {
 
 } // namespace
 
-bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc) {
-    // reduced or R alone (Q of n columns or none), at most 128 columns, at least two levels' worth of rows
-    return n >= 1 && n <= 128 && m > 1024 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
+void launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q, uint64_t q_outer, uint64_t q_stride,
+                       float* out, uint64_t out_outer, uint64_t out_stride, uint64_t out_ld, const float* up,
+                       bool shared_up, uint32_t batch, uint32_t blocks, uint32_t rows, uint32_t last_rows, uint32_t n) {
+    if (batch == 0 || blocks == 0 || n == 0 || std::max(rows, last_rows) == 0) return;
+    const int np = (int)((n + 63) / 64 * 64);
+    const size_t smem = ((size_t)n * LDX + (size_t)n * np) * sizeof(float);
+    cuda_check(cudaFuncSetAttribute(tsqr_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+               "tsqr_apply shared memory");
+    ApplyParams a{};
+    a.q = q; a.out = out; a.up = up;
+    a.shared_up = shared_up ? 1 : 0;
+    a.blocks = blocks; a.rows = rows; a.last_rows = last_rows;
+    a.tiles = (std::max(rows, last_rows) + TR - 1) / TR;
+    a.n = (int)n; a.np = np;
+    a.q_outer = q_outer; a.q_stride = q_stride;
+    a.out_outer = out_outer; a.out_stride = out_stride; a.out_ld = out_ld;
+    a.total = (uint64_t)batch * blocks * a.tiles;
+    const unsigned grid = (unsigned)std::min<uint64_t>(a.total, (uint64_t)ctx.sm_count * 8);
+    tsqr_apply_kernel<<<grid, 256, smem, stream>>>(a);
+    cuda_check(cudaGetLastError(), "tsqr_apply launch");
 }
 
-void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr) {
-    if (pr.batch == 0) return;
-    const uint32_t m = pr.m, n = pr.n, batch = pr.batch;
-    const bool want_q = pr.qc != 0;
-    const std::vector<Level> levels = plan(m, n);
-    const size_t nl = levels.size();
-    const uint32_t top_rows = levels.back().blocks * n;
+namespace {
 
-    // workspace: per level l >= 1 the stack S_l (its input) and, with Q wanted, Q_l of the same
-    // shape; the top's Q; the scratch slots of the largest qr_mid launch
+struct Layout {
+    std::vector<Level>  levels;
+    std::vector<size_t> s_off, q_off;   // per level l >= 1: its stack of R's and (with Q) its Q, in floats
+    size_t              mid_off = 0, total = 0;
+    uint32_t            top_rows = 0;
+};
+
+Layout layout(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, bool want_q) {
+    Layout L;
+    L.levels = plan(m, n);
+    const size_t nl = L.levels.size();
+    L.top_rows = nl ? L.levels.back().blocks * n : m;
     auto up64 = [](size_t f) { return (f + 63) & ~(size_t)63; };
-    std::vector<size_t> s_off(nl + 1, 0), q_off(nl + 1, 0);
-    size_t total = 0;
+    L.s_off.assign(nl + 1, 0);
+    L.q_off.assign(nl + 1, 0);
     for (size_t l = 1; l <= nl; ++l) {
-        const size_t floats = (size_t)batch * levels[l - 1].blocks * n * n;   // S_l: blocks of level l-1, n x n each
-        s_off[l] = total; total += up64(floats);
-        if (want_q) { q_off[l] = total; total += up64(floats); }
+        const size_t floats = (size_t)batch * L.levels[l - 1].blocks * n * n;   // one n x n block per block below
+        L.s_off[l] = L.total; L.total += up64(floats);
+        if (want_q) { L.q_off[l] = L.total; L.total += up64(floats); }
     }
-    size_t mid_floats = qr_mid_workspace_floats(ctx, top_rows, n, batch);
-    for (const Level& L : levels) {
-        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, L.c, n, batch * (L.blocks - 1)));
-        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, L.last_rows, n, batch));
+    size_t mid_floats = qr_mid_workspace_floats(ctx, L.top_rows, n, batch);
+    for (const Level& lv : L.levels) {
+        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, lv.c, n, batch * (lv.blocks - 1)));
+        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, lv.last_rows, n, batch));
     }
-    const size_t mid_off = total;
-    total += up64(mid_floats);
-    float* ws = static_cast<float*>(ctx.workspace(stream, total * sizeof(float)));
+    L.mid_off = L.total;
+    L.total += up64(mid_floats);
+    return L;
+}
+
+} // namespace
+
+size_t tsqr_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, bool want_q) {
+    return layout(ctx, m, n, batch, want_q).total;
+}
+
+// Thin QR of `batch` matrices of m x n (n <= 128, any m >= n) read with row stride lda and matrix
+// stride a_outer: q [batch][m][n] contiguous (null: R alone), r [batch] n x n at stride r_outer.
+void tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m,
+               uint32_t n, uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws) {
+    if (batch == 0) return;
+    const bool want_q = q != nullptr;
+    const Layout L = layout(ctx, m, n, batch, want_q);
+    const size_t nl = L.levels.size();
+    const uint32_t qc = want_q ? n : 0;
 
     // up the tree
     for (size_t l = 0; l < nl; ++l) {
-        const Level& L = levels[l];
-        const float* in = l == 0 ? pr.a : ws + s_off[l];
-        float* qout = !want_q ? nullptr : (l == 0 ? pr.q : ws + q_off[l]);
-        float* rout = ws + s_off[l + 1];
-        const uint64_t in_outer = (uint64_t)L.rows * n, r_outer = (uint64_t)L.blocks * n * n;
+        const Level& lv = L.levels[l];
+        const float* in = l == 0 ? a : ws + L.s_off[l];
+        const uint32_t in_ld = l == 0 ? lda : n;
+        const uint64_t in_outer = l == 0 ? a_outer : (uint64_t)lv.rows * n;
+        float* qout = !want_q ? nullptr : (l == 0 ? q : ws + L.q_off[l]);
+        float* rout = ws + L.s_off[l + 1];
         MidOptions o;
-        o.ws = ws + mid_off;
-        o.a_stride = (uint64_t)L.c * n; o.q_stride = (uint64_t)L.c * n; o.r_stride = (uint64_t)n * n;
-        o.a_outer = in_outer; o.q_outer = in_outer; o.r_outer = r_outer;
-        if (L.blocks > 1) {   // the full blocks of every matrix in one launch
-            QrProblem p{in, qout, rout, batch * (L.blocks - 1), L.c, n, want_q ? n : 0, n};
-            o.inner_count = L.blocks - 1;
+        o.ws = ws + L.mid_off;
+        o.lda = in_ld;
+        o.a_stride = (uint64_t)lv.c * in_ld; o.q_stride = (uint64_t)lv.c * n; o.r_stride = (uint64_t)n * n;
+        o.a_outer = in_outer; o.q_outer = (uint64_t)lv.rows * n; o.r_outer = (uint64_t)lv.blocks * n * n;
+        if (lv.blocks > 1) {   // the full blocks of every matrix in one launch
+            QrProblem p{in, qout, rout, batch * (lv.blocks - 1), lv.c, n, qc, n};
+            o.inner_count = lv.blocks - 1;
             launch_qr_mid(ctx, stream, p, o);
         }
         {   // each matrix's last block (c rows plus the remainder)
-            const uint64_t skip = (uint64_t)(L.blocks - 1);
-            QrProblem p{in + skip * L.c * n, qout ? qout + skip * L.c * n : nullptr, rout + skip * n * n, batch,
-                        L.last_rows, n, want_q ? n : 0, n};
+            const uint64_t skip = (uint64_t)(lv.blocks - 1);
+            QrProblem p{in + skip * lv.c * in_ld, qout ? qout + skip * lv.c * n : nullptr, rout + skip * n * n, batch,
+                        lv.last_rows, n, qc, n};
             o.inner_count = 1;
             launch_qr_mid(ctx, stream, p, o);
         }
@@ -196,34 +241,45 @@ void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr
     // the top: one block per matrix; its R is the matrix's R
     {
         MidOptions o;
-        o.ws = ws + mid_off;
-        QrProblem p{ws + s_off[nl], want_q ? ws + q_off[nl] : nullptr, pr.r, batch, top_rows, n, want_q ? n : 0, n};
+        o.ws = ws + L.mid_off;
+        o.inner_count = 1;
+        o.r_outer = r_outer;
+        o.r_stride = (uint64_t)n * n;
+        if (nl == 0) {
+            o.lda = lda; o.a_outer = a_outer; o.a_stride = (uint64_t)m * lda;
+            o.q_outer = (uint64_t)m * n; o.q_stride = o.q_outer;
+            QrProblem p{a, q, r, batch, m, n, qc, n};
+            launch_qr_mid(ctx, stream, p, o);
+            return;
+        }
+        o.a_outer = (uint64_t)L.top_rows * n; o.a_stride = o.a_outer;
+        o.q_outer = o.a_outer; o.q_stride = o.a_outer;
+        QrProblem p{ws + L.s_off[nl], want_q ? ws + L.q_off[nl] : nullptr, r, batch, L.top_rows, n, qc, n};
         launch_qr_mid(ctx, stream, p, o);
     }
     if (!want_q) return;
 
-    // down the tree: level l's Q blocks times the n x n blocks of level l+1's Q
-    const int np = (int)((n + 63) / 64 * 64);
-    const size_t smem = ((size_t)n * LDX + (size_t)n * np) * sizeof(float);
-    cuda_check(cudaFuncSetAttribute(tsqr_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-               "tsqr_apply shared memory");
+    // down the tree: level l's Q blocks times the n x n blocks of level l+1's Q, in place
     for (size_t l = nl; l-- > 0;) {
-        const Level& L = levels[l];
-        ApplyParams a{};
-        a.q = l == 0 ? pr.q : ws + q_off[l];
-        a.up = ws + q_off[l + 1];
-        a.blocks = L.blocks;
-        a.rows = L.c;
-        a.last_rows = L.last_rows;
-        a.tiles = (std::max(L.c, L.last_rows) + TR - 1) / TR;
-        a.n = (int)n; a.np = np;
-        a.q_outer = (uint64_t)L.rows * n;
-        a.q_stride = (uint64_t)L.c * n;
-        a.total = (uint64_t)batch * L.blocks * a.tiles;
-        const unsigned grid = (unsigned)std::min<uint64_t>(a.total, (uint64_t)ctx.sm_count * 8);
-        tsqr_apply_kernel<<<grid, 256, smem, stream>>>(a);
-        cuda_check(cudaGetLastError(), "tsqr_apply launch");
+        const Level& lv = L.levels[l];
+        float* ql = l == 0 ? q : ws + L.q_off[l];
+        launch_tsqr_apply(ctx, stream, ql, (uint64_t)lv.rows * n, (uint64_t)lv.c * n, ql, (uint64_t)lv.rows * n,
+                          (uint64_t)lv.c * n, n, ws + L.q_off[l + 1], false, batch, lv.blocks, lv.c, lv.last_rows, n);
     }
+}
+
+bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc) {
+    // reduced or R alone (Q of n columns or none), at most 128 columns, at least two levels' worth of rows
+    return n >= 1 && n <= 128 && m > 1024 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
+}
+
+void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr) {
+    if (pr.batch == 0) return;
+    const bool want_q = pr.qc != 0;
+    const size_t floats = tsqr_workspace_floats(ctx, pr.m, pr.n, pr.batch, want_q);
+    float* ws = static_cast<float*>(ctx.workspace(stream, floats * sizeof(float)));
+    tsqr_core(ctx, stream, pr.a, pr.n, (uint64_t)pr.m * pr.n, pr.m, pr.n, pr.batch, want_q ? pr.q : nullptr, pr.r,
+              (uint64_t)pr.n * pr.n, ws);
 }
 
 } // namespace mlb

@@ -138,6 +138,68 @@ def test_config4_tall_shrunk_batch():
     check(a, q, r, "reduced", r_ref)
 
 
+BLOCKED = [(40, 40), (100, 64), (64, 100), (200, 200), (300, 2000), (1025, 1025), (1500, 1200), (2000, 300),
+           (1100, 130), (3000, 200)]
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("shape", BLOCKED)
+def test_blocked_kernel_shapes(shape, mode):
+    """The grid-parallel blocked QR, forced on shapes small enough for the CPU oracle."""
+    m, n = shape
+    if mode == "complete" and m > 2000:
+        pytest.skip("a 3000 x 3000 Q on the CPU oracle takes too long")
+    rng = np.random.default_rng(m * 7 + n)
+    a = rng.standard_normal((2, m, n)).astype(np.float32)
+    q, r = gpu_qr(a, mode, kernel="blocked")
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+def test_blocked_special_matrices():
+    m, n = 700, 500
+    eye = np.eye(m, n, dtype=np.float32)
+    rng = np.random.default_rng(15)
+    low = (rng.standard_normal((m, 40)) @ rng.standard_normal((40, n))).astype(np.float32)      # rank 40
+    bad = rng.standard_normal((m, n)).astype(np.float32)
+    bad[5, 7] = np.inf
+    a = np.stack([eye, np.zeros((m, n), np.float32), np.full((m, n), 3.25, np.float32), low, bad,
+                  (rng.standard_normal((m, n)) * 1e-30).astype(np.float32),
+                  (rng.standard_normal((m, n)) * 1e30).astype(np.float32)])
+    q, r = gpu_qr(a, "reduced", kernel="blocked")
+    assert np.isnan(q[4]).all() and np.isnan(r[4]).all()
+    good = [0, 1, 2, 3, 5, 6]
+    check(a[good], q[good], r[good], "reduced")
+    assert np.abs(r[1]).max() == 0.0
+
+
+def _gpu_float64_check(a, q, r, mode):
+    """Reconstruction and orthogonality in float64 on the GPU, and R against torch's float64 QR
+    after sign normalisation: for matrices too large for the CPU oracle."""
+    n = a.shape[-1]
+    tol = workloads.tolerance(n)
+    a64, q64, r64 = a.double(), q.double(), r.double()
+    recon = (torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)).max().item()
+    eye = torch.eye(q.shape[-1], device=a.device, dtype=torch.float64)
+    orth = torch.linalg.matrix_norm(q64.mT @ q64 - eye).max().item()
+    assert recon <= tol, f"reconstruction {recon:.3e} > {tol:.3e}"
+    assert orth <= tol, f"orthogonality {orth:.3e} > {tol:.3e}"
+    assert torch.count_nonzero(torch.tril(r, -1)).item() == 0
+    r_ref = torch.linalg.qr(a64, mode="r")[1]
+    k = min(a.shape[-2:])
+    s = torch.sign(torch.diagonal(r64, dim1=-2, dim2=-1)) * torch.sign(torch.diagonal(r_ref, dim1=-2, dim2=-1))
+    diff = (r64[..., :k, :] * s[..., :, None] - r_ref).abs().max().item() / r_ref.abs().max().item()
+    assert diff <= 1e-4, f"R differs from the float64 QR by {diff:.3e}"
+
+
+def test_config5a_4096_square():
+    a = workloads.generate("c5a_4096x4096").cuda()
+    assert mlt.qr_kernel(4096, 4096, 1) == "blocked"
+    q, r = mlt.qr(a)
+    torch.cuda.synchronize()
+    _gpu_float64_check(a, q, r, "reduced")
+
+
 def test_mid_kernel_on_small_shapes_agrees_with_small_kernel():
     rng = np.random.default_rng(5)
     a = rng.standard_normal((50, 24, 18)).astype(np.float32)
