@@ -67,6 +67,14 @@ void   launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q
                          float* out, uint64_t out_outer, uint64_t out_stride, uint64_t out_ld, const float* up,
                          bool shared_up, uint32_t batch, uint32_t blocks, uint32_t rows, uint32_t last_rows, uint32_t n);
 
+// A panel of the blocked QR (mp x jb, jb <= 32, mp <= 16384) to compact-WY form in three launches
+// (qr_panel.cu): its R into the working copy's upper triangle, Y (unit lower trapezoidal) into y,
+// T into t[32][32].
+bool   panel_fast_fits(uint32_t mp, uint32_t jb);
+size_t panel_fast_workspace_floats(uint32_t mp);
+void   panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t mp, uint32_t jb, float* y, size_t ldy,
+                         float* t, float* ws);
+
 // Blocked compact-WY QR over the whole grid, any shape.
 bool qr_blocked_fits(uint32_t m, uint32_t n);
 void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);

@@ -31,6 +31,7 @@
 #include "kernels.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 namespace mlb {
@@ -360,9 +361,11 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
         tsqr_floats = std::max(tsqr_floats, tsqr_workspace_floats(ctx, m - k0, std::min<uint32_t>(NB, K - k0), 1, true));
     const size_t o_ts = take(tsqr_floats);
+    const size_t o_pf = take(panel_fast_workspace_floats(std::min<uint32_t>(m, 16384)));
+    static const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree, for comparison
     float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
     float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
-    float *Zp = ws + o_zp, *Z = ws + o_z, *ts = ws + o_ts;
+    float *Zp = ws + o_zp, *Z = ws + o_z, *ts = ws + o_ts, *pf = ws + o_pf;
     MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
 
     for (uint32_t b = 0; b < pr.batch; ++b) {
@@ -377,12 +380,17 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // forward: panels and trailing updates
         for (uint32_t pi = 0; pi < npanels; ++pi) {
             const uint32_t k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
-            tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
-            ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
-            reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
-            if (mp > jb)   // the rows below the top block: Qp U^-1
-                launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0, ldy, Ui,
-                                  true, 1, 1, mp - jb, mp - jb, jb);
+            if (!slow_panels && panel_fast_fits(mp, jb)) {
+                panel_factor_fast(stream, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
+                                  T + (size_t)pi * 1024, pf);
+            } else {   // taller than the register-resident panel kernels take: the general tree
+                tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
+                ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
+                reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
+                if (mp > jb)   // the rows below the top block: Qp U^-1
+                    launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0, ldy,
+                                      Ui, true, 1, 1, mp - jb, mp - jb, jb);
+            }
             if (k0 + jb < n)
                 apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, true,
                                       W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, n - k0 - jb, Zp, Z);

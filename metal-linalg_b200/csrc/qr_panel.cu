@@ -1,0 +1,458 @@
+// Panel factorisation for the blocked QR: a panel of up to 16384 rows x 32
+// columns to compact-WY form (Y unit lower trapezoidal, T, R) in three launches.
+//
+// It takes the place of the reference's tall-panel kernels bd_tsqr_leaf,
+// bd_tsqr_top and bd_tsqr_rebuild (shaders/Svd_Bidiag.metal:583-869, driven by
+// src/band_reduce.mm:196-251): TSQR over row blocks, then Householder
+// reconstruction (Ballard et al. 2014) so that the trailing update sees one
+// ordinary block reflector.
+//
+//   panel_leaf_kernel   one thread block per block of 256 * RPT rows, a thread
+//                       per row (RPT rows) held in registers. 32 column steps;
+//                       a step is ONE reduction over the block of 32 numbers per
+//                       thread, x[row][j] * x[row][c] for all 32 columns c: for
+//                       c > j these are the reflector's dot products with the
+//                       trailing columns, for c = j its norm, and for c < j its
+//                       products with the earlier reflectors, which is the Gram
+//                       matrix that T is built from. The current column is kept
+//                       at register index 0 by rotating the row one place per
+//                       step, so the step loop is not unrolled and every
+//                       register index is a constant. Out: the block's V, T, R.
+//   panel_top_kernel    one thread block: the same factorisation of the stacked
+//                       R's (at most 512 rows), the tree's Q on the first 32
+//                       rows, LU with sign choice of Q1 - S (every pivot at least
+//                       1 in magnitude), T = -U S L1^-T, the panel's R = S R, and
+//                       for every leaf the 32 x 32 factor B' = (its block of the
+//                       top Q) U^-1.
+//   panel_apply_kernel  per leaf: Y rows = [B'; 0] - V (T (V_top^T B')).
+#include "common.cuh"
+#include "kernels.h"
+
+#include <algorithm>
+
+namespace mlb {
+
+namespace {
+
+constexpr int PT = 256;     // threads per block
+constexpr unsigned kFull = 0xffffffffu;
+
+struct PanelSmem {
+    float red[PT / 32][32];   // each warp's column sums
+    float prow[32];           // the pivot row, in rotated column order
+    float wv[2][32];          // per rotated column the update coefficient (0 where there is nothing to update)
+    float scal[2][4];         // tau, 1/(alpha - beta), beta
+    float taus[32];
+    float G[32][33];          // G[k][j] = v_k^T v_j for k < j
+    float T[32][33];
+};
+
+// Sum over the warp of 32 values a lane: lane c returns the sum of p[c].
+__device__ __forceinline__ float butterfly32(float (&p)[32], int lane) {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float send = upper ? p[i] : p[i + half];
+            const float keep = upper ? p[i + half] : p[i];
+            p[i] = keep + __shfl_xor_sync(kFull, send, half);
+        }
+    }
+    return p[0];
+}
+
+// Householder QR of the rows held by the block: thread t holds rows t + 256 k, k < RPT, 32 columns
+// each. Afterwards x holds R (rows < 32, on and above the diagonal) and the reflectors' tails,
+// scaled to unit diagonal (below it); s.taus, s.G are set. Rows >= the block's real row count
+// must be zero on entry.
+template <int RPT>
+__device__ __forceinline__ void factor_rows(float (&x)[RPT][32], PanelSmem& s) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
+        // the original column (j + k) % 32 is at register index k
+        float p[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) p[c] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < RPT; ++k) {
+            const float v = (t + PT * k > j) ? x[k][0] : 0.0f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) p[c] = fmaf(v, x[k][c], p[c]);
+        }
+        if (t == j) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) s.prow[c] = x[0][c];
+        }
+        s.red[warp][lane] = butterfly32(p, lane);
+        __syncthreads();
+        const int buf = j & 1;
+        if (warp == 0) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < PT / 32; ++w) v += s.red[w][lane];
+            const float ss = __shfl_sync(kFull, v, 0);
+            float beta, tau, sc;
+            reflector(s.prow[0], ss, beta, tau, sc);
+            const float val = fmaf(sc, v, s.prow[lane]);
+            s.wv[buf][lane] = (lane >= 1 && lane <= 31 - j) ? tau * val : 0.0f;
+            if (lane >= 32 - j) s.G[(j + lane) & 31][j] = val;
+            if (lane == 0) {
+                s.scal[buf][0] = tau;
+                s.scal[buf][1] = sc;
+                s.scal[buf][2] = beta;
+                s.taus[j] = tau;
+            }
+        }
+        __syncthreads();
+        const float sc = s.scal[buf][1], beta = s.scal[buf][2];
+        float w[32];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(&s.wv[buf][4 * q]);
+            w[4 * q] = f.x; w[4 * q + 1] = f.y; w[4 * q + 2] = f.z; w[4 * q + 3] = f.w;
+        }
+#pragma unroll
+        for (int k = 0; k < RPT; ++k) {
+            const int row = t + PT * k;
+            const float vr = row > j ? sc * x[k][0] : (row == j ? 1.0f : 0.0f);
+            const float head = row > j ? vr : (row == j ? beta : x[k][0]);
+#pragma unroll
+            for (int c = 1; c < 32; ++c) x[k][c - 1] = fmaf(-w[c], vr, x[k][c]);   // update and rotate left
+            x[k][31] = head;
+        }
+    }
+}
+
+// T from s.G and s.taus (slarft's forward recurrence), by warp 0, a row of T per lane.
+__device__ __forceinline__ void build_t(PanelSmem& s) {
+    if (threadIdx.x < 32) {
+        const int i = threadIdx.x;
+        float tr[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float tau = s.taus[j];
+            float a = 0.0f;
+#pragma unroll
+            for (int k = 0; k < j; ++k) a = fmaf(tr[k], s.G[k][j], a);
+            tr[j] = i < j ? -tau * a : (i == j ? tau : 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s.T[i][j] = tr[j];
+    }
+}
+
+// The clean reflector entry of row `row`: unit diagonal, zeros above.
+__device__ __forceinline__ float clean_v(float x, int row, int c) { return c < row ? x : (c == row ? 1.0f : 0.0f); }
+
+// C (32 x 32, ld 33) = op(A) B for 32 x 32 matrices in shared memory, by the whole block.
+template <bool TransA>
+__device__ __forceinline__ void mat32(const float (*A)[33], const float (*B)[33], float (*C)[33]) {
+    const int i = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+        const float a = TransA ? A[k][i] : A[i][k];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(a, B[k][c0 + e], acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) C[i][c0 + e] = acc[e];
+}
+
+struct LeafParams {
+    const float* panel;     // the panel's first entry in the working copy
+    size_t       ldw;
+    uint32_t     mp, jb, lr;   // rows and columns of the panel, rows per leaf
+    float*       Vl;        // [leaves][lr][32] clean reflectors
+    float*       Tl;        // [leaves][32][32]
+    float*       Sl;        // [leaves * 32][32] the stack of R's
+};
+
+template <int RPT>
+__global__ void __launch_bounds__(PT) panel_leaf_kernel(const LeafParams p) {
+    __shared__ __align__(16) PanelSmem s;
+    const int t = threadIdx.x;
+    const uint32_t blk = blockIdx.x, row0 = blk * p.lr;
+    float x[RPT][32];
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+        const uint32_t gr = row0 + t + PT * k;
+        const float* src = p.panel + (size_t)gr * p.ldw;
+        if (gr < p.mp && p.jb == 32) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 f = *reinterpret_cast<const float4*>(src + 4 * q);
+                x[k][4 * q] = f.x; x[k][4 * q + 1] = f.y; x[k][4 * q + 2] = f.z; x[k][4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) x[k][c] = (gr < p.mp && (uint32_t)c < p.jb) ? src[c] : 0.0f;
+        }
+    }
+    factor_rows<RPT>(x, s);
+    __syncthreads();
+    build_t(s);
+    if (t < 32) {
+        float* dst = p.Sl + ((size_t)blk * 32 + t) * 32;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) dst[c] = c >= t ? x[0][c] : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+        const int row = t + PT * k;
+        float* dst = p.Vl + ((size_t)blk * p.lr + row) * 32;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(dst + 4 * q) =
+                make_float4(clean_v(x[k][4 * q], row, 4 * q), clean_v(x[k][4 * q + 1], row, 4 * q + 1),
+                            clean_v(x[k][4 * q + 2], row, 4 * q + 2), clean_v(x[k][4 * q + 3], row, 4 * q + 3));
+    }
+    __syncthreads();
+    for (int idx = t; idx < 1024; idx += PT) p.Tl[(size_t)blk * 1024 + idx] = s.T[idx >> 5][idx & 31];
+}
+
+struct TopParams {
+    const float* Sl;        // [S][32] stacked R's
+    uint32_t     S;         // rows of the stack (leaves * 32, at most 512)
+    const float* Vl;        // leaf 0's clean reflectors (its first 32 rows are used)
+    const float* Tl;        // leaf 0's T
+    float*       Bp;        // [S][32] out: per leaf B' = (its block of the top Q) U^-1
+    float*       w;         // the panel's first entry in the working copy: gets S R (upper triangle)
+    size_t       ldw;
+    float*       y;         // the panel's first entry in Y: gets the unit lower triangular L1
+    size_t       ldy;
+    float*       t;         // [32][32] out: T of the panel
+    uint32_t     jb, mp;
+};
+
+__global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
+    __shared__ __align__(16) PanelSmem s;
+    __shared__ float V1[32][33], M[32][33], B0[32][33], X[32][33], Q[32][33], V0[32][33], T0[32][33], Rm[32][33];
+    __shared__ float sgn[32];
+    const int t = threadIdx.x;
+    float x[2][32];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t r = t + PT * k;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < p.S) f = *reinterpret_cast<const float4*>(p.Sl + (size_t)r * 32 + 4 * q);
+            x[k][4 * q] = f.x; x[k][4 * q + 1] = f.y; x[k][4 * q + 2] = f.z; x[k][4 * q + 3] = f.w;
+        }
+    }
+    for (int idx = t; idx < 1024; idx += PT) {
+        V0[idx >> 5][idx & 31] = p.Vl[idx];
+        T0[idx >> 5][idx & 31] = p.Tl[idx];
+    }
+    factor_rows<2>(x, s);
+    __syncthreads();
+    build_t(s);
+    if (t < 32) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            Rm[t][c] = c >= t ? x[0][c] : 0.0f;
+            V1[t][c] = clean_v(x[0][c], t, c);
+        }
+    }
+    __syncthreads();
+    // the top Q's rows: B = [I; 0] - V (T V1^T)
+    {   // M = T V1^T: M[k][c] = sum_k' T[k][k'] V1[c][k']
+        const int i = t >> 3, c0 = (t & 7) * 4;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float a = s.T[i][k];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(a, V1[c0 + e][k], acc[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) M[i][c0 + e] = acc[e];
+    }
+    __syncthreads();
+    float b[2][32];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int row = t + PT * k;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) b[k][c] = (row == c) ? 1.0f : 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) {
+            const float v = clean_v(x[k][kk], row, kk);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) b[k][c] = fmaf(-v, M[kk][c], b[k][c]);
+        }
+    }
+    if (t < 32) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) B0[t][c] = b[0][c];
+    }
+    __syncthreads();
+    // the panel's Q on its first 32 rows: Q1 = B0 - V0 (T0 (V0^T B0)), V0 and T0 leaf 0's
+    mat32<true>(V0, B0, X);
+    __syncthreads();
+    mat32<false>(T0, X, M);
+    __syncthreads();
+    mat32<false>(V0, M, X);
+    __syncthreads();
+    for (int idx = t; idx < 1024; idx += PT) Q[idx >> 5][idx & 31] = B0[idx >> 5][idx & 31] - X[idx >> 5][idx & 31];
+    __syncthreads();
+    // LU of Q1 - S with S = -sgn(pivot) chosen on the way (every pivot at least 1 in magnitude)
+    if (t < 32) {
+        const int i = t;
+        for (int j = 0; j < 32; ++j) {
+            const float d = Q[j][j];
+            const float sg = d >= 0.0f ? -1.0f : 1.0f;
+            const float piv = d - sg;
+            __syncwarp();
+            if (i == j) {
+                Q[j][j] = piv;
+                sgn[j] = sg;
+            }
+            float l = 0.0f;
+            if (i > j) {
+                l = Q[i][j] / piv;
+                Q[i][j] = l;
+            }
+            __syncwarp();
+            if (i > j)
+                for (int c = j + 1; c < 32; ++c) Q[i][c] = fmaf(-l, Q[j][c], Q[i][c]);
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    // B' = B U^-1, a row per thread: x U = b by forward substitution over the columns
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t r = t + PT * k;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float a = b[k][c];
+#pragma unroll
+            for (int kk = 0; kk < c; ++kk) a = fmaf(-b[k][kk], Q[kk][c], a);
+            b[k][c] = a / Q[c][c];
+        }
+        if (r < p.S) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(p.Bp + (size_t)r * 32 + 4 * q) =
+                    make_float4(b[k][4 * q], b[k][4 * q + 1], b[k][4 * q + 2], b[k][4 * q + 3]);
+        }
+    }
+    // T = -U S L1^-T, a row per lane: T L1^T = -U S forward over the columns
+    if (t < 32) {
+        const int i = t;
+        float tr[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float a = -Q[i][c] * sgn[c];
+#pragma unroll
+            for (int k = 0; k < c; ++k) a = fmaf(-tr[k], Q[c][k], a);   // L1[c][k], k < c; tr[k] = 0 for k < i
+            tr[c] = c >= i ? a : 0.0f;
+        }
+        const uint32_t jb = p.jb;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            p.t[i * 32 + c] = ((uint32_t)i < jb && (uint32_t)c < jb) ? tr[c] : 0.0f;
+            if ((uint32_t)c < jb) {
+                // Y's first 32 rows are L's (unit lower trapezoidal; for a panel narrower than 32 the
+                // rows from jb on are ordinary rows of L)
+                if ((uint32_t)i < p.mp) p.y[(size_t)i * p.ldy + c] = c < i ? Q[i][c] : (c == i ? 1.0f : 0.0f);
+                if ((uint32_t)i < jb && c >= i) p.w[(size_t)i * p.ldw + c] = sgn[i] * Rm[i][c];
+            }
+        }
+    }
+}
+
+struct ApplyParams {
+    const float* Vl;        // [leaves][lr][32]
+    const float* Tl;        // [leaves][32][32]
+    const float* Bp;        // [leaves * 32][32]
+    float*       y;         // the panel's first entry in Y
+    size_t       ldy;
+    uint32_t     mp, jb, lr;
+};
+
+template <int RPT>
+__global__ void __launch_bounds__(PT) panel_apply_kernel(const ApplyParams p) {
+    __shared__ float Vt[32][33], Ti[32][33], Bi[32][33], X[32][33], M[32][33];
+    const int t = threadIdx.x;
+    const uint32_t blk = blockIdx.x;
+    for (int idx = t; idx < 1024; idx += PT) {
+        Vt[idx >> 5][idx & 31] = p.Vl[(size_t)blk * p.lr * 32 + idx];
+        Ti[idx >> 5][idx & 31] = p.Tl[(size_t)blk * 1024 + idx];
+        Bi[idx >> 5][idx & 31] = p.Bp[(size_t)blk * 1024 + idx];
+    }
+    __syncthreads();
+    mat32<true>(Vt, Bi, X);
+    __syncthreads();
+    mat32<false>(Ti, X, M);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+        const uint32_t row = t + PT * k, gr = blk * p.lr + row;
+        if (gr >= p.mp || (blk == 0 && row < 32)) continue;   // the first 32 rows are L1, written by the top kernel
+        const float* vsrc = p.Vl + ((size_t)blk * p.lr + row) * 32;
+        float v[32], yv[32];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(vsrc + 4 * q);
+            v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) yv[c] = row < 32 ? Bi[row][c] : 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) yv[c] = fmaf(-v[kk], M[kk][c], yv[c]);
+        }
+        float* dst = p.y + (size_t)gr * p.ldy;
+        if (p.jb == 32 && (p.ldy & 3) == 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(yv[4 * q], yv[4 * q + 1], yv[4 * q + 2], yv[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if ((uint32_t)c < p.jb) dst[c] = yv[c];
+        }
+    }
+}
+
+int rows_per_thread(uint32_t mp) { return mp <= 4096 ? 1 : mp <= 8192 ? 2 : 4; }
+
+} // namespace
+
+bool panel_fast_fits(uint32_t mp, uint32_t jb) { return jb >= 1 && jb <= 32 && mp >= jb && mp <= 16384; }
+
+size_t panel_fast_workspace_floats(uint32_t mp) {
+    const uint32_t lr = PT * rows_per_thread(mp), leaves = (mp + lr - 1) / lr;
+    return (size_t)leaves * lr * 32 + (size_t)leaves * 1024 * 3 + 256;
+}
+
+// The panel at `panel` (mp x jb, row stride ldw, inside the working copy) to compact-WY form: its R
+// (S R) into the working copy's upper triangle, Y into `y` (row stride ldy), T into t[32][32].
+void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t mp, uint32_t jb, float* y, size_t ldy,
+                       float* t, float* ws) {
+    const int rpt = rows_per_thread(mp);
+    const uint32_t lr = PT * rpt, leaves = (mp + lr - 1) / lr;
+    float* Vl = ws;
+    float* Tl = Vl + (size_t)leaves * lr * 32;
+    float* Sl = Tl + (size_t)leaves * 1024;
+    float* Bp = Sl + (size_t)leaves * 1024;
+    LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
+    if (rpt == 1) panel_leaf_kernel<1><<<leaves, PT, 0, stream>>>(lp);
+    else if (rpt == 2) panel_leaf_kernel<2><<<leaves, PT, 0, stream>>>(lp);
+    else panel_leaf_kernel<4><<<leaves, PT, 0, stream>>>(lp);
+    TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp};
+    panel_top_kernel<<<1, PT, 0, stream>>>(tp);
+    ApplyParams ap{Vl, Tl, Bp, y, ldy, mp, jb, lr};
+    if (rpt == 1) panel_apply_kernel<1><<<leaves, PT, 0, stream>>>(ap);
+    else if (rpt == 2) panel_apply_kernel<2><<<leaves, PT, 0, stream>>>(ap);
+    else panel_apply_kernel<4><<<leaves, PT, 0, stream>>>(ap);
+    cuda_check(cudaGetLastError(), "panel launch");
+}
+
+} // namespace mlb
