@@ -39,7 +39,7 @@ namespace mlb {
 namespace {
 
 constexpr int NB  = 32;     // panel width
-constexpr int RCH = 256;    // rows per chunk of the Y^T C partial sums
+constexpr int RCH = 64;     // rows per chunk of the Y^T C partial sums (the inner updates are narrow: many short chunks)
 
 struct MatInfo {            // per matrix, written by the scan
     unsigned amax_bits;     // bit pattern of the largest magnitude (non-negative floats order as integers)
@@ -322,6 +322,248 @@ __global__ void __launch_bounds__(256) yz_kernel(const float* __restrict__ Y, si
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// The same three kernels for an aggregate of up to 128 reflectors
+// ---------------------------------------------------------------------------
+constexpr int AG  = 128;    // columns per aggregate (four panels)
+constexpr int WCH = 512;    // rows per chunk of the wide Y^T C partial sums
+
+// Zp[chunk][i][j] = sum over the chunk's rows r of Y[r][i] C[r][j]; i < 128 (columns of Y from kw on
+// read as zero), j < nc. Grid (ceil(nc / 128), chunks); a thread accumulates 8 x 8.
+__global__ void __launch_bounds__(256) ytc_wide_kernel(const float* __restrict__ Y, size_t ldy,
+                                                       const float* __restrict__ C, size_t ldc, uint32_t mp, uint32_t kw,
+                                                       uint32_t nc, float* Zp, uint32_t ncp) {
+    __shared__ __align__(16) float Ys[32][132];
+    __shared__ __align__(16) float Cs[32][132];
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+    const uint32_t j0 = blockIdx.x * 128;
+    const uint32_t r_begin = blockIdx.y * WCH, r_end = min(mp, r_begin + WCH);
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+    for (uint32_t r0 = r_begin; r0 < r_end; r0 += 32) {
+        __syncthreads();
+#pragma unroll 4
+        for (int e = 0; e < 16; ++e) {
+            const int idx = threadIdx.x + 256 * e;
+            const uint32_t r = r0 + (idx >> 7), c = idx & 127;
+            Ys[idx >> 7][c] = (r < r_end && c < kw) ? Y[(size_t)r * ldy + c] : 0.0f;
+            Cs[idx >> 7][c] = (r < r_end && j0 + c < nc) ? C[(size_t)r * ldc + j0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const float4 y0 = *reinterpret_cast<const float4*>(&Ys[r][8 * tr]);
+            const float4 y1 = *reinterpret_cast<const float4*>(&Ys[r][8 * tr + 4]);
+            const float4 c0 = *reinterpret_cast<const float4*>(&Cs[r][8 * tc]);
+            const float4 c1 = *reinterpret_cast<const float4*>(&Cs[r][8 * tc + 4]);
+            const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+            const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(yv[a], cv[b], acc[a][b]);
+        }
+    }
+    float* out = Zp + (size_t)blockIdx.y * AG * ncp;
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const uint32_t j = j0 + 8 * tc + b;
+            if (j < nc) out[(size_t)(8 * tr + a) * ncp + j] = acc[a][b];
+        }
+}
+
+// Z[i][j] = sum_k op(T)[i][k] (sum_chunks Zp[chunk][k][j]), T 128 x 128. Grid ceil(nc / 32).
+// Dynamic shared memory: op(T) transposed [128][132] and the summed chunks [128][36].
+__global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
+                                                            uint32_t ncp, const float* __restrict__ T, int transposed,
+                                                            float* Z) {
+    extern __shared__ __align__(16) float dsm[];
+    float (*Tt)[132] = reinterpret_cast<float (*)[132]>(dsm);                // Tt[k][i] = op(T)[i][k]
+    float (*Zs)[36]  = reinterpret_cast<float (*)[36]>(dsm + 128 * 132);
+    const uint32_t j0 = blockIdx.x * 32;
+    for (int idx = threadIdx.x; idx < 128 * 128; idx += 256) {
+        const int k = idx >> 7, i = idx & 127;
+        Tt[k][i] = transposed ? T[k * 128 + i] : T[i * 128 + k];
+    }
+    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+        const uint32_t k = idx >> 5, j = j0 + (idx & 31);
+        float sum = 0.0f;
+        if (j < nc)
+            for (uint32_t ch = 0; ch < chunks; ++ch) sum += Zp[((size_t)ch * AG + k) * ncp + j];
+        Zs[k][idx & 31] = sum;
+    }
+    __syncthreads();
+    const int ig = threadIdx.x >> 3, jg = threadIdx.x & 7;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+#pragma unroll 4
+    for (int k = 0; k < 128; ++k) {
+        const float4 t4 = *reinterpret_cast<const float4*>(&Tt[k][4 * ig]);
+        const float4 z0 = *reinterpret_cast<const float4*>(&Zs[k][4 * jg]);
+        const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+        const float zv[4] = {z0.x, z0.y, z0.z, z0.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(tv[a], zv[b], acc[a][b]);
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t j = j0 + 4 * jg + b;
+            if (j < nc) Z[(size_t)(4 * ig + a) * ncp + j] = acc[a][b];
+        }
+}
+
+// C[r][j] -= sum_k Y[r][k] Z[k][j], k < kw <= 128. Grid (ceil(nc / 128), ceil(mp / 128)); a thread owns 8 x 8.
+__global__ void __launch_bounds__(256) yz_wide_kernel(const float* __restrict__ Y, size_t ldy,
+                                                      const float* __restrict__ Z, uint32_t ncp, float* C, size_t ldc,
+                                                      uint32_t mp, uint32_t kw, uint32_t nc) {
+    __shared__ __align__(16) float Ys[32][132];   // [k][row]
+    __shared__ __align__(16) float Zs[32][128];   // [k][col]
+    const uint32_t j0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+    for (uint32_t k0 = 0; k0 < kw; k0 += 32) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+            const uint32_t r = idx >> 5, k = idx & 31;
+            Ys[k][r] = (r0 + r < mp && k0 + k < kw) ? Y[(size_t)(r0 + r) * ldy + k0 + k] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < 32 * 128; idx += 256) {
+            const uint32_t k = idx >> 7, j = idx & 127;
+            Zs[k][j] = (j0 + j < nc && k0 + k < kw) ? Z[(size_t)(k0 + k) * ncp + j0 + j] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int k = 0; k < 32; ++k) {
+            const float4 y0 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr]);
+            const float4 y1 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr + 4]);
+            const float4 z0 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc]);
+            const float4 z1 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc + 4]);
+            const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+            const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(yv[a], zv[b], acc[a][b]);
+        }
+    }
+    const bool vec = (ldc & 3) == 0 && (reinterpret_cast<size_t>(C) & 15) == 0 && j0 + 8 * tc + 8 <= nc;
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+        const uint32_t r = r0 + 8 * tr + a;
+        if (r >= mp) continue;
+        float* row = C + (size_t)r * ldc + j0 + 8 * tc;
+        if (vec) {
+            float4 c0 = *reinterpret_cast<float4*>(row), c1 = *reinterpret_cast<float4*>(row + 4);
+            c0.x -= acc[a][0]; c0.y -= acc[a][1]; c0.z -= acc[a][2]; c0.w -= acc[a][3];
+            c1.x -= acc[a][4]; c1.y -= acc[a][5]; c1.z -= acc[a][6]; c1.w -= acc[a][7];
+            *reinterpret_cast<float4*>(row) = c0;
+            *reinterpret_cast<float4*>(row + 4) = c1;
+        } else {
+#pragma unroll
+            for (int b = 0; b < 8; ++b)
+                if (j0 + 8 * tc + b < nc) row[b] -= acc[a][b];
+        }
+    }
+}
+
+// T of an aggregate (128 x 128, zero padded) from its panels' T's and the Gram matrix of its Y:
+// T(0:c, c:c+32) = -T(0:c, 0:c) (Y(:, 0:c)^T Y_q) T_q for each panel q after the first
+// (the reference: bd_merge_t, shaders/Svd_Bidiag.metal:1131-1164). One block; dynamic shared memory.
+struct MergeParams {
+    const float* gram;      // partial Gram matrices [chunks][128][gld] (null when there is one panel)
+    uint32_t     chunks, gld;
+    const float* tp;        // the panels' T's, [panels][32][32]
+    uint32_t     panels;
+    float*       tagg;      // [128][128]
+};
+
+__global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
+    extern __shared__ __align__(16) float dsm[];
+    float (*Ta)[129] = reinterpret_cast<float (*)[129]>(dsm);
+    float (*Gq)[33]  = reinterpret_cast<float (*)[33]>(dsm + 128 * 129);
+    float (*Tq)[33]  = reinterpret_cast<float (*)[33]>(dsm + 128 * 129 + 96 * 33);
+    float (*X)[33]   = reinterpret_cast<float (*)[33]>(dsm + 128 * 129 + 96 * 33 + 32 * 33);
+    const int t = threadIdx.x;
+    for (int idx = t; idx < 128 * 128; idx += 256) {
+        const int i = idx >> 7, j = idx & 127;
+        float v = 0.0f;
+        if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) v = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
+        Ta[i][j] = v;
+    }
+    __syncthreads();
+    for (uint32_t q = 1; q < p.panels; ++q) {
+        const int c0 = 32 * (int)q;
+        for (int idx = t; idx < c0 * 32; idx += 256) {
+            const int i = idx >> 5, c = idx & 31;
+            float g = 0.0f;
+            for (uint32_t ch = 0; ch < p.chunks; ++ch) g += p.gram[((size_t)ch * AG + i) * p.gld + c0 + c];
+            Gq[i][c] = g;
+        }
+        for (int idx = t; idx < 1024; idx += 256) Tq[idx >> 5][idx & 31] = Ta[c0 + (idx >> 5)][c0 + (idx & 31)];
+        __syncthreads();
+        for (int idx = t; idx < c0 * 32; idx += 256) {
+            const int i = idx >> 5, c = idx & 31;
+            float a = 0.0f;
+#pragma unroll 8
+            for (int k = 0; k < 32; ++k) a = fmaf(Gq[i][k], Tq[k][c], a);
+            X[i][c] = a;
+        }
+        __syncthreads();
+        for (int idx = t; idx < c0 * 32; idx += 256) {
+            const int i = idx >> 5, c = idx & 31;
+            float a = 0.0f;
+            for (int k = i; k < c0; ++k) a = fmaf(Ta[i][k], X[k][c], a);   // T is upper triangular
+            Ta[i][c0 + c] = -a;
+        }
+        __syncthreads();
+    }
+    for (int idx = t; idx < 128 * 128; idx += 256) p.tagg[idx] = Ta[idx >> 7][idx & 127];
+}
+
+constexpr size_t kReduceWideSmem = (128 * 132 + 128 * 36) * sizeof(float);
+constexpr size_t kMergeSmem = (128 * 129 + 96 * 33 + 32 * 33 + 96 * 33) * sizeof(float);
+
+// C (mp rows, nc columns) <- (I - Y op(T) Y^T) C for an aggregate: Y mp x kw (kw <= 128), T 128 x 128.
+void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
+                     size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z) {
+    if (nc == 0 || mp == 0) return;
+    const uint32_t chunks = (mp + WCH - 1) / WCH, ncp = (nc + 3) & ~3u;
+    ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
+    reduce_t_wide_kernel<<<(nc + 31) / 32, 256, kReduceWideSmem, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    yz_wide_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, kw, nc);
+    cuda_check(cudaGetLastError(), "aggregate reflector launch");
+}
+
+// T of the aggregate whose Y starts at `Y` (ma rows, wa columns, `panels` panels with T's at tp).
+void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t ma, uint32_t wa, uint32_t panels,
+                       const float* tp, float* tagg, float* zp) {
+    MergeParams mp{nullptr, 0, 0, tp, panels, tagg};
+    if (panels > 1) {
+        const uint32_t chunks = (ma + WCH - 1) / WCH, gld = (wa + 3) & ~3u;
+        ytc_wide_kernel<<<dim3(1, chunks), 256, 0, stream>>>(Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
+        mp.gram = zp; mp.chunks = chunks; mp.gld = gld;
+    }
+    merge_t_kernel<<<1, 256, kMergeSmem, stream>>>(mp);
+    cuda_check(cudaGetLastError(), "aggregate T launch");
+}
+
 unsigned grid_for(size_t count) { return (unsigned)std::min<size_t>((count + 255) / 256, 148 * 8); }
 
 // C (mp rows from C's first row, nc columns) <- (I - Y op(T) Y^T) C
@@ -350,23 +592,35 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const uint32_t chunks = (m + RCH - 1) / RCH, ncp = (wide + 3) & ~3u;
 
     // workspace (floats), shared by the matrices of the batch, which are factored one after another
+    const uint32_t naggs = (K + AG - 1) / AG;
+    const uint32_t chunks_w = (m + WCH - 1) / WCH;
     auto up64 = [](size_t f) { return (f + 63) & ~(size_t)63; };
     size_t off = 0;
     auto take = [&](size_t floats) { const size_t o = off; off += up64(floats); return o; };
     const size_t o_w = take((size_t)m * ldw), o_y = take((size_t)m * ldy), o_t = take((size_t)npanels * 1024);
+    const size_t o_ta = take((size_t)naggs * AG * AG);
     const size_t o_qp = take((size_t)m * NB), o_rp = take(NB * NB), o_ui = take(NB * NB);
-    const size_t o_zp = take((size_t)chunks * 32 * ncp), o_z = take((size_t)32 * ncp);
+    const size_t o_zp = take(std::max((size_t)chunks * 32 * ncp, (size_t)chunks_w * AG * ncp)), o_z = take((size_t)AG * ncp);
     const size_t o_info = take(64);
     size_t tsqr_floats = 0;
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
-        tsqr_floats = std::max(tsqr_floats, tsqr_workspace_floats(ctx, m - k0, std::min<uint32_t>(NB, K - k0), 1, true));
+        if (!panel_fast_fits(m - k0, std::min<uint32_t>(NB, K - k0)))
+            tsqr_floats = std::max(tsqr_floats, tsqr_workspace_floats(ctx, m - k0, std::min<uint32_t>(NB, K - k0), 1, true));
     const size_t o_ts = take(tsqr_floats);
     const size_t o_pf = take(panel_fast_workspace_floats(std::min<uint32_t>(m, 16384)));
     static const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree, for comparison
     float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
-    float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
+    float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
     float *Zp = ws + o_zp, *Z = ws + o_z, *ts = ws + o_ts, *pf = ws + o_pf;
     MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
+    static bool configured = false;
+    if (!configured) {
+        cuda_check(cudaFuncSetAttribute(reduce_t_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kReduceWideSmem), "reduce_t_wide shared memory");
+        cuda_check(cudaFuncSetAttribute(merge_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMergeSmem),
+                   "merge_t shared memory");
+        configured = true;
+    }
 
     for (uint32_t b = 0; b < pr.batch; ++b) {
         const float* A = pr.a + (size_t)b * m * n;
@@ -377,33 +631,49 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         scan_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, (size_t)m * n, info);
         scale_copy_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, W, m, n, ldw, info);
 
-        // forward: panels and trailing updates
-        for (uint32_t pi = 0; pi < npanels; ++pi) {
-            const uint32_t k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
-            if (!slow_panels && panel_fast_fits(mp, jb)) {
-                panel_factor_fast(stream, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
-                                  T + (size_t)pi * 1024, pf);
-            } else {   // taller than the register-resident panel kernels take: the general tree
-                tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
-                ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
-                reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
-                if (mp > jb)   // the rows below the top block: Qp U^-1
-                    launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0, ldy,
-                                      Ui, true, 1, 1, mp - jb, mp - jb, jb);
+        // forward. Panels of 32 columns in aggregates of 128: a panel's reflector is applied at once
+        // only to the columns left in its aggregate; the columns right of the aggregate get all of
+        // its (up to) 128 reflectors in one rank-128 update.
+        for (uint32_t ag = 0; ag < naggs; ++ag) {
+            const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0, pans = (wa + NB - 1) / NB;
+            for (uint32_t pp = 0; pp < pans; ++pp) {
+                const uint32_t pi = ag * (AG / NB) + pp, k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
+                if (!slow_panels && panel_fast_fits(mp, jb)) {
+                    panel_factor_fast(stream, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
+                                      T + (size_t)pi * 1024, pf);
+                } else {   // taller than the register-resident panel kernels take: the general tree
+                    tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
+                    ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
+                    reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
+                    if (mp > jb)   // the rows below the top block: Qp U^-1
+                        launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0,
+                                          ldy, Ui, true, 1, 1, mp - jb, mp - jb, jb);
+                }
+                if (pp)   // Y is read as one mp x wa matrix by the aggregate's products: zeros above the panel's top
+                    cuda_check(cudaMemset2DAsync(Y + (size_t)j0 * ldy + k0, (size_t)ldy * sizeof(float), 0,
+                                                 jb * sizeof(float), k0 - j0, stream), "cudaMemset2DAsync");
+                const uint32_t inside = j0 + wa - (k0 + jb);   // columns of the aggregate right of the panel
+                if (inside)
+                    apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, true,
+                                          W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside, Zp, Z);
             }
-            if (k0 + jb < n)
-                apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, true,
-                                      W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, n - k0 - jb, Zp, Z);
+            const uint32_t right = n - (j0 + wa);
+            if (right || qc)
+                build_aggregate_t(stream, Y + (size_t)j0 * ldy + j0, ldy, ma, wa, pans, T + (size_t)ag * (AG / NB) * 1024,
+                                  Ta + (size_t)ag * AG * AG, Zp);
+            if (right)
+                apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z);
         }
         r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
         if (!qc) continue;
 
-        // backward: Q = H_0 ... H_{K-1} [I; 0]
+        // backward: Q = H_0 ... H_{K-1} [I; 0], an aggregate at a time
         launch_fill_identity(stream, Q, 1, m, qc);
-        for (uint32_t pi = npanels; pi-- > 0;) {
-            const uint32_t k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
-            apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, false,
-                                  Q + (size_t)k0 * qc + k0, qc, mp, jb, qc - k0, Zp, Z);
+        for (uint32_t ag = naggs; ag-- > 0;) {
+            const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0;
+            apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, false,
+                            Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z);
         }
         nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);
     }

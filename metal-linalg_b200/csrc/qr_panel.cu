@@ -47,6 +47,29 @@ struct PanelSmem {
     float T[32][33];
 };
 
+// slarfg's reflector as common.cuh's, with rsqrt / rcp and one Newton step each instead of the
+// IEEE square root and divisions (it sits on the critical path of every column step).
+__device__ __forceinline__ float newton_div(float a, float b) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+    const float q = a * r;
+    return fmaf(fmaf(-b, q, a), r, q);
+}
+__device__ __forceinline__ void reflector_fast(float alpha, float ss, float& beta, float& tau, float& sc) {
+    beta = alpha;
+    tau  = 0.0f;
+    sc   = 0.0f;
+    if (ss >= kTinySumsq) {
+        const float n2 = fmaf(alpha, alpha, ss);
+        const float y = rsqrtf(n2);
+        float nrm = n2 * y;
+        nrm = fmaf(fmaf(-nrm, nrm, n2), 0.5f * y, nrm);
+        beta = -copysignf(nrm, alpha);
+        tau  = newton_div(beta - alpha, beta);
+        sc   = newton_div(1.0f, alpha - beta);
+    }
+}
+
 // Sum over the warp of 32 values a lane: lane c returns the sum of p[c].
 __device__ __forceinline__ float butterfly32(float (&p)[32], int lane) {
 #pragma unroll
@@ -94,7 +117,7 @@ __device__ __forceinline__ void factor_rows(float (&x)[RPT][32], PanelSmem& s) {
             for (int w = 0; w < PT / 32; ++w) v += s.red[w][lane];
             const float ss = __shfl_sync(kFull, v, 0);
             float beta, tau, sc;
-            reflector(s.prow[0], ss, beta, tau, sc);
+            reflector_fast(s.prow[0], ss, beta, tau, sc);
             const float val = fmaf(sc, v, s.prow[lane]);
             s.wv[buf][lane] = (lane >= 1 && lane <= 31 - j) ? tau * val : 0.0f;
             if (lane >= 32 - j) s.G[(j + lane) & 31][j] = val;
@@ -229,7 +252,8 @@ struct TopParams {
 
 __global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
     __shared__ __align__(16) PanelSmem s;
-    __shared__ float V1[32][33], M[32][33], B0[32][33], X[32][33], Q[32][33], V0[32][33], T0[32][33], Rm[32][33];
+    __shared__ float V1[32][33], M[32][33], B0[32][33], X[32][33], V0[32][33], T0[32][33], Rm[32][33];
+    __shared__ __align__(16) float M4[32][36], Q[32][36];   // read as 16-byte words
     __shared__ float sgn[32];
     const int t = threadIdx.x;
     float x[2][32];
@@ -269,26 +293,37 @@ __global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
             for (int e = 0; e < 4; ++e) acc[e] = fmaf(a, V1[c0 + e][k], acc[e]);
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) M[i][c0 + e] = acc[e];
+        for (int e = 0; e < 4; ++e) M4[i][c0 + e] = acc[e];
     }
     __syncthreads();
-    float b[2][32];
+    // a row of B per thread and pass; the rows wait in global memory (Bp) for U
+    auto b_row = [&](const float (&xr)[32], const int row) {
+        float b[32];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int row = t + PT * k;
-#pragma unroll
-        for (int c = 0; c < 32; ++c) b[k][c] = (row == c) ? 1.0f : 0.0f;
+        for (int c = 0; c < 32; ++c) b[c] = (row == c) ? 1.0f : 0.0f;
 #pragma unroll
         for (int kk = 0; kk < 32; ++kk) {
-            const float v = clean_v(x[k][kk], row, kk);
+            const float v = clean_v(xr[kk], row, kk);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) b[k][c] = fmaf(-v, M[kk][c], b[k][c]);
+            for (int q = 0; q < 8; ++q) {
+                const float4 m4 = *reinterpret_cast<const float4*>(&M4[kk][4 * q]);
+                b[4 * q] = fmaf(-v, m4.x, b[4 * q]); b[4 * q + 1] = fmaf(-v, m4.y, b[4 * q + 1]);
+                b[4 * q + 2] = fmaf(-v, m4.z, b[4 * q + 2]); b[4 * q + 3] = fmaf(-v, m4.w, b[4 * q + 3]);
+            }
         }
-    }
-    if (t < 32) {
+        if (row < 32) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) B0[t][c] = b[0][c];
-    }
+            for (int c = 0; c < 32; ++c) B0[row][c] = b[c];
+        }
+        if ((uint32_t)row < p.S) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(p.Bp + (size_t)row * 32 + 4 * q) =
+                    make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
+        }
+    };
+    b_row(x[0], t);
+    b_row(x[1], t + PT);
     __syncthreads();
     // the panel's Q on its first 32 rows: Q1 = B0 - V0 (T0 (V0^T B0)), V0 and T0 leaf 0's
     mat32<true>(V0, B0, X);
@@ -323,23 +358,33 @@ __global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
         }
     }
     __syncthreads();
-    // B' = B U^-1, a row per thread: x U = b by forward substitution over the columns
-#pragma unroll
+    // B' = B U^-1, a row per thread and pass: x U = b, eliminating with one row of U at a time
+#pragma unroll 1
     for (int k = 0; k < 2; ++k) {
         const uint32_t r = t + PT * k;
+        if (r >= p.S) continue;
+        float b[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            float a = b[k][c];
-#pragma unroll
-            for (int kk = 0; kk < c; ++kk) a = fmaf(-b[k][kk], Q[kk][c], a);
-            b[k][c] = a / Q[c][c];
+        for (int q = 0; q < 8; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(p.Bp + (size_t)r * 32 + 4 * q);
+            b[4 * q] = f.x; b[4 * q + 1] = f.y; b[4 * q + 2] = f.z; b[4 * q + 3] = f.w;
         }
-        if (r < p.S) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(p.Bp + (size_t)r * 32 + 4 * q) =
-                    make_float4(b[k][4 * q], b[k][4 * q + 1], b[k][4 * q + 2], b[k][4 * q + 3]);
+        for (int kk = 0; kk < 32; ++kk) {
+            b[kk] = newton_div(b[kk], Q[kk][kk]);
+#pragma unroll
+            for (int q = kk / 4; q < 8; ++q) {
+                const float4 u4 = *reinterpret_cast<const float4*>(&Q[kk][4 * q]);
+                if (4 * q + 0 > kk) b[4 * q + 0] = fmaf(-b[kk], u4.x, b[4 * q + 0]);
+                if (4 * q + 1 > kk) b[4 * q + 1] = fmaf(-b[kk], u4.y, b[4 * q + 1]);
+                if (4 * q + 2 > kk) b[4 * q + 2] = fmaf(-b[kk], u4.z, b[4 * q + 2]);
+                if (4 * q + 3 > kk) b[4 * q + 3] = fmaf(-b[kk], u4.w, b[4 * q + 3]);
+            }
         }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(p.Bp + (size_t)r * 32 + 4 * q) =
+                make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
     }
     // T = -U S L1^-T, a row per lane: T L1^T = -U S forward over the columns
     if (t < 32) {
