@@ -75,6 +75,13 @@ size_t panel_fast_workspace_floats(uint32_t mp);
 void   panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t mp, uint32_t jb, float* y, size_t ldy,
                          float* t, float* ws);
 
+// The rank-128 products of the blocked QR on the tcgen05 tensor cores, 3xTF32 (tc_gemm.cu).
+// `error` is set non-zero if a bounded wait inside the kernel ran out.
+void launch_tc_ytc(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp, uint32_t kw,
+                   uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, unsigned* error);
+void launch_tc_yz(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
+                  uint32_t mp, uint32_t kw, uint32_t nc, unsigned* error);
+
 // Blocked compact-WY QR over the whole grid, any shape.
 bool qr_blocked_fits(uint32_t m, uint32_t n);
 void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);

@@ -2,31 +2,34 @@
 //
 // It takes the place of the reference's qr_blocked (src/qr_blocked.mm:56-302 with
 // src/band_reduce.mm:196-507 and the panel kernels of shaders/Svd_Bidiag.metal:
-// 428-886,1125-1279): a scaled working copy of the matrix, panels factored by
-// TSQR with Householder reconstruction, the trailing matrix updated by a block
-// reflector per panel, R read off the working copy, Q formed backward from
-// [I; 0] by the same block reflectors.
+// 428-886,1125-1279) and has its structure: a scaled working copy W of the
+// matrix; panels of 32 columns gathered in aggregates of 128; R read off W; Q
+// formed backward from [I; 0] by the aggregates' block reflectors.
 //
-// Per panel of 32 columns (rows k0..m, columns k0..k0+jb of the working copy W):
+//   panel      rows k0..m, columns k0..k0+32 of W to compact-WY form (Y, T, R) by
+//              TSQR over row blocks with Householder reconstruction (Ballard,
+//              Demmel, Grigori, Jacquelin, Nguyen, Solomonik 2014; the reference:
+//              bd_tsqr_top, shaders/Svd_Bidiag.metal:757-802): the register-resident
+//              kernels of qr_panel.cu up to 16384 rows, the general tree
+//              (tsqr_core + reconstruct_kernel here) beyond;
+//   inside     the panel's reflector applied to the columns left in its aggregate
+//              (at most 96) by inner_update_kernel, one launch;
+//   aggregate  T of the aggregate's 128 reflectors from its panels' T's and the
+//              Gram matrix Y^T Y (merge_t_kernel; the reference: bd_merge_t), then
+//              the rank-128 update of everything right of it, C -= Y (T^T (Y^T C)):
+//              Zp = Y^T C by row chunks and C -= Y Z on the tcgen05 tensor cores by
+//              3xTF32 (tc_gemm.cu), the chunks summed and multiplied by T^T in
+//              between (reduce_t_wide_kernel). QR_TENSOR=0 runs both products as
+//              FP32 FMA kernels instead (ytc_wide_kernel, yz_wide_kernel): the
+//              fallback with plain float32 rounding.
 //
-//   1. thin QR of the panel by the tree of row blocks (tsqr_core: the
-//      block-per-matrix kernel on blocks of 256 rows, then on the stack of their
-//      R's): explicit Qp (mp x jb) and Rp;
-//   2. Householder reconstruction (Ballard, Demmel, Grigori, Jacquelin, Nguyen,
-//      Solomonik, "Reconstructing Householder vectors from TSQR", 2014; the
-//      reference does the same in bd_tsqr_top, shaders/Svd_Bidiag.metal:757-802):
-//      LU without pivoting of Qp - [S; 0] with the signs S = -sgn(pivot) chosen on
-//      the way, so that every pivot is at least 1 in magnitude: L is the unit lower
-//      trapezoidal Y of the compact-WY form, T = -U S L1^-T, and the panel's R is
-//      S Rp. Only the top jb x jb block takes part in the elimination
-//      (reconstruct_kernel, one warp); the rows below are Qp U^-1, a product;
-//   3. the block reflector applied to the columns right of the panel:
-//      C -= Y (T^T (Y^T C)) as Zp = Y^T C by row chunks (ytc_kernel), the chunks
-//      summed and multiplied by T^T (reduce_t_kernel), C -= Y Z (yz_kernel).
+// The chain of panels runs on a high-priority stream of its own; after an
+// aggregate it updates only the next aggregate's columns itself and leaves the
+// columns beyond to the caller's stream, where that update runs beside the next
+// panels (look-ahead).
 //
 // Y is kept apart from W (clean: unit diagonal, zeros above) so that the products
-// read it as a plain matrix. The products here are register-tiled FP32 FMA
-// kernels reading 16-byte words from shared memory.
+// read it as a plain matrix.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -39,7 +42,6 @@ namespace mlb {
 namespace {
 
 constexpr int NB  = 32;     // panel width
-constexpr int RCH = 64;     // rows per chunk of the Y^T C partial sums (the inner updates are narrow: many short chunks)
 
 struct MatInfo {            // per matrix, written by the scan
     unsigned amax_bits;     // bit pattern of the largest magnitude (non-negative floats order as integers)
@@ -191,140 +193,7 @@ __global__ void __launch_bounds__(32) reconstruct_kernel(const ReconParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Block reflector application: three kernels
-// ---------------------------------------------------------------------------
-
-// Zp[chunk][i][j] = sum over the chunk's rows r of Y[r][i] C[r][j]; i < 32 (columns of Y from jb on
-// read as zero), j < nc. Grid (ceil(nc / 128), chunks). A thread accumulates 4 x 4.
-__global__ void __launch_bounds__(256) ytc_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ C,
-                                                  size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* Zp,
-                                                  uint32_t ncp) {
-    __shared__ __align__(16) float Ys[32][36];
-    __shared__ __align__(16) float Cs[32][132];
-    const int ti = threadIdx.x & 7, tj = threadIdx.x >> 3;
-    const uint32_t j0 = blockIdx.x * 128;
-    const uint32_t r_begin = blockIdx.y * RCH, r_end = min(mp, r_begin + RCH);
-    float acc[4][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
-    for (uint32_t r0 = r_begin; r0 < r_end; r0 += 32) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 32 * 32; idx += 256) {
-            const uint32_t r = r0 + (idx >> 5), i = idx & 31;
-            Ys[idx >> 5][i] = (r < r_end && i < jb) ? Y[(size_t)r * ldy + i] : 0.0f;
-        }
-        for (int idx = threadIdx.x; idx < 32 * 128; idx += 256) {
-            const uint32_t r = r0 + (idx >> 7), j = j0 + (idx & 127);
-            Cs[idx >> 7][idx & 127] = (r < r_end && j < nc) ? C[(size_t)r * ldc + j] : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            const float4 y = *reinterpret_cast<const float4*>(&Ys[r][4 * ti]);
-            const float4 c = *reinterpret_cast<const float4*>(&Cs[r][4 * tj]);
-            const float yv[4] = {y.x, y.y, y.z, y.w}, cv[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(yv[a], cv[b], acc[a][b]);
-        }
-    }
-    float* out = Zp + (size_t)blockIdx.y * 32 * ncp;
-#pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t j = j0 + 4 * tj + b;
-            if (j < nc) out[(size_t)(4 * ti + a) * ncp + j] = acc[a][b];
-        }
-}
-
-// Z[i][j] = sum_k op(T)[i][k] (sum_chunks Zp[chunk][k][j]); op = transpose (the factorisation) or not (Q).
-// Grid ceil(nc / 64).
-__global__ void __launch_bounds__(256) reduce_t_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
-                                                       uint32_t ncp, const float* __restrict__ T, int transposed,
-                                                       float* Z) {
-    __shared__ float Ts[32][33];
-    __shared__ float Zs[32][65];
-    const uint32_t j0 = blockIdx.x * 64;
-    for (int idx = threadIdx.x; idx < 1024; idx += 256) Ts[idx >> 5][idx & 31] = T[idx];
-    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
-        const uint32_t k = idx >> 6, j = j0 + (idx & 63);
-        float s = 0.0f;
-        if (j < nc)
-            for (uint32_t ch = 0; ch < chunks; ++ch) s += Zp[((size_t)ch * 32 + k) * ncp + j];
-        Zs[k][idx & 63] = s;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
-        const uint32_t i = idx >> 6, jj = idx & 63;
-        float s = 0.0f;
-#pragma unroll 8
-        for (int k = 0; k < 32; ++k) s = fmaf(transposed ? Ts[k][i] : Ts[i][k], Zs[k][jj], s);
-        if (j0 + jj < nc) Z[(size_t)i * ncp + j0 + jj] = s;
-    }
-}
-
-// C[r][j] -= sum_k Y[r][k] Z[k][j], k < 32. Grid (ceil(nc / 128), ceil(mp / 128)); a thread owns 8 x 8.
-__global__ void __launch_bounds__(256) yz_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ Z,
-                                                 uint32_t ncp, float* C, size_t ldc, uint32_t mp, uint32_t jb,
-                                                 uint32_t nc) {
-    __shared__ __align__(16) float Ys[32][132];   // [k][row]
-    __shared__ __align__(16) float Zs[32][128];   // [k][col]
-    const uint32_t j0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
-    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
-        const uint32_t r = idx >> 5, k = idx & 31;
-        Ys[k][r] = (r0 + r < mp && k < jb) ? Y[(size_t)(r0 + r) * ldy + k] : 0.0f;
-    }
-    for (int idx = threadIdx.x; idx < 32 * 128; idx += 256) {
-        const uint32_t k = idx >> 7, j = idx & 127;
-        Zs[k][j] = (j0 + j < nc) ? Z[(size_t)k * ncp + j0 + j] : 0.0f;
-    }
-    __syncthreads();
-    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
-    float acc[8][8];
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
-#pragma unroll 4
-    for (int k = 0; k < 32; ++k) {
-        const float4 y0 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr]);
-        const float4 y1 = *reinterpret_cast<const float4*>(&Ys[k][8 * tr + 4]);
-        const float4 z0 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc]);
-        const float4 z1 = *reinterpret_cast<const float4*>(&Zs[k][8 * tc + 4]);
-        const float yv[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-        const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-#pragma unroll
-        for (int a = 0; a < 8; ++a)
-#pragma unroll
-            for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(yv[a], zv[b], acc[a][b]);
-    }
-    const bool vec = (ldc & 3) == 0 && (reinterpret_cast<size_t>(C) & 15) == 0 && j0 + 8 * tc + 8 <= nc;
-#pragma unroll
-    for (int a = 0; a < 8; ++a) {
-        const uint32_t r = r0 + 8 * tr + a;
-        if (r >= mp) continue;
-        float* row = C + (size_t)r * ldc + j0 + 8 * tc;
-        if (vec) {
-            float4 c0 = *reinterpret_cast<float4*>(row), c1 = *reinterpret_cast<float4*>(row + 4);
-            c0.x -= acc[a][0]; c0.y -= acc[a][1]; c0.z -= acc[a][2]; c0.w -= acc[a][3];
-            c1.x -= acc[a][4]; c1.y -= acc[a][5]; c1.z -= acc[a][6]; c1.w -= acc[a][7];
-            *reinterpret_cast<float4*>(row) = c0;
-            *reinterpret_cast<float4*>(row + 4) = c1;
-        } else {
-#pragma unroll
-            for (int b = 0; b < 8; ++b)
-                if (j0 + 8 * tc + b < nc) row[b] -= acc[a][b];
-        }
-    }
-}
-
-
-// ---------------------------------------------------------------------------
-// The same three kernels for an aggregate of up to 128 reflectors
+// Block reflector application for an aggregate of up to 128 reflectors: three kernels
 // ---------------------------------------------------------------------------
 constexpr int AG  = 128;    // columns per aggregate (four panels)
 constexpr int WCH = 512;    // rows per chunk of the wide Y^T C partial sums
@@ -497,32 +366,41 @@ struct MergeParams {
 __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
     extern __shared__ __align__(16) float dsm[];
     float (*Ta)[129] = reinterpret_cast<float (*)[129]>(dsm);
-    float (*Gq)[33]  = reinterpret_cast<float (*)[33]>(dsm + 128 * 129);
-    float (*Tq)[33]  = reinterpret_cast<float (*)[33]>(dsm + 128 * 129 + 96 * 33);
-    float (*X)[33]   = reinterpret_cast<float (*)[33]>(dsm + 128 * 129 + 96 * 33 + 32 * 33);
+    float (*G)[129]  = reinterpret_cast<float (*)[129]>(dsm + 128 * 129);
+    float (*X)[33]   = reinterpret_cast<float (*)[33]>(dsm + 2 * 128 * 129);
     const int t = threadIdx.x;
+    const int width = 32 * (int)p.panels;
     for (int idx = t; idx < 128 * 128; idx += 256) {
         const int i = idx >> 7, j = idx & 127;
         float v = 0.0f;
         if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) v = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
         Ta[i][j] = v;
+        // the Gram matrix: the chunks' partial sums added up, consecutive threads on consecutive columns
+        float g = 0.0f;
+        if (p.gram && i < width && j < width && (j >> 5) > (i >> 5) && (uint32_t)j < p.gld) {
+            const float* src = p.gram + (size_t)i * p.gld + j;
+            const size_t stride = (size_t)AG * p.gld;
+            uint32_t ch = 0;
+            float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
+            for (; ch + 4 <= p.chunks; ch += 4) {
+                g0 += src[(size_t)ch * stride];
+                g1 += src[(size_t)(ch + 1) * stride];
+                g2 += src[(size_t)(ch + 2) * stride];
+                g3 += src[(size_t)(ch + 3) * stride];
+            }
+            for (; ch < p.chunks; ++ch) g0 += src[(size_t)ch * stride];
+            g = (g0 + g1) + (g2 + g3);
+        }
+        G[i][j] = g;
     }
     __syncthreads();
     for (uint32_t q = 1; q < p.panels; ++q) {
         const int c0 = 32 * (int)q;
-        for (int idx = t; idx < c0 * 32; idx += 256) {
-            const int i = idx >> 5, c = idx & 31;
-            float g = 0.0f;
-            for (uint32_t ch = 0; ch < p.chunks; ++ch) g += p.gram[((size_t)ch * AG + i) * p.gld + c0 + c];
-            Gq[i][c] = g;
-        }
-        for (int idx = t; idx < 1024; idx += 256) Tq[idx >> 5][idx & 31] = Ta[c0 + (idx >> 5)][c0 + (idx & 31)];
-        __syncthreads();
-        for (int idx = t; idx < c0 * 32; idx += 256) {
+        for (int idx = t; idx < c0 * 32; idx += 256) {      // X = G(0:c0, c0:c0+32) T_q
             const int i = idx >> 5, c = idx & 31;
             float a = 0.0f;
 #pragma unroll 8
-            for (int k = 0; k < 32; ++k) a = fmaf(Gq[i][k], Tq[k][c], a);
+            for (int k = 0; k < 32; ++k) a = fmaf(G[i][c0 + k], Ta[c0 + k][c0 + c], a);
             X[i][c] = a;
         }
         __syncthreads();
@@ -537,45 +415,170 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
     for (int idx = t; idx < 128 * 128; idx += 256) p.tagg[idx] = Ta[idx >> 7][idx & 127];
 }
 
+// The two large products run on the tensor cores (3xTF32, tc_gemm.cu) unless QR_TENSOR=0 asks for
+// the FP32 FMA kernels above, which stay as the fallback.
+bool use_tensor_cores() {
+    static const bool on = [] {
+        const char* e = std::getenv("QR_TENSOR");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 constexpr size_t kReduceWideSmem = (128 * 132 + 128 * 36) * sizeof(float);
-constexpr size_t kMergeSmem = (128 * 129 + 96 * 33 + 32 * 33 + 96 * 33) * sizeof(float);
+constexpr size_t kMergeSmem = (2 * 128 * 129 + 96 * 33) * sizeof(float);
 
 // C (mp rows, nc columns) <- (I - Y op(T) Y^T) C for an aggregate: Y mp x kw (kw <= 128), T 128 x 128.
 void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
-                     size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z) {
+                     size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z, unsigned* error) {
     if (nc == 0 || mp == 0) return;
     const uint32_t chunks = (mp + WCH - 1) / WCH, ncp = (nc + 3) & ~3u;
-    ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
+    const bool tc = use_tensor_cores();
+    if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, WCH, error);
+    else ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
     reduce_t_wide_kernel<<<(nc + 31) / 32, 256, kReduceWideSmem, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    yz_wide_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, kw, nc);
+    if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
+    else yz_wide_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, kw, nc);
     cuda_check(cudaGetLastError(), "aggregate reflector launch");
 }
 
 // T of the aggregate whose Y starts at `Y` (ma rows, wa columns, `panels` panels with T's at tp).
 void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t ma, uint32_t wa, uint32_t panels,
-                       const float* tp, float* tagg, float* zp) {
+                       const float* tp, float* tagg, float* zp, unsigned* error) {
     MergeParams mp{nullptr, 0, 0, tp, panels, tagg};
     if (panels > 1) {
-        const uint32_t chunks = (ma + WCH - 1) / WCH, gld = (wa + 3) & ~3u;
-        ytc_wide_kernel<<<dim3(1, chunks), 256, 0, stream>>>(Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
+        // the Gram matrix Y^T Y by chunks of rows (short chunks on the tensor cores: the product is
+        // small and tall, and many blocks hide its latency)
+        const uint32_t rows = use_tensor_cores() ? 128u : (uint32_t)WCH;
+        const uint32_t chunks = (ma + rows - 1) / rows, gld = (wa + 3) & ~3u;
+        if (use_tensor_cores()) launch_tc_ytc(stream, Y, ldy, Y, ldy, ma, wa, wa, zp, gld, rows, error);
+        else ytc_wide_kernel<<<dim3(1, chunks), 256, 0, stream>>>(Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
         mp.gram = zp; mp.chunks = chunks; mp.gld = gld;
     }
     merge_t_kernel<<<1, 256, kMergeSmem, stream>>>(mp);
     cuda_check(cudaGetLastError(), "aggregate T launch");
 }
 
-unsigned grid_for(size_t count) { return (unsigned)std::min<size_t>((count + 255) / 256, 148 * 8); }
+// ---------------------------------------------------------------------------
+// A panel's own update: its reflector applied to the few columns left in its aggregate
+// ---------------------------------------------------------------------------
+// C (mp x nc, nc <= 96) <- (I - Y T^T Y^T) C in ONE launch: a block owns four columns of C over all
+// the rows, so nothing crosses blocks. Pass 1: a thread takes rows t, t + 256, ... and accumulates
+// its part of Z = Y^T C (32 x 4) in registers; the parts are summed over the block (shuffles, then
+// shared memory). W = T^T Z by one warp. Pass 2: the rows again, C -= Y W. Y (mp x 32) is re-read
+// by every block from L2.
+constexpr int ICS = 4;      // columns per block
 
-// C (mp rows from C's first row, nc columns) <- (I - Y op(T) Y^T) C
-void apply_block_reflector(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
-                           size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* zp, float* z) {
-    if (nc == 0 || mp == 0) return;
-    const uint32_t chunks = (mp + RCH - 1) / RCH, ncp = (nc + 3) & ~3u;
-    ytc_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, jb, nc, zp, ncp);
-    reduce_t_kernel<<<(nc + 63) / 64, 256, 0, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    yz_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, jb, nc);
-    cuda_check(cudaGetLastError(), "block reflector launch");
+__global__ void __launch_bounds__(256) inner_update_kernel(const float* __restrict__ Y, size_t ldy,
+                                                           const float* __restrict__ T, float* C, size_t ldc,
+                                                           uint32_t mp, uint32_t jb, uint32_t nc) {
+    __shared__ float red[8][32 * ICS];
+    __shared__ float Zs[32][ICS], Ws[32][ICS];
+    __shared__ float Ts[32][33];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t c0 = blockIdx.x * ICS;
+    const uint32_t ncb = min((uint32_t)ICS, nc - c0);
+    for (int idx = t; idx < 1024; idx += 256) Ts[idx >> 5][idx & 31] = T[idx];
+    const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
+
+    float z[32][ICS];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) z[k][j] = 0.0f;
+    for (uint32_t r = t; r < mp; r += 256) {
+        float y[32], c[ICS];
+        const float* yr = Y + (size_t)r * ldy;
+        if (yvec) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 f = *reinterpret_cast<const float4*>(yr + 4 * q);
+                y[4 * q] = f.x; y[4 * q + 1] = f.y; y[4 * q + 2] = f.z; y[4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) y[k] = (uint32_t)k < jb ? yr[k] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) c[j] = (uint32_t)j < ncb ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+#pragma unroll
+            for (int j = 0; j < ICS; ++j) z[k][j] = fmaf(y[k], c[j], z[k][j]);
+    }
+    // block sum of the 128 numbers: per column j a 32-value butterfly (lane k ends with the warp's z[k][j])
+#pragma unroll
+    for (int j = 0; j < ICS; ++j) {
+        float pcol[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) pcol[k] = z[k][j];
+#pragma unroll
+        for (int half = 16; half >= 1; half >>= 1) {
+            const bool upper = (lane & half) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float send = upper ? pcol[i] : pcol[i + half];
+                const float keep = upper ? pcol[i + half] : pcol[i];
+                pcol[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+            }
+        }
+        red[warp][lane * ICS + j] = pcol[0];
+    }
+    __syncthreads();
+    if (t < 32 * ICS) {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][t];
+        Zs[t / ICS][t % ICS] = v;
+    }
+    __syncthreads();
+    if (t < 32 * ICS) {     // W = T^T Z
+        const int i = t / ICS, j = t % ICS;
+        float v = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) v = fmaf(Ts[k][i], Zs[k][j], v);
+        Ws[i][j] = v;
+    }
+    __syncthreads();
+    float w[32][ICS];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) w[k][j] = Ws[k][j];
+    for (uint32_t r = t; r < mp; r += 256) {
+        float y[32];
+        const float* yr = Y + (size_t)r * ldy;
+        if (yvec) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 f = *reinterpret_cast<const float4*>(yr + 4 * q);
+                y[4 * q] = f.x; y[4 * q + 1] = f.y; y[4 * q + 2] = f.z; y[4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) y[k] = (uint32_t)k < jb ? yr[k] : 0.0f;
+        }
+        float d[ICS];
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) d[j] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+#pragma unroll
+            for (int j = 0; j < ICS; ++j) d[j] = fmaf(y[k], w[k][j], d[j]);
+#pragma unroll
+        for (int j = 0; j < ICS; ++j)
+            if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] -= d[j];
+    }
 }
+
+void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T, float* C, size_t ldc, uint32_t mp,
+                 uint32_t jb, uint32_t nc) {
+    if (nc == 0 || mp == 0) return;
+    inner_update_kernel<<<(nc + ICS - 1) / ICS, 256, 0, stream>>>(Y, ldy, T, C, ldc, mp, jb, nc);
+    cuda_check(cudaGetLastError(), "inner update launch");
+}
+
+unsigned grid_for(size_t count) { return (unsigned)std::min<size_t>((count + 255) / 256, 148 * 8); }
 
 } // namespace
 
@@ -589,7 +592,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const uint32_t ldw = (n + 3) & ~3u, ldy = (K + 3) & ~3u;
     const uint32_t npanels = (K + NB - 1) / NB;
     const uint32_t wide = std::max(n, qc);                       // the widest matrix a reflector is applied to
-    const uint32_t chunks = (m + RCH - 1) / RCH, ncp = (wide + 3) & ~3u;
+    const uint32_t ncp = (wide + 3) & ~3u;
 
     // workspace (floats), shared by the matrices of the batch, which are factored one after another
     const uint32_t naggs = (K + AG - 1) / AG;
@@ -600,7 +603,10 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_w = take((size_t)m * ldw), o_y = take((size_t)m * ldy), o_t = take((size_t)npanels * 1024);
     const size_t o_ta = take((size_t)naggs * AG * AG);
     const size_t o_qp = take((size_t)m * NB), o_rp = take(NB * NB), o_ui = take(NB * NB);
-    const size_t o_zp = take(std::max((size_t)chunks * 32 * ncp, (size_t)chunks_w * AG * ncp)), o_z = take((size_t)AG * ncp);
+    const size_t gram_floats = (size_t)((m + 127) / 128) * AG * AG;   // the Gram partials of an aggregate, 128 rows a chunk
+    const size_t o_zp = take(std::max({(size_t)chunks_w * AG * ncp, gram_floats}));
+    const size_t o_z = take((size_t)AG * ncp);
+    const size_t o_zp2 = take((size_t)chunks_w * AG * ncp), o_z2 = take((size_t)AG * ncp);   // the second stream's
     const size_t o_info = take(64);
     size_t tsqr_floats = 0;
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
@@ -611,7 +617,8 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     static const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree, for comparison
     float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
     float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
-    float *Zp = ws + o_zp, *Z = ws + o_z, *ts = ws + o_ts, *pf = ws + o_pf;
+    float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
+    static const bool look_ahead = std::getenv("QR_NO_LOOKAHEAD") == nullptr;
     MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
     static bool configured = false;
     if (!configured) {
@@ -634,36 +641,64 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // forward. Panels of 32 columns in aggregates of 128: a panel's reflector is applied at once
         // only to the columns left in its aggregate; the columns right of the aggregate get all of
         // its (up to) 128 reflectors in one rank-128 update.
+        //
+        // Look-ahead: the chain of panels runs on the context's high-priority stream `ps`, the large
+        // updates on the caller's stream `us`. After an aggregate's panels, `ps` itself updates only
+        // the next aggregate's columns, so that its panels can start; the columns beyond go to `us`
+        // and run beside those panels. Updates of one column range stay in order: before its own
+        // update `ps` waits for the previous update on `us`, which covered the same columns.
+        cudaStream_t ps = look_ahead && naggs > 1 ? ctx.aux : stream, us = stream;
+        const bool two = ps != us;
+        if (two) {
+            cuda_check(cudaEventRecord(ctx.ev_update[1], us), "cudaEventRecord");        // the working copy is ready
+            cuda_check(cudaStreamWaitEvent(ps, ctx.ev_update[1], 0), "cudaStreamWaitEvent");
+        }
         for (uint32_t ag = 0; ag < naggs; ++ag) {
             const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0, pans = (wa + NB - 1) / NB;
             for (uint32_t pp = 0; pp < pans; ++pp) {
                 const uint32_t pi = ag * (AG / NB) + pp, k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
                 if (!slow_panels && panel_fast_fits(mp, jb)) {
-                    panel_factor_fast(stream, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
+                    panel_factor_fast(ps, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
                                       T + (size_t)pi * 1024, pf);
                 } else {   // taller than the register-resident panel kernels take: the general tree
-                    tsqr_core(ctx, stream, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
+                    tsqr_core(ctx, ps, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
                     ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};
-                    reconstruct_kernel<<<1, 32, 0, stream>>>(rp);
+                    reconstruct_kernel<<<1, 32, 0, ps>>>(rp);
                     if (mp > jb)   // the rows below the top block: Qp U^-1
-                        launch_tsqr_apply(ctx, stream, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0,
+                        launch_tsqr_apply(ctx, ps, Qp + (size_t)jb * jb, 0, 0, Y + (size_t)(k0 + jb) * ldy + k0, 0, 0,
                                           ldy, Ui, true, 1, 1, mp - jb, mp - jb, jb);
                 }
                 if (pp)   // Y is read as one mp x wa matrix by the aggregate's products: zeros above the panel's top
                     cuda_check(cudaMemset2DAsync(Y + (size_t)j0 * ldy + k0, (size_t)ldy * sizeof(float), 0,
-                                                 jb * sizeof(float), k0 - j0, stream), "cudaMemset2DAsync");
+                                                 jb * sizeof(float), k0 - j0, ps), "cudaMemset2DAsync");
                 const uint32_t inside = j0 + wa - (k0 + jb);   // columns of the aggregate right of the panel
                 if (inside)
-                    apply_block_reflector(stream, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024, true,
-                                          W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside, Zp, Z);
+                    apply_inner(ps, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024,
+                                W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside);
             }
             const uint32_t right = n - (j0 + wa);
             if (right || qc)
-                build_aggregate_t(stream, Y + (size_t)j0 * ldy + j0, ldy, ma, wa, pans, T + (size_t)ag * (AG / NB) * 1024,
-                                  Ta + (size_t)ag * AG * AG, Zp);
-            if (right)
-                apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
-                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z);
+                build_aggregate_t(ps, Y + (size_t)j0 * ldy + j0, ldy, ma, wa, pans, T + (size_t)ag * (AG / NB) * 1024,
+                                  Ta + (size_t)ag * AG * AG, Zp, &info->bad);
+            if (right && !two) {
+                apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z, &info->bad);
+            } else if (right) {
+                const uint32_t next = std::min<uint32_t>(AG, right);
+                if (ag > 0) cuda_check(cudaStreamWaitEvent(ps, ctx.ev_update[(ag - 1) & 1], 0), "cudaStreamWaitEvent");
+                apply_aggregate(ps, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, next, Zp, Z, &info->bad);
+                cuda_check(cudaEventRecord(ctx.ev_panel[ag & 1], ps), "cudaEventRecord");
+                cuda_check(cudaStreamWaitEvent(us, ctx.ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
+                if (right > next)
+                    apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                    W + (size_t)j0 * ldw + j0 + wa + next, ldw, ma, wa, right - next, Zp2, Z2, &info->bad);
+                cuda_check(cudaEventRecord(ctx.ev_update[ag & 1], us), "cudaEventRecord");
+            }
+        }
+        if (two) {   // the caller's stream joins the panel stream
+            cuda_check(cudaEventRecord(ctx.ev_panel[0], ps), "cudaEventRecord");
+            cuda_check(cudaStreamWaitEvent(us, ctx.ev_panel[0], 0), "cudaStreamWaitEvent");
         }
         r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
         if (!qc) continue;
@@ -673,7 +708,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         for (uint32_t ag = naggs; ag-- > 0;) {
             const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0;
             apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, false,
-                            Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z);
+                            Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad);
         }
         nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);
     }

@@ -236,6 +236,30 @@ __global__ void __launch_bounds__(PT) panel_leaf_kernel(const LeafParams p) {
     for (int idx = t; idx < 1024; idx += PT) p.Tl[(size_t)blk * 1024 + idx] = s.T[idx >> 5][idx & 31];
 }
 
+// One row of the top Q's first 32 columns, B = [I; 0] - V M with M = T V1^T, to Bp.
+__device__ __forceinline__ void top_q_row(const float (&xr)[32], const int row, const float (*M4)[36], float* Bp,
+                                          uint32_t S) {
+    float b[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) b[c] = (row == c) ? 1.0f : 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) {
+        const float v = clean_v(xr[kk], row, kk);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 m4 = *reinterpret_cast<const float4*>(&M4[kk][4 * q]);
+            b[4 * q] = fmaf(-v, m4.x, b[4 * q]); b[4 * q + 1] = fmaf(-v, m4.y, b[4 * q + 1]);
+            b[4 * q + 2] = fmaf(-v, m4.z, b[4 * q + 2]); b[4 * q + 3] = fmaf(-v, m4.w, b[4 * q + 3]);
+        }
+    }
+    if ((uint32_t)row < S) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(Bp + (size_t)row * 32 + 4 * q) =
+                make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
+    }
+}
+
 struct TopParams {
     const float* Sl;        // [S][32] stacked R's
     uint32_t     S;         // rows of the stack (leaves * 32, at most 512)
@@ -248,17 +272,19 @@ struct TopParams {
     size_t       ldy;
     float*       t;         // [32][32] out: T of the panel
     uint32_t     jb, mp;
+    float*       Rt;        // [32][32] scratch: the R of the stack, from the top kernel to the finish kernel
 };
 
-__global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
+// The stack of R's factored; out: its R (Rt) and the rows of its Q's first 32 columns (Bp).
+template <int RPT>
+__global__ void __launch_bounds__(PT, 1) panel_top_kernel(const TopParams p) {
     __shared__ __align__(16) PanelSmem s;
-    __shared__ float V1[32][33], M[32][33], B0[32][33], X[32][33], V0[32][33], T0[32][33], Rm[32][33];
-    __shared__ __align__(16) float M4[32][36], Q[32][36];   // read as 16-byte words
-    __shared__ float sgn[32];
+    __shared__ float V1[32][33];
+    __shared__ __align__(16) float M4[32][36];   // read as 16-byte words
     const int t = threadIdx.x;
-    float x[2][32];
+    float x[RPT][32];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < RPT; ++k) {
         const uint32_t r = t + PT * k;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -267,17 +293,13 @@ __global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
             x[k][4 * q] = f.x; x[k][4 * q + 1] = f.y; x[k][4 * q + 2] = f.z; x[k][4 * q + 3] = f.w;
         }
     }
-    for (int idx = t; idx < 1024; idx += PT) {
-        V0[idx >> 5][idx & 31] = p.Vl[idx];
-        T0[idx >> 5][idx & 31] = p.Tl[idx];
-    }
-    factor_rows<2>(x, s);
+    factor_rows<RPT>(x, s);
     __syncthreads();
     build_t(s);
     if (t < 32) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-            Rm[t][c] = c >= t ? x[0][c] : 0.0f;
+            p.Rt[t * 32 + c] = c >= t ? x[0][c] : 0.0f;
             V1[t][c] = clean_v(x[0][c], t, c);
         }
     }
@@ -297,33 +319,24 @@ __global__ void __launch_bounds__(PT) panel_top_kernel(const TopParams p) {
     }
     __syncthreads();
     // a row of B per thread and pass; the rows wait in global memory (Bp) for U
-    auto b_row = [&](const float (&xr)[32], const int row) {
-        float b[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) b[c] = (row == c) ? 1.0f : 0.0f;
-#pragma unroll
-        for (int kk = 0; kk < 32; ++kk) {
-            const float v = clean_v(xr[kk], row, kk);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float4 m4 = *reinterpret_cast<const float4*>(&M4[kk][4 * q]);
-                b[4 * q] = fmaf(-v, m4.x, b[4 * q]); b[4 * q + 1] = fmaf(-v, m4.y, b[4 * q + 1]);
-                b[4 * q + 2] = fmaf(-v, m4.z, b[4 * q + 2]); b[4 * q + 3] = fmaf(-v, m4.w, b[4 * q + 3]);
-            }
-        }
-        if (row < 32) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) B0[row][c] = b[c];
-        }
-        if ((uint32_t)row < p.S) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(p.Bp + (size_t)row * 32 + 4 * q) =
-                    make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
-        }
-    };
-    b_row(x[0], t);
-    b_row(x[1], t + PT);
+    top_q_row(x[0], t, M4, p.Bp, p.S);
+    asm volatile("" ::: "memory");   // keeps the compiler from holding all of M4 in registers across the two rows
+    if (RPT > 1) top_q_row(x[RPT - 1], t + PT, M4, p.Bp, p.S);
+}
+
+// Householder reconstruction from the top's Q rows (Bp) and leaf 0's reflectors: the panel's T, R
+// and L1, and Bp <- Bp U^-1.
+__global__ void __launch_bounds__(PT) panel_finish_kernel(const TopParams p) {
+    __shared__ float M[32][33], B0[32][33], X[32][33], V0[32][33], T0[32][33], Rm[32][33];
+    __shared__ __align__(16) float Q[32][36];   // read as 16-byte words
+    __shared__ float sgn[32];
+    const int t = threadIdx.x;
+    for (int idx = t; idx < 1024; idx += PT) {
+        V0[idx >> 5][idx & 31] = p.Vl[idx];
+        T0[idx >> 5][idx & 31] = p.Tl[idx];
+        B0[idx >> 5][idx & 31] = p.Bp[idx];
+        Rm[idx >> 5][idx & 31] = p.Rt[idx];
+    }
     __syncthreads();
     // the panel's Q on its first 32 rows: Q1 = B0 - V0 (T0 (V0^T B0)), V0 and T0 leaf 0's
     mat32<true>(V0, B0, X);
@@ -466,7 +479,7 @@ __global__ void __launch_bounds__(PT) panel_apply_kernel(const ApplyParams p) {
     }
 }
 
-int rows_per_thread(uint32_t mp) { return mp <= 4096 ? 1 : mp <= 8192 ? 2 : 4; }
+int rows_per_thread(uint32_t mp) { return mp <= 2048 ? 1 : mp <= 8192 ? 2 : 4; }
 
 } // namespace
 
@@ -474,7 +487,7 @@ bool panel_fast_fits(uint32_t mp, uint32_t jb) { return jb >= 1 && jb <= 32 && m
 
 size_t panel_fast_workspace_floats(uint32_t mp) {
     const uint32_t lr = PT * rows_per_thread(mp), leaves = (mp + lr - 1) / lr;
-    return (size_t)leaves * lr * 32 + (size_t)leaves * 1024 * 3 + 256;
+    return (size_t)leaves * lr * 32 + (size_t)leaves * 1024 * 3 + 1024 + 256;
 }
 
 // The panel at `panel` (mp x jb, row stride ldw, inside the working copy) to compact-WY form: its R
@@ -491,8 +504,11 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     if (rpt == 1) panel_leaf_kernel<1><<<leaves, PT, 0, stream>>>(lp);
     else if (rpt == 2) panel_leaf_kernel<2><<<leaves, PT, 0, stream>>>(lp);
     else panel_leaf_kernel<4><<<leaves, PT, 0, stream>>>(lp);
-    TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp};
-    panel_top_kernel<<<1, PT, 0, stream>>>(tp);
+    float* Rt = Bp + (size_t)leaves * 1024;
+    TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp, Rt};
+    if (leaves * 32 <= PT) panel_top_kernel<1><<<1, PT, 0, stream>>>(tp);
+    else panel_top_kernel<2><<<1, PT, 0, stream>>>(tp);
+    panel_finish_kernel<<<1, PT, 0, stream>>>(tp);
     ApplyParams ap{Vl, Tl, Bp, y, ldy, mp, jb, lr};
     if (rpt == 1) panel_apply_kernel<1><<<leaves, PT, 0, stream>>>(ap);
     else if (rpt == 2) panel_apply_kernel<2><<<leaves, PT, 0, stream>>>(ap);

@@ -58,7 +58,12 @@ DeviceContext& context(int device) {
         cuda_check(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking), "cudaStreamCreate");
+        int least = 0, greatest = 0;   // the panel chain of the blocked QR goes ahead of the bulk updates
+        cuda_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
+        cuda_check(cudaStreamCreateWithPriority(&c->aux, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
         for (int i = 0; i < 2; ++i) {
+            cuda_check(cudaEventCreateWithFlags(&c->ev_panel[i], cudaEventDisableTiming), "cudaEventCreate");
+            cuda_check(cudaEventCreateWithFlags(&c->ev_update[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming), "cudaEventCreate");

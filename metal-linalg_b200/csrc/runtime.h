@@ -34,6 +34,9 @@ struct DeviceContext {
     cudaStream_t   copy_in = nullptr, copy_out = nullptr, compute = nullptr;   // host-pointer staging
     cudaEvent_t    ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr},
                    ev_out[2] = {nullptr, nullptr};
+    // the blocked QR's second stream (trailing updates beside the next panels) and its events
+    cudaStream_t   aux = nullptr;
+    cudaEvent_t    ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr};
 
     // At least `bytes` of device scratch for work on `stream`, 256-byte aligned,
     // kept for later calls. Growing it waits for the GPU (cudaFree does).
