@@ -39,8 +39,9 @@ ROWS = COLS = 32
 BATCH = 262144                       # per GPU
 BYTES_PER_MATRIX = 3 * ROWS * COLS * 4   # A read, Q and R written
 # DRAM bytes per matrix of the small kernel from the ncu capture summarised in
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over one launch / matrices); None until captured.
-MEASURED_TRAFFIC_PER_MATRIX = None
+# profiles/qr_small_32x32_batch65536.md: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on
+# 65 536 matrices / 65 536 = (268.51 MB + 477.52 MB) / 65 536. Traffic grows in proportion to the batch.
+MEASURED_TRAFFIC_PER_MATRIX = 11383
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -349,6 +350,8 @@ def other_configs(torch, mlt, _lib, workloads, args):
     add("c4_65536x64_tall", torch.randn(64, 65536, 64, generator=g, device="cuda"), "reduced", False)
     add("c5a_4096x4096", torch.rand(1, 4096, 4096, generator=g, device="cuda") * 2 - 1, "reduced", False,
         steps=min(args.steps, 5))
+    add("c5b_8192x8192 (one of the eight matrices: one per GPU)",
+        torch.rand(1, 8192, 8192, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=2)
     return out
 
 

@@ -355,8 +355,24 @@ __global__ void __launch_bounds__(256) yz_wide_kernel(const float* __restrict__ 
 // T of an aggregate (128 x 128, zero padded) from its panels' T's and the Gram matrix of its Y:
 // T(0:c, c:c+32) = -T(0:c, 0:c) (Y(:, 0:c)^T Y_q) T_q for each panel q after the first
 // (the reference: bd_merge_t, shaders/Svd_Bidiag.metal:1131-1164). One block; dynamic shared memory.
+// The chunks' partial Gram matrices added up into the first one, an entry per thread.
+__global__ void gram_sum_kernel(float* zp, uint32_t chunks, uint32_t count) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
+    uint32_t ch = 0;
+    for (; ch + 4 <= chunks; ch += 4) {
+        g0 += zp[(size_t)ch * count + i];
+        g1 += zp[(size_t)(ch + 1) * count + i];
+        g2 += zp[(size_t)(ch + 2) * count + i];
+        g3 += zp[(size_t)(ch + 3) * count + i];
+    }
+    for (; ch < chunks; ++ch) g0 += zp[(size_t)ch * count + i];
+    zp[i] = (g0 + g1) + (g2 + g3);
+}
+
 struct MergeParams {
-    const float* gram;      // partial Gram matrices [chunks][128][gld] (null when there is one panel)
+    const float* gram;      // the Gram matrix [128][gld] (null when there is one panel)
     uint32_t     chunks, gld;
     const float* tp;        // the panels' T's, [panels][32][32]
     uint32_t     panels;
@@ -375,23 +391,8 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
         float v = 0.0f;
         if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) v = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
         Ta[i][j] = v;
-        // the Gram matrix: the chunks' partial sums added up, consecutive threads on consecutive columns
-        float g = 0.0f;
-        if (p.gram && i < width && j < width && (j >> 5) > (i >> 5) && (uint32_t)j < p.gld) {
-            const float* src = p.gram + (size_t)i * p.gld + j;
-            const size_t stride = (size_t)AG * p.gld;
-            uint32_t ch = 0;
-            float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
-            for (; ch + 4 <= p.chunks; ch += 4) {
-                g0 += src[(size_t)ch * stride];
-                g1 += src[(size_t)(ch + 1) * stride];
-                g2 += src[(size_t)(ch + 2) * stride];
-                g3 += src[(size_t)(ch + 3) * stride];
-            }
-            for (; ch < p.chunks; ++ch) g0 += src[(size_t)ch * stride];
-            g = (g0 + g1) + (g2 + g3);
-        }
-        G[i][j] = g;
+        // the Gram matrix, already summed over the chunks (gram_sum_kernel)
+        G[i][j] = (p.gram && i < width && j < width && (uint32_t)j < p.gld) ? p.gram[(size_t)i * p.gld + j] : 0.0f;
     }
     __syncthreads();
     for (uint32_t q = 1; q < p.panels; ++q) {
@@ -453,6 +454,7 @@ void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t
         const uint32_t chunks = (ma + rows - 1) / rows, gld = (wa + 3) & ~3u;
         if (use_tensor_cores()) launch_tc_ytc(stream, Y, ldy, Y, ldy, ma, wa, wa, zp, gld, rows, error);
         else ytc_wide_kernel<<<dim3(1, chunks), 256, 0, stream>>>(Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
+        gram_sum_kernel<<<(AG * gld + 255) / 256, 256, 0, stream>>>(zp, chunks, AG * gld);
         mp.gram = zp; mp.chunks = chunks; mp.gld = gld;
     }
     merge_t_kernel<<<1, 256, kMergeSmem, stream>>>(mp);
