@@ -419,11 +419,8 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
 // The two large products run on the tensor cores (3xTF32, tc_gemm.cu) unless QR_TENSOR=0 asks for
 // the FP32 FMA kernels above, which stay as the fallback.
 bool use_tensor_cores() {
-    static const bool on = [] {
-        const char* e = std::getenv("QR_TENSOR");
-        return !(e && e[0] == '0');
-    }();
-    return on;
+    const char* e = std::getenv("QR_TENSOR");
+    return !(e && e[0] == '0');
 }
 
 constexpr size_t kReduceWideSmem = (128 * 132 + 128 * 36) * sizeof(float);
@@ -616,11 +613,11 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
             tsqr_floats = std::max(tsqr_floats, tsqr_workspace_floats(ctx, m - k0, std::min<uint32_t>(NB, K - k0), 1, true));
     const size_t o_ts = take(tsqr_floats);
     const size_t o_pf = take(panel_fast_workspace_floats(std::min<uint32_t>(m, 16384)));
-    static const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree, for comparison
+    const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree for every panel, for comparison
     float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
     float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
     float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
-    static const bool look_ahead = std::getenv("QR_NO_LOOKAHEAD") == nullptr;
+    const bool look_ahead = std::getenv("QR_NO_LOOKAHEAD") == nullptr;
     MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
     static bool configured = false;
     if (!configured) {

@@ -156,6 +156,34 @@ def test_blocked_kernel_shapes(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
+@pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1"])
+def test_blocked_fallback_paths(switch):
+    """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
+    the tensor cores, one stream instead of look-ahead, the general tree for every panel."""
+    rng = np.random.default_rng(16)
+    a = rng.standard_normal((1, 900, 700)).astype(np.float32)
+    q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
+    name, value = switch.split("=")
+    os.environ[name] = value
+    try:
+        q1, r1 = gpu_qr(a, "reduced", kernel="blocked")
+    finally:
+        os.environ.pop(name, None)
+    check(a, q1, r1, "reduced")
+    assert harness.r_parity(r1, r0) <= 1e-4
+    _, r_ref = harness.oracle_qr(a)
+    assert harness.r_parity(r1, r_ref) <= 1e-4
+
+
+def test_blocked_panels_taller_than_the_register_kernels():
+    """More than 16384 rows: every panel goes through the general tree and reconstruct_kernel."""
+    rng = np.random.default_rng(17)
+    a = rng.standard_normal((1, 20000, 70)).astype(np.float32)
+    q, r = gpu_qr(a, "reduced", kernel="blocked")
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
 def test_blocked_special_matrices():
     m, n = 700, 500
     eye = np.eye(m, n, dtype=np.float32)
