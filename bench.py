@@ -364,6 +364,7 @@ PROFILE_CASES = {
     "mid256": (592, 256, 256, "reduced"),
     "tsqr": (8, 65536, 64, "reduced"),
     "blocked4096": (1, 4096, 4096, "reduced"),
+    "blocked8192": (1, 8192, 8192, "reduced"),
 }
 
 

@@ -36,6 +36,7 @@ constexpr int LBO   = 16 * 128 + 16;       // bytes between 16-byte columns of K
 constexpr int TILE  = (KT / 4) * LBO;      // bytes of one 128 x 32 operand tile
 constexpr int STAGE = 4 * TILE;            // A_hi, A_lo, B_hi, B_lo
 constexpr uint32_t kSpinLimit = 1u << 20;
+constexpr int CLD   = 132;                 // leading dimension of the output tile in shared memory
 
 struct TcParams {
     const float* a;        // operand A source
@@ -105,15 +106,21 @@ __device__ __forceinline__ void put_mn_contiguous(const float (&v)[16], char* hi
 
 // Tiles whose K index runs along contiguous memory (element (mn, k) at src[mn * ld + k]).
 __device__ __forceinline__ void fetch_k_contiguous(float (&v)[16], const float* src, size_t ld, uint32_t mn_valid,
-                                                   uint32_t k_valid) {
+                                                   uint32_t k_valid, bool aligned) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         const int idx = threadIdx.x + TCT * e;
         const int kq = idx & 7, mn = idx >> 3;
+        if (aligned && k_valid == KT) {      // whole 16-byte words
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if ((uint32_t)mn < mn_valid) f = *reinterpret_cast<const float4*>(src + (size_t)mn * ld + 4 * kq);
+            v[4 * e] = f.x; v[4 * e + 1] = f.y; v[4 * e + 2] = f.z; v[4 * e + 3] = f.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t k = 4 * kq + i;
-            v[4 * e + i] = ((uint32_t)mn < mn_valid && k < k_valid) ? src[(size_t)mn * ld + k] : 0.0f;
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t k = 4 * kq + i;
+                v[4 * e + i] = ((uint32_t)mn < mn_valid && k < k_valid) ? src[(size_t)mn * ld + k] : 0.0f;
+            }
         }
     }
 }
@@ -166,6 +173,27 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
     }
     const uint32_t k_len = k_end - k_begin, tiles = (k_len + KT - 1) / KT;
 
+    // The block's 128 x 128 tile of the output goes through shared memory, so that global memory
+    // sees whole rows: for C -= Y Z the tile of C is fetched now (cp.async, under the products).
+    float (*Ct)[CLD] = reinterpret_cast<float (*)[CLD]>(smem + 2 * STAGE);
+    float* out_tile = p.out + (size_t)blockIdx.y * 128 * p.ldo + j0;
+    const uint32_t out_rows = p.mode == 0 ? 128u : min(m_valid, 128u);
+    const bool out_vec = (p.ldo & 3) == 0 && (reinterpret_cast<size_t>(out_tile) & 15) == 0 && n_valid >= 128;
+    if (p.mode == 1) {
+        for (int idx = threadIdx.x; idx < 128 * 32; idx += TCT) {
+            const uint32_t r = idx >> 5, q = idx & 31;
+            if (r >= out_rows) continue;
+            const float* src = out_tile + (size_t)r * p.ldo + 4 * q;
+            if (out_vec) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(&Ct[r][4 * q])), "l"(src) : "memory");
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) Ct[r][4 * q + e] = 4 * q + e < n_valid ? src[e] : 0.0f;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bars[s])));
@@ -180,11 +208,12 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = tmem_base_slot;
 
+    const bool a_aligned = (p.lda & 3) == 0 && (reinterpret_cast<size_t>(a_src) & 15) == 0;
     float ra[16], rb[16];
     auto fetch = [&](uint32_t kt) {
         const uint32_t k0 = kt * KT, kv = min(k_len - k0, (uint32_t)KT);
         if (p.mode == 0) fetch_mn_contiguous(ra, a_src + (size_t)k0 * p.lda, p.lda, m_valid, kv);
-        else             fetch_k_contiguous(ra, a_src + k0, p.lda, m_valid, kv);
+        else             fetch_k_contiguous(ra, a_src + k0, p.lda, m_valid, kv, a_aligned);
         fetch_mn_contiguous(rb, b_src + (size_t)k0 * p.ldb, p.ldb, n_valid, kv);
     };
     if (tiles > 0) fetch(0);
@@ -229,6 +258,7 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
         const uint32_t last = tiles - 1;
         if (!wait_barrier(smem_u32(&bars[last & 1]), (last >> 1) & 1)) failed = 1;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool ok = !failed;
@@ -252,25 +282,35 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
                            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                          : "r"(taddr) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (p.mode == 0) {          // Zp[chunk][i = row][j0 + c]
-                float* dst = p.out + ((size_t)blockIdx.y * 128 + row) * p.ldo + j0 + c0;
+            if (p.mode == 0) {          // the chunk's partial sums
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (c0 + c < n_valid) dst[c] = __uint_as_float(v[c]);
-            } else if (row < m_valid) { // C[r0 + row][j0 + c] -= acc
-                float* dst = p.out + ((size_t)blockIdx.y * 128 + row) * p.ldo + j0 + c0;
+                for (int c = 0; c < 32; ++c) Ct[row][c0 + c] = __uint_as_float(v[c]);
+            } else {                    // C's tile minus the product
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (c0 + c < n_valid) dst[c] -= __uint_as_float(v[c]);
+                for (int c = 0; c < 32; ++c) Ct[row][c0 + c] -= __uint_as_float(v[c]);
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (ok && tiles > 0) {              // rows of the tile to global memory, a warp a row, 16 bytes a lane
+        for (uint32_t r = warp; r < out_rows; r += TCT / 32) {
+            float* dst = out_tile + (size_t)r * p.ldo + 4 * lane;
+            const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
+            if (out_vec) {
+                *reinterpret_cast<float4*>(dst) = f;
+            } else {
+                const float e[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (4 * lane + i < n_valid) dst[i] = e[i];
+            }
+        }
+    }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" :: "r"(tmem_d) : "memory");
 }
 
-constexpr size_t kTcSmem = 2 * STAGE + 1024;
+constexpr size_t kTcSmem = 2 * STAGE + 128 * CLD * sizeof(float) + 1024;
 
 void configure() {
     static bool done = false;
