@@ -30,7 +30,7 @@ namespace mlb {
 namespace {
 
 constexpr int TCT   = 256;                 // threads
-constexpr int KT    = 32;                  // K elements per stage
+constexpr int KT    = 16;                  // K elements per stage
 constexpr int SBO   = 128;                 // bytes between 8-row groups
 constexpr int LBO   = 16 * 128 + 16;       // bytes between 16-byte columns of K (16 row groups, padded one word)
 constexpr int TILE  = (KT / 4) * LBO;      // bytes of one 128 x 32 operand tile
@@ -84,11 +84,12 @@ __device__ __forceinline__ void put_word(char* hi_tile, char* lo_tile, int r, in
 //
 // Tiles whose MN index runs along contiguous memory (element (mn, k) at src[k * ld + mn]): lanes
 // along mn (coalesced), four k's a thread and word.
-__device__ __forceinline__ void fetch_mn_contiguous(float (&v)[16], const float* src, size_t ld, uint32_t mn_valid,
+constexpr int WPT = KT / 8;                // 16-byte words per thread and tile
+__device__ __forceinline__ void fetch_mn_contiguous(float (&v)[4 * WPT], const float* src, size_t ld, uint32_t mn_valid,
                                                     uint32_t k_valid) {
     const int mn = threadIdx.x & 127;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < WPT; ++e) {
         const int kq = (threadIdx.x >> 7) + 2 * e;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -97,20 +98,20 @@ __device__ __forceinline__ void fetch_mn_contiguous(float (&v)[16], const float*
         }
     }
 }
-__device__ __forceinline__ void put_mn_contiguous(const float (&v)[16], char* hi_tile, char* lo_tile) {
+__device__ __forceinline__ void put_mn_contiguous(const float (&v)[4 * WPT], char* hi_tile, char* lo_tile) {
     const int mn = threadIdx.x & 127;
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
+    for (int e = 0; e < WPT; ++e)
         put_word(hi_tile, lo_tile, mn, (threadIdx.x >> 7) + 2 * e, v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
 }
 
 // Tiles whose K index runs along contiguous memory (element (mn, k) at src[mn * ld + k]).
-__device__ __forceinline__ void fetch_k_contiguous(float (&v)[16], const float* src, size_t ld, uint32_t mn_valid,
+__device__ __forceinline__ void fetch_k_contiguous(float (&v)[4 * WPT], const float* src, size_t ld, uint32_t mn_valid,
                                                    uint32_t k_valid, bool aligned) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < WPT; ++e) {
         const int idx = threadIdx.x + TCT * e;
-        const int kq = idx & 7, mn = idx >> 3;
+        const int kq = idx & (KT / 4 - 1), mn = idx / (KT / 4);
         if (aligned && k_valid == KT) {      // whole 16-byte words
             float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
             if ((uint32_t)mn < mn_valid) f = *reinterpret_cast<const float4*>(src + (size_t)mn * ld + 4 * kq);
@@ -124,11 +125,11 @@ __device__ __forceinline__ void fetch_k_contiguous(float (&v)[16], const float* 
         }
     }
 }
-__device__ __forceinline__ void put_k_contiguous(const float (&v)[16], char* hi_tile, char* lo_tile) {
+__device__ __forceinline__ void put_k_contiguous(const float (&v)[4 * WPT], char* hi_tile, char* lo_tile) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < WPT; ++e) {
         const int idx = threadIdx.x + TCT * e;
-        put_word(hi_tile, lo_tile, idx >> 3, idx & 7, v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+        put_word(hi_tile, lo_tile, idx / (KT / 4), idx & (KT / 4 - 1), v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
     }
 }
 
@@ -143,7 +144,7 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-__global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
     extern __shared__ __align__(1024) char smem[];
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ uint32_t tmem_base_slot;
@@ -174,25 +175,12 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
     const uint32_t k_len = k_end - k_begin, tiles = (k_len + KT - 1) / KT;
 
     // The block's 128 x 128 tile of the output goes through shared memory, so that global memory
-    // sees whole rows: for C -= Y Z the tile of C is fetched now (cp.async, under the products).
-    float (*Ct)[CLD] = reinterpret_cast<float (*)[CLD]>(smem + 2 * STAGE);
+    // sees whole rows. It takes the stages' place once the products are done (two blocks fit a
+    // multiprocessor that way, and one block's waits hide behind the other's work).
+    float (*Ct)[CLD] = reinterpret_cast<float (*)[CLD]>(smem);
     float* out_tile = p.out + (size_t)blockIdx.y * 128 * p.ldo + j0;
     const uint32_t out_rows = p.mode == 0 ? 128u : min(m_valid, 128u);
     const bool out_vec = (p.ldo & 3) == 0 && (reinterpret_cast<size_t>(out_tile) & 15) == 0 && n_valid >= 128;
-    if (p.mode == 1) {
-        for (int idx = threadIdx.x; idx < 128 * 32; idx += TCT) {
-            const uint32_t r = idx >> 5, q = idx & 31;
-            if (r >= out_rows) continue;
-            const float* src = out_tile + (size_t)r * p.ldo + 4 * q;
-            if (out_vec) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(&Ct[r][4 * q])), "l"(src) : "memory");
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) Ct[r][4 * q + e] = 4 * q + e < n_valid ? src[e] : 0.0f;
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s)
@@ -209,7 +197,7 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
     const uint32_t tmem_d = tmem_base_slot;
 
     const bool a_aligned = (p.lda & 3) == 0 && (reinterpret_cast<size_t>(a_src) & 15) == 0;
-    float ra[16], rb[16];
+    float ra[4 * WPT], rb[4 * WPT];
     auto fetch = [&](uint32_t kt) {
         const uint32_t k0 = kt * KT, kv = min(k_len - k0, (uint32_t)KT);
         if (p.mode == 0) fetch_mn_contiguous(ra, a_src + (size_t)k0 * p.lda, p.lda, m_valid, kv);
@@ -258,11 +246,26 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
         const uint32_t last = tiles - 1;
         if (!wait_barrier(smem_u32(&bars[last & 1]), (last >> 1) & 1)) failed = 1;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool ok = !failed;
     if (!ok && threadIdx.x == 0) atomicExch(p.error, 1u);
+    if (ok && tiles > 0 && p.mode == 1) {   // C's tile, a warp a row
+        for (uint32_t r = warp; r < out_rows; r += TCT / 32) {
+            const float* src = out_tile + (size_t)r * p.ldo + 4 * lane;
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (out_vec) {
+                f = *reinterpret_cast<const float4*>(src);
+            } else {
+                if (4 * lane + 0 < n_valid) f.x = src[0];
+                if (4 * lane + 1 < n_valid) f.y = src[1];
+                if (4 * lane + 2 < n_valid) f.z = src[2];
+                if (4 * lane + 3 < n_valid) f.w = src[3];
+            }
+            *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = f;
+        }
+        __syncthreads();
+    }
 
     if (ok && tiles > 0) {
         // warp w reads lanes 32 (w % 4) .. + 31 (its rows of the tile), columns 64 (w / 4) .. + 63
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(TCT, 1) tc_gemm_kernel(const TcParams p) {
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" :: "r"(tmem_d) : "memory");
 }
 
-constexpr size_t kTcSmem = 2 * STAGE + 128 * CLD * sizeof(float) + 1024;
+constexpr size_t kTcSmem = (2 * STAGE > 128 * CLD * (int)sizeof(float) ? 2 * STAGE : 128 * CLD * (int)sizeof(float)) + 1024;
 
 void configure() {
     static bool done = false;
