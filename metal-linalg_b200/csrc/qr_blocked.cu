@@ -13,7 +13,7 @@
 //              kernels of qr_panel.cu up to 16384 rows, the general tree
 //              (tsqr_core + reconstruct_kernel here) beyond;
 //   inside     the panel's reflector applied to the columns left in its aggregate
-//              (at most 96) by inner_update_kernel, one launch;
+//              (at most 96) by inner_z_kernel + inner_apply_kernel;
 //   aggregate  T of the aggregate's 128 reflectors from its panels' T's and the
 //              Gram matrix Y^T Y (merge_t_kernel; the reference: bd_merge_t), then
 //              the rank-128 update of everything right of it, C -= Y (T^T (Y^T C)):
@@ -461,43 +461,44 @@ void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t
 // ---------------------------------------------------------------------------
 // A panel's own update: its reflector applied to the few columns left in its aggregate
 // ---------------------------------------------------------------------------
-// C (mp x nc, nc <= 96) <- (I - Y T^T Y^T) C in ONE launch: a block owns four columns of C over all
-// the rows, so nothing crosses blocks. Pass 1: a thread takes rows t, t + 256, ... and accumulates
-// its part of Z = Y^T C (32 x 4) in registers; the parts are summed over the block (shuffles, then
-// shared memory). W = T^T Z by one warp. Pass 2: the rows again, C -= Y W. Y (mp x 32) is re-read
-// by every block from L2.
-constexpr int ICS = 4;      // columns per block
+// C (mp x nc, nc <= 96) <- (I - Y T^T Y^T) C in two launches over a grid of (4 columns) x (1024
+// rows). inner_z_kernel: a block's part of Z = Y^T C (32 x 4), a thread taking four rows in
+// registers, summed over the block (shuffles, then shared memory), to zpart[row chunk].
+// inner_apply_kernel: every block sums the row chunks' parts for its columns (a fixed order, so
+// the result does not depend on scheduling), W = T^T Z, and C -= Y W on its rows.
+constexpr int ICS = 4;          // columns per block
+constexpr int IRB = 1024;       // rows per block
 
-__global__ void __launch_bounds__(256) inner_update_kernel(const float* __restrict__ Y, size_t ldy,
-                                                           const float* __restrict__ T, float* C, size_t ldc,
-                                                           uint32_t mp, uint32_t jb, uint32_t nc) {
+__device__ __forceinline__ void inner_load_y(float (&y)[32], const float* yr, bool yvec, uint32_t jb) {
+    if (yvec) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(yr + 4 * q);
+            y[4 * q] = f.x; y[4 * q + 1] = f.y; y[4 * q + 2] = f.z; y[4 * q + 3] = f.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) y[k] = (uint32_t)k < jb ? yr[k] : 0.0f;
+    }
+}
+
+// zpart [row chunks][32][ncp]
+__global__ void __launch_bounds__(256) inner_z_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ C,
+                                                      size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* zpart,
+                                                      uint32_t ncp) {
     __shared__ float red[8][32 * ICS];
-    __shared__ float Zs[32][ICS], Ws[32][ICS];
-    __shared__ float Ts[32][33];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const uint32_t c0 = blockIdx.x * ICS;
-    const uint32_t ncb = min((uint32_t)ICS, nc - c0);
-    for (int idx = t; idx < 1024; idx += 256) Ts[idx >> 5][idx & 31] = T[idx];
+    const uint32_t c0 = blockIdx.x * ICS, ncb = min((uint32_t)ICS, nc - c0);
+    const uint32_t r_begin = blockIdx.y * IRB, r_end = min(mp, r_begin + IRB);
     const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
-
     float z[32][ICS];
 #pragma unroll
     for (int k = 0; k < 32; ++k)
 #pragma unroll
         for (int j = 0; j < ICS; ++j) z[k][j] = 0.0f;
-    for (uint32_t r = t; r < mp; r += 256) {
+    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
         float y[32], c[ICS];
-        const float* yr = Y + (size_t)r * ldy;
-        if (yvec) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float4 f = *reinterpret_cast<const float4*>(yr + 4 * q);
-                y[4 * q] = f.x; y[4 * q + 1] = f.y; y[4 * q + 2] = f.z; y[4 * q + 3] = f.w;
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) y[k] = (uint32_t)k < jb ? yr[k] : 0.0f;
-        }
+        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
 #pragma unroll
         for (int j = 0; j < ICS; ++j) c[j] = (uint32_t)j < ncb ? C[(size_t)r * ldc + c0 + j] : 0.0f;
 #pragma unroll
@@ -528,7 +529,28 @@ __global__ void __launch_bounds__(256) inner_update_kernel(const float* __restri
         float v = 0.0f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) v += red[w][t];
-        Zs[t / ICS][t % ICS] = v;
+        const uint32_t k = t / ICS, j = t % ICS;
+        if (j < ncb) zpart[((size_t)blockIdx.y * 32 + k) * ncp + c0 + j] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) inner_apply_kernel(const float* __restrict__ Y, size_t ldy,
+                                                          const float* __restrict__ T, float* C, size_t ldc, uint32_t mp,
+                                                          uint32_t jb, uint32_t nc, const float* __restrict__ zpart,
+                                                          uint32_t ncp, uint32_t chunks) {
+    __shared__ float Zs[32][ICS], Ws[32][ICS];
+    __shared__ float Ts[32][33];
+    const int t = threadIdx.x;
+    const uint32_t c0 = blockIdx.x * ICS, ncb = min((uint32_t)ICS, nc - c0);
+    const uint32_t r_begin = blockIdx.y * IRB, r_end = min(mp, r_begin + IRB);
+    const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
+    for (int idx = t; idx < 1024; idx += 256) Ts[idx >> 5][idx & 31] = T[idx];
+    if (t < 32 * ICS) {
+        const uint32_t k = t / ICS, j = t % ICS;
+        float v = 0.0f;
+        if (j < ncb)
+            for (uint32_t ch = 0; ch < chunks; ++ch) v += zpart[((size_t)ch * 32 + k) * ncp + c0 + j];
+        Zs[k][j] = v;
     }
     __syncthreads();
     if (t < 32 * ICS) {     // W = T^T Z
@@ -544,19 +566,9 @@ __global__ void __launch_bounds__(256) inner_update_kernel(const float* __restri
     for (int k = 0; k < 32; ++k)
 #pragma unroll
         for (int j = 0; j < ICS; ++j) w[k][j] = Ws[k][j];
-    for (uint32_t r = t; r < mp; r += 256) {
+    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
         float y[32];
-        const float* yr = Y + (size_t)r * ldy;
-        if (yvec) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float4 f = *reinterpret_cast<const float4*>(yr + 4 * q);
-                y[4 * q] = f.x; y[4 * q + 1] = f.y; y[4 * q + 2] = f.z; y[4 * q + 3] = f.w;
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) y[k] = (uint32_t)k < jb ? yr[k] : 0.0f;
-        }
+        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
         float d[ICS];
 #pragma unroll
         for (int j = 0; j < ICS; ++j) d[j] = 0.0f;
@@ -570,10 +582,14 @@ __global__ void __launch_bounds__(256) inner_update_kernel(const float* __restri
     }
 }
 
+// zpart: scratch of at least ceil(mp / 1024) * 32 * ((nc + 3) & ~3) floats
 void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T, float* C, size_t ldc, uint32_t mp,
-                 uint32_t jb, uint32_t nc) {
+                 uint32_t jb, uint32_t nc, float* zpart) {
     if (nc == 0 || mp == 0) return;
-    inner_update_kernel<<<(nc + ICS - 1) / ICS, 256, 0, stream>>>(Y, ldy, T, C, ldc, mp, jb, nc);
+    const uint32_t chunks = (mp + IRB - 1) / IRB, ncp = (nc + 3) & ~3u;
+    const dim3 grid((nc + ICS - 1) / ICS, chunks);
+    inner_z_kernel<<<grid, 256, 0, stream>>>(Y, ldy, C, ldc, mp, jb, nc, zpart, ncp);
+    inner_apply_kernel<<<grid, 256, 0, stream>>>(Y, ldy, T, C, ldc, mp, jb, nc, zpart, ncp, chunks);
     cuda_check(cudaGetLastError(), "inner update launch");
 }
 
@@ -673,7 +689,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                 const uint32_t inside = j0 + wa - (k0 + jb);   // columns of the aggregate right of the panel
                 if (inside)
                     apply_inner(ps, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024,
-                                W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside);
+                                W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside, Zp);
             }
             const uint32_t right = n - (j0 + wa);
             if (right || qc)
