@@ -347,28 +347,32 @@ __global__ void __launch_bounds__(PT) panel_finish_kernel(const TopParams p) {
     __syncthreads();
     for (int idx = t; idx < 1024; idx += PT) Q[idx >> 5][idx & 31] = B0[idx >> 5][idx & 31] - X[idx >> 5][idx & 31];
     __syncthreads();
-    // LU of Q1 - S with S = -sgn(pivot) chosen on the way (every pivot at least 1 in magnitude)
+    // LU of Q1 - S with S = -sgn(pivot) chosen on the way (every pivot at least 1 in magnitude): one
+    // warp, a row per lane in registers, the pivot row handed round by shuffles
     if (t < 32) {
         const int i = t;
+        float q[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) q[c] = Q[i][c];
+#pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const float d = Q[j][j];
+            const float d = __shfl_sync(kFull, q[j], j);
             const float sg = d >= 0.0f ? -1.0f : 1.0f;
             const float piv = d - sg;
-            __syncwarp();
             if (i == j) {
-                Q[j][j] = piv;
+                q[j] = piv;
                 sgn[j] = sg;
             }
-            float l = 0.0f;
-            if (i > j) {
-                l = Q[i][j] / piv;
-                Q[i][j] = l;
+            const float l = i > j ? newton_div(q[j], piv) : 0.0f;
+            if (i > j) q[j] = l;
+#pragma unroll
+            for (int c = j + 1; c < 32; ++c) {
+                const float pc = __shfl_sync(kFull, q[c], j);
+                q[c] = fmaf(-l, pc, q[c]);      // l = 0 in the rows above: unchanged
             }
-            __syncwarp();
-            if (i > j)
-                for (int c = j + 1; c < 32; ++c) Q[i][c] = fmaf(-l, Q[j][c], Q[i][c]);
-            __syncwarp();
         }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) Q[i][c] = q[c];
     }
     __syncthreads();
     // B' = B U^-1, a row per thread and pass: x U = b, eliminating with one row of U at a time
