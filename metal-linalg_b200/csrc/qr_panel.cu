@@ -38,10 +38,9 @@ constexpr int PT = 256;     // threads per block
 constexpr unsigned kFull = 0xffffffffu;
 
 struct PanelSmem {
-    float red[PT / 32][32];   // each warp's column sums
-    float prow[32];           // the pivot row, in rotated column order
-    float wv[2][32];          // per rotated column the update coefficient (0 where there is nothing to update)
-    float scal[2][4];         // tau, 1/(alpha - beta), beta
+    float red[2][PT / 32][32];   // each warp's column sums, by step parity
+    float prow[2][32];           // the pivot row, in rotated column order, by step parity
+    float wv[PT / 32][32];       // per warp: per rotated column the update coefficient (0 where nothing is to update)
     float taus[32];
     float G[32][33];          // G[k][j] = v_k^T v_j for k < j
     float T[32][33];
@@ -104,38 +103,35 @@ __device__ __forceinline__ void factor_rows(float (&x)[RPT][32], PanelSmem& s) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) p[c] = fmaf(v, x[k][c], p[c]);
         }
+        const int buf = j & 1;
         if (t == j) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) s.prow[c] = x[0][c];
+            for (int c = 0; c < 32; ++c) s.prow[buf][c] = x[0][c];
         }
-        s.red[warp][lane] = butterfly32(p, lane);
+        s.red[buf][warp][lane] = butterfly32(p, lane);
         __syncthreads();
-        const int buf = j & 1;
-        if (warp == 0) {
-            float v = 0.0f;
+        // every warp sums the block's columns and forms the reflector for itself: one barrier a step
+        // (the buffers alternate, so the next step's writes cannot overtake this step's reads)
+        float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < PT / 32; ++w) v += s.red[w][lane];
-            const float ss = __shfl_sync(kFull, v, 0);
-            float beta, tau, sc;
-            reflector_fast(s.prow[0], ss, beta, tau, sc);
-            const float val = fmaf(sc, v, s.prow[lane]);
-            s.wv[buf][lane] = (lane >= 1 && lane <= 31 - j) ? tau * val : 0.0f;
+        for (int w = 0; w < PT / 32; ++w) v += s.red[buf][w][lane];
+        const float ss = __shfl_sync(kFull, v, 0);
+        float beta, tau, sc;
+        reflector_fast(s.prow[buf][0], ss, beta, tau, sc);
+        const float val = fmaf(sc, v, s.prow[buf][lane]);
+        s.wv[warp][lane] = (lane >= 1 && lane <= 31 - j) ? tau * val : 0.0f;
+        if (warp == 0) {
             if (lane >= 32 - j) s.G[(j + lane) & 31][j] = val;
-            if (lane == 0) {
-                s.scal[buf][0] = tau;
-                s.scal[buf][1] = sc;
-                s.scal[buf][2] = beta;
-                s.taus[j] = tau;
-            }
+            if (lane == 0) s.taus[j] = tau;
         }
-        __syncthreads();
-        const float sc = s.scal[buf][1], beta = s.scal[buf][2];
+        __syncwarp();
         float w[32];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            const float4 f = *reinterpret_cast<const float4*>(&s.wv[buf][4 * q]);
+            const float4 f = *reinterpret_cast<const float4*>(&s.wv[warp][4 * q]);
             w[4 * q] = f.x; w[4 * q + 1] = f.y; w[4 * q + 2] = f.z; w[4 * q + 3] = f.w;
         }
+        __syncwarp();
 #pragma unroll
         for (int k = 0; k < RPT; ++k) {
             const int row = t + PT * k;
