@@ -294,6 +294,38 @@ __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restr
         }
 }
 
+// The same for a narrow update (the look-ahead's 128 columns): eight columns a block, so that a
+// narrow Z still spreads over many blocks; T is read from global memory (L2) as it is.
+// Grid ceil(nc / 8); thread (i, half) computes Z[i][4 half .. + 3] of the block's eight columns.
+__global__ void __launch_bounds__(256) reduce_t_narrow_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
+                                                              uint32_t ncp, const float* __restrict__ T, int transposed,
+                                                              float* Z) {
+    __shared__ __align__(16) float Zs[128][8];
+    const uint32_t j0 = blockIdx.x * 8;
+    for (int idx = threadIdx.x; idx < 128 * 8; idx += 256) {
+        const uint32_t k = idx >> 3, j = j0 + (idx & 7);
+        float sum = 0.0f;
+        if (j < nc)
+            for (uint32_t ch = 0; ch < chunks; ++ch) sum += Zp[((size_t)ch * AG + k) * ncp + j];
+        Zs[k][idx & 7] = sum;
+    }
+    __syncthreads();
+    const int i = threadIdx.x & 127, h = threadIdx.x >> 7;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+    for (int k = 0; k < 128; ++k) {
+        const float t = transposed ? T[k * 128 + i] : T[i * 128 + k];
+        const float4 z = *reinterpret_cast<const float4*>(&Zs[k][4 * h]);
+        acc[0] = fmaf(t, z.x, acc[0]); acc[1] = fmaf(t, z.y, acc[1]);
+        acc[2] = fmaf(t, z.z, acc[2]); acc[3] = fmaf(t, z.w, acc[3]);
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t j = j0 + 4 * h + b;
+        if (j < nc) Z[(size_t)i * ncp + j] = acc[b];
+    }
+}
+
 // C[r][j] -= sum_k Y[r][k] Z[k][j], k < kw <= 128. Grid (ceil(nc / 128), ceil(mp / 128)); a thread owns 8 x 8.
 __global__ void __launch_bounds__(256) yz_wide_kernel(const float* __restrict__ Y, size_t ldy,
                                                       const float* __restrict__ Z, uint32_t ncp, float* C, size_t ldc,
@@ -430,11 +462,16 @@ constexpr size_t kMergeSmem = (2 * 128 * 129 + 96 * 33) * sizeof(float);
 void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
                      size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z, unsigned* error) {
     if (nc == 0 || mp == 0) return;
-    const uint32_t chunks = (mp + WCH - 1) / WCH, ncp = (nc + 3) & ~3u;
+    const uint32_t ncp = (nc + 3) & ~3u;
     const bool tc = use_tensor_cores();
-    if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, WCH, error);
+    // a narrow update (the look-ahead's) in short row chunks, so that it still fills the GPU
+    const bool narrow = tc && nc <= 256;
+    const uint32_t rows = narrow ? 128u : (uint32_t)WCH;
+    const uint32_t chunks = (mp + rows - 1) / rows;
+    if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
-    reduce_t_wide_kernel<<<(nc + 31) / 32, 256, kReduceWideSmem, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    if (narrow) reduce_t_narrow_kernel<<<(nc + 7) / 8, 256, 0, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    else reduce_t_wide_kernel<<<(nc + 31) / 32, 256, kReduceWideSmem, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
     else yz_wide_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, kw, nc);
     cuda_check(cudaGetLastError(), "aggregate reflector launch");
@@ -619,9 +656,12 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_ta = take((size_t)naggs * AG * AG);
     const size_t o_qp = take((size_t)m * NB), o_rp = take(NB * NB), o_ui = take(NB * NB);
     const size_t gram_floats = (size_t)((m + 127) / 128) * AG * AG;   // the Gram partials of an aggregate, 128 rows a chunk
-    const size_t o_zp = take(std::max({(size_t)chunks_w * AG * ncp, gram_floats}));
+    // partial sums Y^T C: 512-row chunks of the full width, or 128-row chunks of a narrow (<= 256 columns) update
+    const size_t zp_floats = std::max({(size_t)chunks_w * AG * ncp, gram_floats,
+                                       (size_t)((m + 127) / 128) * AG * std::min<size_t>(ncp, 256)});
+    const size_t o_zp = take(zp_floats);
     const size_t o_z = take((size_t)AG * ncp);
-    const size_t o_zp2 = take((size_t)chunks_w * AG * ncp), o_z2 = take((size_t)AG * ncp);   // the second stream's
+    const size_t o_zp2 = take(zp_floats), o_z2 = take((size_t)AG * ncp);   // the second stream's
     const size_t o_info = take(64);
     size_t tsqr_floats = 0;
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
