@@ -466,7 +466,7 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const bool tc = use_tensor_cores();
     // a narrow update (the look-ahead's) in short row chunks, so that it still fills the GPU
     const bool narrow = tc && nc <= 256;
-    const uint32_t rows = narrow ? 128u : (uint32_t)WCH;
+    const uint32_t rows = narrow ? 128u : tc ? 256u : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
     const uint32_t chunks = (mp + rows - 1) / rows;
     if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
@@ -648,7 +648,6 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
 
     // workspace (floats), shared by the matrices of the batch, which are factored one after another
     const uint32_t naggs = (K + AG - 1) / AG;
-    const uint32_t chunks_w = (m + WCH - 1) / WCH;
     auto up64 = [](size_t f) { return (f + 63) & ~(size_t)63; };
     size_t off = 0;
     auto take = [&](size_t floats) { const size_t o = off; off += up64(floats); return o; };
@@ -657,7 +656,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_qp = take((size_t)m * NB), o_rp = take(NB * NB), o_ui = take(NB * NB);
     const size_t gram_floats = (size_t)((m + 127) / 128) * AG * AG;   // the Gram partials of an aggregate, 128 rows a chunk
     // partial sums Y^T C: 512-row chunks of the full width, or 128-row chunks of a narrow (<= 256 columns) update
-    const size_t zp_floats = std::max({(size_t)chunks_w * AG * ncp, gram_floats,
+    const size_t zp_floats = std::max({(size_t)((m + 255) / 256) * AG * ncp, gram_floats,
                                        (size_t)((m + 127) / 128) * AG * std::min<size_t>(ncp, 256)});
     const size_t o_zp = take(zp_floats);
     const size_t o_z = take((size_t)AG * ncp);
