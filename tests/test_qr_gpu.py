@@ -112,8 +112,8 @@ def test_tsqr_shapes(shape, mode):
     m, n = shape
     rng = np.random.default_rng(m + n)
     a = rng.standard_normal((2, m, n)).astype(np.float32)
-    assert mlt.qr_kernel(m, n, 2, mode) == "tsqr"
-    q, r = gpu_qr(a, mode)
+    assert mlt.qr_kernel(m, n, 64, mode) == "tsqr"             # a batch goes to the tree ...
+    q, r = gpu_qr(a, mode, kernel="tsqr")
     _, r_ref = harness.oracle_qr(a, mode)
     check(a, q, r, mode, r_ref)
 
@@ -477,6 +477,11 @@ def test_device_queries():
     assert mlt.qr_policy_source().startswith(("tuned:", "env:", "user"))
     assert mlt.calibration_status() == ""
     assert mlt.qr_kernel(32, 32, 1000) == "small" and mlt.qr_kernel(256, 256, 4096) == "mid"
+    # the measured routing: one matrix is spread over the grid from sqrt(M k) of 300, a batch later
+    assert mlt.qr_kernel(512, 512, 1) == "blocked" and mlt.qr_kernel(512, 512, 16) == "mid"
+    assert mlt.qr_kernel(4096, 64, 1) == "blocked" and mlt.qr_kernel(4096, 64, 16) == "tsqr"
+    assert mlt.qr_kernel(1 << 20, 32, 1) == "tsqr" and mlt.qr_kernel(65536, 64, 64) == "tsqr"
+    assert mlt.qr_kernel(128, 128, 1) == "mid" and mlt.qr_kernel(4096, 4096, 64) == "blocked"
 
 
 # ---------------------------------------------------------------------------
