@@ -23,6 +23,9 @@ inline uint32_t qr_k(const QrProblem& p) { return p.m < p.n ? p.m : p.n; }
 // A matrix in one warp's registers (or a part of a warp's): m, n, qc <= 32.
 bool qr_small_fits(uint32_t m, uint32_t n, uint32_t qc);
 void launch_qr_small(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
+// The same for square matrices of 8, 16 or 32 rows on 16-byte boundaries, streamed through shared
+// memory by bulk asynchronous copies; false (nothing launched) for any other call.
+bool launch_qr_small_stream(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
 
 // A matrix to a thread block: panels of 32 columns factored in shared memory,
 // the trailing matrix streamed through a per-block scratch copy that stays in L2.

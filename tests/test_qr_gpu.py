@@ -101,6 +101,46 @@ def test_mid_kernel_shapes(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
+@pytest.mark.parametrize("stream", ["0", "2"])
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("n,batch", [(8, 60001), (16, 30001), (32, 9001), (32, 37), (16, 3), (8, 1)])
+def test_small_square_streaming_and_direct(n, batch, mode, stream):
+    """Square 8, 16 and 32: the kernel that streams matrices through shared memory by bulk copies
+    (QR_SMALL_STREAM=2: wherever it can) and the one that loads and stores for itself (0), on batches
+    that leave the last warp's unit part filled and give every persistent warp several units."""
+    rng = np.random.default_rng(n + batch)
+    a = rng.standard_normal((batch, n, n)).astype(np.float32)
+    a[batch - 1] *= 1e-30
+    good = np.ones(batch, bool)
+    if batch > 2:
+        a[batch // 2, n - 1, 0] = np.inf
+        good[batch // 2] = False
+    os.environ["QR_SMALL_STREAM"] = stream
+    try:
+        q, r = gpu_qr(a, mode)
+    finally:
+        os.environ.pop("QR_SMALL_STREAM", None)
+    if batch > 2:
+        assert np.isnan(r[batch // 2]).all() and (q is None or np.isnan(q[batch // 2]).all())
+    _, r_ref = harness.oracle_qr(a[good], mode)
+    check(a[good], None if q is None else q[good], r[good], mode, r_ref)
+
+
+def test_small_square_off_a_16_byte_boundary():
+    """The bulk copies need 16-byte boundaries: a tensor that starts 4 bytes off one takes the
+    kernel that loads and stores for itself, with the same results."""
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((1000, 16, 16)).astype(np.float32)
+    base = torch.empty(a.size + 1, dtype=torch.float32, device="cuda")
+    t = base[1:].view(1000, 16, 16)
+    t.copy_(torch.as_tensor(a))
+    assert t.data_ptr() % 16 == 4
+    q, r = mlt.qr(t)
+    torch.cuda.synchronize()
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q.cpu().numpy(), r.cpu().numpy(), "reduced", r_ref)
+
+
 TALL = [(1025, 8), (1500, 64), (2048, 64), (4096, 16), (5000, 33), (20000, 40), (17000, 24), (9000, 128), (70000, 5)]
 
 
