@@ -27,8 +27,10 @@
 // the panels on the output buffer itself.
 #include "common.cuh"
 #include "kernels.h"
+#include "qr_panel_cols.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -54,6 +56,7 @@ struct MidParams {
     int          scale;
     int          ldv;
     int          npanels;
+    int          by_columns;   // panels of at most 256 rows factored with a column per lane
     // matrix index -> (outer, inner) = (mat / inner_count, mat % inner_count) when inner_count > 0:
     // the matrix's buffers then start at outer * *_outer + inner * *_stride
     unsigned     inner_count;
@@ -373,7 +376,53 @@ __device__ void build_t(const Smem& s, int ldv, int mp) {
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
+// The three steps above in one for a panel of at most 256 rows, with a column per lane
+// (qr_panel_cols.cuh: the panel in the registers of the block, one barrier and no shuffle
+// reduction a step; measured 4 times as fast as factor_panel on 256 rows). In: the panel in s.Vs.
+// Out as finish_panel's and build_t's: the factored panel in the scratch matrix, the clean V in
+// s.Vs, T in s.Ts. The trailing tile buffer and the partial-sum buffer serve as its scratch.
+__device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float* W, size_t ldw, int k0) {
+    using namespace cols;
+    cols::Smem& cs = *reinterpret_cast<cols::Smem*>(s.Cs);
+    static_assert(sizeof(cols::Smem) <= 32 * LDC * sizeof(float), "the tile buffer holds the panel scratch");
+    float* pub = s.Zp;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nw = (mp + 31) >> 5;          // the warps that hold rows
+    pair_t x2[16];
+    float my_sc = 0.0f;
+    if (warp < nw) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int row0 = warp * 32 + 4 * q;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row0 < mp) v = *reinterpret_cast<const float4*>(s.Vs + lane * ldv + row0);
+            x2[2 * q]     = pack(v.x, v.y);
+            x2[2 * q + 1] = pack(v.z, v.w);
+        }
+        factor_cols<32, false>(x2, cs, pub, nullptr, my_sc, nw);
+    }
+    __syncthreads();
+    if (warp == 0) build_t_to(cs, s.Ts, LDZ);
+    if (warp < nw) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float e[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int r = 4 * q + t, row = warp * 32 + r;
+                const float raw = warp == 0 ? cs.rows[r][lane] : row_of<32>(x2, r);
+                const float g = row > lane ? raw * my_sc : raw;      // R, beta on the diagonal, the unit-diagonal reflector below
+                const bool in = lane < jb && row < mp;
+                if (in) W[(size_t)(k0 + row) * ldw + k0 + lane] = g;
+                e[t] = in ? (row < lane ? 0.0f : (row == lane ? 1.0f : g)) : 0.0f;
+            }
+            *reinterpret_cast<float4*>(s.Vs + lane * ldv + warp * 32 + 4 * q) = make_float4(e[0], e[1], e[2], e[3]);
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
     extern __shared__ __align__(16) float smem_raw[];
     const Smem s = carve(smem_raw, p.ldv);
     const int m = p.m, n = p.n, K = p.K, ldv = p.ldv;
@@ -392,17 +441,36 @@ __global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
         float*       Q = p.qc ? p.q + oq : nullptr;
         float*       R = p.r + orr;
 
+        // rows of A, the scratch matrix and R on 16-byte boundaries: the copy loops move 16 bytes a lane
+        const bool vec4 = (n & 3) == 0 && (p.lda & 3) == 0 && ((reinterpret_cast<size_t>(A) | reinterpret_cast<size_t>(R)) & 15) == 0;
         // 0. scan: largest magnitude, non-finite entries
         int expo = 0;
         if (p.scale) {
             float amax = 0.0f;
             int   bad = 0;
-            for (int i = threadIdx.x / 32; i < m; i += NT / 32)
-                for (int j = threadIdx.x & 31; j < n; j += 32) {
-                    const float v = A[(size_t)i * p.lda + j];
-                    amax = fmaxf(amax, fabsf(v));
-                    bad |= nonfinite(v);
-                }
+            if (vec4) {      // 16 bytes a lane, four rows in flight
+                for (int i0 = threadIdx.x / 32; i0 < m; i0 += 4 * (NT / 32))
+                    for (int j = (threadIdx.x & 31) * 4; j < n; j += 128) {
+                        float4 v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int i = i0 + u * (NT / 32);
+                            v[u] = i < m ? *reinterpret_cast<const float4*>(A + (size_t)i * p.lda + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[u].x), fabsf(v[u].y))), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+                            bad |= nonfinite(v[u].x) | nonfinite(v[u].y) | nonfinite(v[u].z) | nonfinite(v[u].w);
+                        }
+                    }
+            } else {
+                for (int i = threadIdx.x / 32; i < m; i += NT / 32)
+                    for (int j = threadIdx.x & 31; j < n; j += 32) {
+                        const float v = A[(size_t)i * p.lda + j];
+                        amax = fmaxf(amax, fabsf(v));
+                        bad |= nonfinite(v);
+                    }
+            }
             amax = warp_max(amax);
             bad = __any_sync(0xffffffffu, bad);
             __syncthreads();   // s.red is free (previous matrix done)
@@ -430,9 +498,13 @@ __global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
             if (pi == 0) load_tile(s.Vs, ldv, A, p.lda, 0, mp, 0, jb, from_a);
             else         load_tile(s.Vs, ldv, W, n, k0, mp, k0, jb, LoadPlain{});
             __syncthreads();
-            factor_panel(s, ldv, mp, jb);
-            finish_panel(s, ldv, mp, jb, W, n, k0);
-            build_t(s, ldv, mp);
+            if (mp <= 256 && p.by_columns) {
+                factor_panel_cols(s, ldv, mp, jb, W, n, k0);
+            } else {
+                factor_panel(s, ldv, mp, jb);
+                finish_panel(s, ldv, mp, jb, W, n, k0);
+                build_t(s, ldv, mp);
+            }
             for (int i = threadIdx.x; i < 32 * 32; i += NT) Tg[(size_t)pi * 1024 + i] = s.Ts[(i >> 5) * LDZ + (i & 31)];
             if (k0 + jb < n) {
                 if (pi == 0) update_columns(s, ldv, A, p.lda, from_a, W, n, 0, mp, jb, n, true);
@@ -444,9 +516,31 @@ __global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
         // 2. R, back in the caller's scale
         {
             const Pow2 up(expo);
-            for (int i = threadIdx.x / 32; i < p.rr; i += NT / 32)
-                for (int j = threadIdx.x & 31; j < n; j += 32)
-                    R[(size_t)i * n + j] = (i < K && j >= i) ? up(W[(size_t)i * n + j]) : 0.0f;
+            if (vec4) {
+                for (int i0 = threadIdx.x / 32; i0 < p.rr; i0 += 4 * (NT / 32))
+                    for (int j = (threadIdx.x & 31) * 4; j < n; j += 128) {
+                        float4 v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int i = i0 + u * (NT / 32);
+                            v[u] = (i < K && j + 3 >= i) ? *reinterpret_cast<const float4*>(W + (size_t)i * n + j)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int i = i0 + u * (NT / 32);
+                            if (i >= p.rr) continue;
+                            const bool in = i < K;
+                            *reinterpret_cast<float4*>(R + (size_t)i * n + j) =
+                                make_float4(in && j >= i ? up(v[u].x) : 0.0f, in && j + 1 >= i ? up(v[u].y) : 0.0f,
+                                            in && j + 2 >= i ? up(v[u].z) : 0.0f, in && j + 3 >= i ? up(v[u].w) : 0.0f);
+                        }
+                    }
+            } else {
+                for (int i = threadIdx.x / 32; i < p.rr; i += NT / 32)
+                    for (int j = threadIdx.x & 31; j < n; j += 32)
+                        R[(size_t)i * n + j] = (i < K && j >= i) ? up(W[(size_t)i * n + j]) : 0.0f;
+            }
         }
         if (!p.qc) continue;
 
@@ -482,6 +576,14 @@ __global__ void __launch_bounds__(NT) qr_mid_kernel(const MidParams p) {
 }
 
 } // namespace
+
+namespace {
+// QR_MID_ROWS=1: every panel by factor_panel (a thread per row entry), for comparison and tests
+int mid_by_columns() {
+    const char* e = std::getenv("QR_MID_ROWS");
+    return !(e && e[0] == '1');
+}
+}
 
 bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
     if (m == 0 || n == 0 || m > 1024) return false;
@@ -525,6 +627,7 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr,
     p.scale = o.scale ? 1 : 0;
     p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
     p.npanels = (p.K + JB - 1) / JB;
+    p.by_columns = mid_by_columns();
     p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
 
     const size_t smem = smem_bytes(p.ldv);
@@ -603,6 +706,7 @@ void launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& pr) 
     p.scale = 1;
     p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
     p.npanels = (p.K + JB - 1) / JB;
+    p.by_columns = mid_by_columns();
     p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
     const size_t smem = smem_bytes(p.ldv);
     if (pr.m > 1024 || smem > (size_t)smem_optin)

@@ -27,8 +27,10 @@
 //   panel_apply_kernel  per leaf: Y rows = [B'; 0] - V (T (V_top^T B')).
 #include "common.cuh"
 #include "kernels.h"
+#include "qr_panel_cols.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace mlb {
 
@@ -145,7 +147,8 @@ __device__ __forceinline__ void factor_rows(float (&x)[RPT][32], PanelSmem& s) {
 }
 
 // T from s.G and s.taus (slarft's forward recurrence), by warp 0, a row of T per lane.
-__device__ __forceinline__ void build_t(PanelSmem& s) {
+template <typename Smem>
+__device__ __forceinline__ void build_t(Smem& s) {
     if (threadIdx.x < 32) {
         const int i = threadIdx.x;
         float tr[32];
@@ -424,6 +427,132 @@ __global__ void __launch_bounds__(PT) panel_finish_kernel(const TopParams p) {
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// The leaf and the top with a column per lane (qr_panel_cols.cuh): blocks of 8 * RW rows.
+// Same inputs and outputs as panel_leaf_kernel and panel_top_kernel.
+// ---------------------------------------------------------------------------
+template <int RW>
+__global__ void __launch_bounds__(PT, 1) panel_leaf_cols_kernel(const LeafParams p) {
+    using namespace cols;
+    __shared__ __align__(16) cols::Smem s;
+    __shared__ __align__(16) float pub[kWarps * RW];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t blk = blockIdx.x, row0 = blk * p.lr + warp * RW;
+    pair_t x2[RW / 2];
+#pragma unroll
+    for (int i = 0; i < RW / 2; ++i) {
+        const uint32_t ra = row0 + 2 * i;
+        float a = 0.0f, b = 0.0f;
+        if ((uint32_t)lane < p.jb) {
+            if (ra < p.mp) a = p.panel[(size_t)ra * p.ldw + lane];
+            if (ra + 1 < p.mp) b = p.panel[(size_t)(ra + 1) * p.ldw + lane];
+        }
+        x2[i] = pack(a, b);
+    }
+    float my_sc;
+    factor_cols<RW, false>(x2, s, pub, nullptr, my_sc);
+    __syncthreads();
+    build_t(s);
+    if (warp == 0) {       // the first 32 rows: R for the stack, the reflectors with a unit diagonal
+        float* dst = p.Sl + (size_t)blk * 1024 + lane;
+        float* vdst = p.Vl + (size_t)blk * p.lr * 32 + lane;
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const float v = s.rows[r][lane];
+            dst[r * 32]  = lane >= r ? v : 0.0f;
+            vdst[r * 32] = r > lane ? v * my_sc : (r == lane ? 1.0f : 0.0f);
+        }
+    }
+    {
+        float* dst = p.Vl + ((size_t)blk * p.lr + warp * RW) * 32 + lane;
+#pragma unroll
+        for (int r = (RW > 32 ? 32 : RW); r < RW; ++r)       // warp 0's rows from 32 on (64 rows a lane)
+            if (warp == 0) dst[r * 32] = row_of<RW>(x2, r) * my_sc;
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+            if (warp != 0) dst[r * 32] = row_of<RW>(x2, r) * my_sc;
+    }
+    __syncthreads();
+    for (int idx = t; idx < 1024; idx += PT) p.Tl[(size_t)blk * 1024 + idx] = s.T[idx >> 5][idx & 31];
+}
+
+template <int RW>
+__global__ void __launch_bounds__(PT, 1) panel_top_cols_kernel(const TopParams p) {
+    using namespace cols;
+    constexpr int kRows = kWarps * RW;
+    extern __shared__ __align__(16) float Us[];          // [32][kRows]: the reflectors' tails in the rows from 32 on
+    __shared__ __align__(16) cols::Smem s;
+    __shared__ float V1[32][33], Mr[32][33];
+    __shared__ __align__(16) float M4[32][36];           // read as 16-byte words
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    pair_t x2[RW / 2];
+#pragma unroll
+    for (int i = 0; i < RW / 2; ++i) {
+        const uint32_t ra = warp * RW + 2 * i;
+        const float a = ra < p.S ? p.Sl[(size_t)ra * 32 + lane] : 0.0f;
+        const float b = ra + 1 < p.S ? p.Sl[(size_t)(ra + 1) * 32 + lane] : 0.0f;
+        x2[i] = pack(a, b);
+    }
+    __shared__ __align__(16) float pub[RW];
+    float my_sc;
+    factor_cols<RW, true>(x2, s, pub, Us, my_sc);
+    if (warp == 0 && RW > 32) {      // warp 0's rows from 32 on are not published into Us by the steps: their tails now
+#pragma unroll
+        for (int r = 32; r < RW; ++r) Us[(size_t)lane * kRows + r] = row_of<RW>(x2, r);
+    }
+    __syncthreads();
+    build_t(s);
+    if (warp == 0) {
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const float v = s.rows[r][lane];
+            p.Rt[r * 32 + lane] = lane >= r ? v : 0.0f;
+            V1[r][lane] = r > lane ? v * my_sc : (r == lane ? 1.0f : 0.0f);
+        }
+    }
+    __syncthreads();
+    // The top Q's rows, B = [I; 0] - V (T V1^T) with V the unit-diagonal reflectors: V = [I; 0] +
+    // (tails) diag(sc), so B = [I - M; 0] - (tails) (diag(sc) M), M = T V1^T.
+    {
+        const int i = t >> 3, c0 = (t & 7) * 4;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float a = s.T[i][k];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(a, V1[c0 + e][k], acc[e]);
+        }
+        const float sci = s.sc[i];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            Mr[i][c0 + e] = acc[e];
+            M4[i][c0 + e] = acc[e] * sci;
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (uint32_t row = t; row < p.S; row += PT) {      // a row of B per thread and pass
+        float b[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) b[c] = (row == (uint32_t)c ? 1.0f : 0.0f) - (row < 32 ? Mr[row][c] : 0.0f);
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) {
+            const float v = row < 32 ? ((uint32_t)kk < row ? s.rows[row][kk] : 0.0f) : Us[kk * kRows + row];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 m4 = *reinterpret_cast<const float4*>(&M4[kk][4 * q]);
+                b[4 * q] = fmaf(-v, m4.x, b[4 * q]); b[4 * q + 1] = fmaf(-v, m4.y, b[4 * q + 1]);
+                b[4 * q + 2] = fmaf(-v, m4.z, b[4 * q + 2]); b[4 * q + 3] = fmaf(-v, m4.w, b[4 * q + 3]);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(p.Bp + (size_t)row * 32 + 4 * q) =
+                make_float4(b[4 * q], b[4 * q + 1], b[4 * q + 2], b[4 * q + 3]);
+    }
+}
+
 struct ApplyParams {
     const float* Vl;        // [leaves][lr][32]
     const float* Tl;        // [leaves][32][32]
@@ -500,14 +629,33 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     float* Tl = Vl + (size_t)leaves * lr * 32;
     float* Sl = Tl + (size_t)leaves * 1024;
     float* Bp = Sl + (size_t)leaves * 1024;
-    LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
-    if (rpt == 1) panel_leaf_kernel<1><<<leaves, PT, 0, stream>>>(lp);
-    else if (rpt == 2) panel_leaf_kernel<2><<<leaves, PT, 0, stream>>>(lp);
-    else panel_leaf_kernel<4><<<leaves, PT, 0, stream>>>(lp);
     float* Rt = Bp + (size_t)leaves * 1024;
+    // a column per lane up to 8192 rows; a row per thread beyond, and for both with QR_PANEL_ROWS=1
+    const char* env = std::getenv("QR_PANEL_ROWS");
+    const bool by_columns = rpt <= 2 && !(env && env[0] == '1');
+    LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
     TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp, Rt};
-    if (leaves * 32 <= PT) panel_top_kernel<1><<<1, PT, 0, stream>>>(tp);
-    else panel_top_kernel<2><<<1, PT, 0, stream>>>(tp);
+    if (by_columns) {
+        static const bool configured = [] {
+            // static and dynamic shared memory together pass the 48 KB that need no opt-in
+            cuda_check(cudaFuncSetAttribute(panel_top_cols_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            32 * 256 * (int)sizeof(float)), "panel_top_cols shared memory");
+            cuda_check(cudaFuncSetAttribute(panel_top_cols_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            32 * 512 * (int)sizeof(float)), "panel_top_cols shared memory");
+            return true;
+        }();
+        (void)configured;
+        if (rpt == 1) panel_leaf_cols_kernel<32><<<leaves, PT, 0, stream>>>(lp);
+        else panel_leaf_cols_kernel<64><<<leaves, PT, 0, stream>>>(lp);
+        if (leaves * 32 <= PT) panel_top_cols_kernel<32><<<1, PT, 32 * 256 * sizeof(float), stream>>>(tp);
+        else panel_top_cols_kernel<64><<<1, PT, 32 * 512 * sizeof(float), stream>>>(tp);
+    } else {
+        if (rpt == 1) panel_leaf_kernel<1><<<leaves, PT, 0, stream>>>(lp);
+        else if (rpt == 2) panel_leaf_kernel<2><<<leaves, PT, 0, stream>>>(lp);
+        else panel_leaf_kernel<4><<<leaves, PT, 0, stream>>>(lp);
+        if (leaves * 32 <= PT) panel_top_kernel<1><<<1, PT, 0, stream>>>(tp);
+        else panel_top_kernel<2><<<1, PT, 0, stream>>>(tp);
+    }
     panel_finish_kernel<<<1, PT, 0, stream>>>(tp);
     ApplyParams ap{Vl, Tl, Bp, y, ldy, mp, jb, lr};
     if (rpt == 1) panel_apply_kernel<1><<<leaves, PT, 0, stream>>>(ap);

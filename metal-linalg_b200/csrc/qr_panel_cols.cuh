@@ -1,0 +1,224 @@
+#pragma once
+// Householder QR of a block of 8 * RW rows x 32 columns by one thread block of
+// eight warps, a COLUMN per lane: warp w holds rows w * RW ... of every column,
+// lane l column l, two rows to a 64-bit register (RW = 32 or 64 rows a lane).
+//
+// With a column per lane a reflector's dot products with the 32 columns are each
+// lane's own packed FMAs; what a step needs across the block is one sum of eight
+// partial products per lane, through shared memory and ONE barrier. (With a row
+// per thread, the layout of factor_rows in qr_panel.cu, the same step reduces 32
+// numbers per thread across the lanes first: 31 shuffles and selects a thread,
+// which made a step four times as long.)
+//
+// Step j: lane j of every warp publishes its rows of column j to shared memory
+// (warp 0, which holds the triangle, with zeros in the rows <= j); every lane
+// reads them back as broadcast 16-byte words and takes the product with its own
+// column; the block sums the eight partial products per column. Lane j's sum is
+// the tail's sum of squares, so the norm costs nothing extra. Every warp forms the
+// reflector for itself (unnormalised, H = I - g u u^T with u = (v1; tail), as in
+// qr_small_steps.cuh) and updates the columns right of j. The columns left of j
+// are not touched: below the diagonal they keep their reflector's tail, so their
+// sums in later steps are the reflectors' products with one another, the Gram
+// matrix that T is built from (slarft's recurrence).
+//
+// The step loops are not unrolled (a panel kernel runs on a few multiprocessors,
+// once: unrolled, every instruction would be fetched from memory for a single
+// use, and the fetches took longer than the arithmetic). Warp 0, which holds the
+// triangle, keeps the pivot row at a constant register index by rotating its
+// first rows (step_warp0 below); the other warps' steps do not depend on j at all.
+//
+// Afterwards: the block's first 32 rows in s.rows (R on and above the diagonal,
+// the reflectors' tails, unnormalised, below it), the tails of the other rows in
+// the registers, in `my_sc` of lane l the scale 1 / v1 that gives column l's
+// reflector a unit diagonal (0 for a reflector that is the identity), s.taus,
+// s.sc, s.G set.
+#include "qr_small_steps.cuh"
+
+namespace mlb {
+namespace cols {
+
+using namespace small;
+
+constexpr int kWarps = 8;
+
+struct Smem {
+    float red[2][kWarps][32];    // each warp's partial products per column, by step parity
+    float prow[2][32];           // the pivot row, by step parity
+    float taus[32], sc[32];
+    float G[32][33];             // G[k][j] = v_k^T v_j for k < j (unit-diagonal reflectors)
+    float T[32][33];
+    float rows[32][32];          // the block's first 32 rows as they finish: R, and the reflectors' tails below the diagonal
+};
+
+// 1 / x to an ulp or so (x normal)
+__device__ __forceinline__ float recip(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r * fmaf(-x, r, 2.0f);
+}
+
+// The step barrier: the `threads` threads of the warps that hold rows, from wherever they are in
+// the code (warp 0 runs a different loop from the others, so this is a named barrier, not
+// __syncthreads()).
+__device__ __forceinline__ void step_barrier(int threads) { asm volatile("bar.sync 1, %0;" :: "r"(threads) : "memory"); }
+
+// What every warp does after the step barrier: the block's sums, the reflector (the same numbers
+// in every warp), the Gram entries and tau. Returns t, the coefficient of this lane's update
+// (0 for the columns left of j, which keep their reflectors), and v1, alpha.
+__device__ __forceinline__ float step_reflector(Smem& s, int j, int buf, int lane, int warp, int nw, float& my_sc,
+                                                float& v1, float& alpha) {
+    float d = s.red[buf][0][lane];
+    for (int w = 1; w < nw; ++w) d += s.red[buf][w][lane];
+    const float xj = s.prow[buf][lane];
+    alpha = s.prow[buf][j];
+    const float ss = __shfl_sync(0xffffffffu, d, j);
+    float gneg;
+    fast_reflector(alpha, ss, v1, gneg);
+    const float sv  = fmaf(v1, xj, d);                    // u^T (this lane's column), u = (v1; tail)
+    const float scj = gneg != 0.0f ? recip(v1) : 0.0f;
+    if (warp == 0) {
+        if (lane < j) s.G[lane][j] = sv * my_sc * scj;
+        if (lane == 0) {
+            s.taus[j] = -gneg * v1 * v1;
+            s.sc[j]   = scj;
+        }
+    }
+    if (lane == j) my_sc = scj;
+    return lane > j ? sv * gneg : 0.0f;
+}
+
+// One step of warp 0, which holds the block's first rows. Its first 16 pairs of rows rotate: the
+// pivot row is always in pair 0 (its low half in the even step P = 0, its high half in the odd
+// one), and after the odd step the two finished rows leave for s.rows and the pairs move up one
+// place (zeros come in at the end), so the step loop is not unrolled, every register index is a
+// constant and the code stays small enough to be fetched once and run from the instruction cache.
+template <int RW, int P>
+__device__ __forceinline__ void step_warp0(pair_t (&x2)[RW / 2], Smem& s, ulonglong2* pj, int it, int lane, int nw,
+                                           float& my_sc) {
+    constexpr int NQ = RW / 4, NP = RW / 2;
+    const int j = 2 * it + P, buf = P;
+    const pair_t zero2 = pack(0.0f, 0.0f);
+    if (lane == j) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            pair_t a = x2[2 * q], b = x2[2 * q + 1];
+            if (q == 0) a = P == 0 ? pack(0.0f, hi_of(a)) : zero2;      // zeros in the rows up to the pivot's
+            pj[q] = make_ulonglong2(a, b);
+        }
+    }
+    __syncwarp();
+    ulonglong2 u[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) u[q] = pj[q];
+    {
+        pair_t s2 = P == 0 ? mul2(u[0].x, x2[0]) : zero2, s2b = mul2(u[0].y, x2[1]);
+#pragma unroll
+        for (int q = 1; q < NQ; ++q) {
+            s2  = fma2(u[q].x, x2[2 * q], s2);
+            s2b = fma2(u[q].y, x2[2 * q + 1], s2b);
+        }
+        s.red[buf][0][lane] = hsum2(s2, s2b);
+    }
+    s.prow[buf][lane] = P == 0 ? lo_of(x2[0]) : hi_of(x2[0]);
+    step_barrier(32 * nw);
+    float v1, alpha;
+    const float  t  = step_reflector(s, j, buf, lane, 0, nw, my_sc, v1, alpha);
+    const pair_t t2 = pack(t, t);
+    const pair_t w0 = P == 0 ? pack(v1, hi_of(u[0].x)) : pack(0.0f, v1);    // the reflector's first pair: v1 in the pivot's row
+    pair_t head = fma2(t2, w0, x2[0]);
+    if (lane == j) head = P == 0 ? pack(alpha - v1, hi_of(head)) : pack(lo_of(head), alpha - v1);   // the owner's pivot becomes beta
+    if (P == 0) {
+        x2[0] = head;
+#pragma unroll
+        for (int i = 1; i < NP; ++i) x2[i] = fma2(t2, (i & 1) ? u[i / 2].y : u[i / 2].x, x2[i]);
+    } else {
+        s.rows[2 * it][lane]     = lo_of(head);
+        s.rows[2 * it + 1][lane] = hi_of(head);
+#pragma unroll
+        for (int i = 1; i < 16; ++i) x2[i - 1] = fma2(t2, (i & 1) ? u[i / 2].y : u[i / 2].x, x2[i]);
+        x2[15] = zero2;
+#pragma unroll
+        for (int i = 16; i < NP; ++i) x2[i] = fma2(t2, (i & 1) ? u[i / 2].y : u[i / 2].x, x2[i]);
+    }
+}
+
+// Keep: the other warps' published rows stay in shared memory, vector j's at keep + j * (8 RW) +
+// (block row); else they go through `pub` like warp 0's (8 RW floats, reused every step).
+// Afterwards: s.rows[r][c] holds the block's first 32 rows, R on and above the diagonal and the
+// reflectors' tails below it; warp 0's rotating pairs are zero, its other rows (RW = 64) and every
+// other warp's hold the tails of their rows; my_sc of lane l is s.sc[l].
+// nw: the warps that hold rows (the first nw; the others do not take part and may not call).
+template <int RW, bool Keep>
+__device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float* pub, float* keep, float& my_sc,
+                                            int nw = kWarps) {
+    constexpr int NQ = RW / 4;           // 16-byte words of a warp's piece of a column
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    my_sc = 0.0f;
+    if (warp == 0) {
+        ulonglong2* pj = reinterpret_cast<ulonglong2*>(pub);
+#pragma unroll 1
+        for (int it = 0; it < 16; ++it) {
+            step_warp0<RW, 0>(x2, s, pj, it, lane, nw, my_sc);
+            step_warp0<RW, 1>(x2, s, pj, it, lane, nw, my_sc);
+        }
+    } else {
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) {
+            const int buf = j & 1;
+            ulonglong2* pj = Keep ? reinterpret_cast<ulonglong2*>(keep + (size_t)j * kWarps * RW) + (size_t)warp * NQ
+                                  : reinterpret_cast<ulonglong2*>(pub) + (size_t)warp * NQ;
+            if (lane == j) {
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) pj[q] = make_ulonglong2(x2[2 * q], x2[2 * q + 1]);
+            }
+            __syncwarp();
+            ulonglong2 u[NQ];
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) u[q] = pj[q];
+            {
+                pair_t s2 = mul2(u[0].x, x2[0]), s2b = mul2(u[0].y, x2[1]);
+#pragma unroll
+                for (int q = 1; q < NQ; ++q) {
+                    s2  = fma2(u[q].x, x2[2 * q], s2);
+                    s2b = fma2(u[q].y, x2[2 * q + 1], s2b);
+                }
+                s.red[buf][warp][lane] = hsum2(s2, s2b);
+            }
+            step_barrier(32 * nw);
+            float v1, alpha;
+            const float  t  = step_reflector(s, j, buf, lane, warp, nw, my_sc, v1, alpha);
+            const pair_t t2 = pack(t, t);
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                x2[2 * q]     = fma2(t2, u[q].x, x2[2 * q]);
+                x2[2 * q + 1] = fma2(t2, u[q].y, x2[2 * q + 1]);
+            }
+        }
+    }
+}
+
+// T from s.G and s.taus (slarft's forward recurrence) by one warp, a row of T per lane, to
+// T[i * ldt + j].
+__device__ __forceinline__ void build_t_to(const Smem& s, float* T, int ldt) {
+    const int i = threadIdx.x & 31;
+    float tr[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float tau = s.taus[j];
+        float a = 0.0f;
+#pragma unroll
+        for (int k = 0; k < j; ++k) a = fmaf(tr[k], s.G[k][j], a);
+        tr[j] = i < j ? -tau * a : (i == j ? tau : 0.0f);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) T[i * ldt + j] = tr[j];
+}
+
+// row r of this lane's column
+template <int RW>
+__device__ __forceinline__ float row_of(const pair_t (&x2)[RW / 2], int r) {
+    return (r & 1) ? hi_of(x2[r / 2]) : lo_of(x2[r / 2]);
+}
+
+} // namespace cols
+} // namespace mlb
