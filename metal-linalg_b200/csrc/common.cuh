@@ -65,6 +65,19 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// First thing in a kernel that may be launched with programmatic stream serialization
+// (launch_dependent in runtime.h): wait until the kernels before it in the stream have completed
+// and their memory is visible, then let the next kernel in the stream be brought onto the
+// multiprocessors, where it waits at the same place. The launch latency of a chain of short
+// kernels is hidden this way, one kernel ahead. Without that launch attribute both are no-ops.
+__device__ __forceinline__ void dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// The same for a kernel whose grid may be larger than the GPU holds at once: it waits, but lets the
+// next kernel come only when it ends (waiting blocks would take the places of its own).
+__device__ __forceinline__ void dependency_wait_only() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float qnan() { return __uint_as_float(0x7FC00000u); }
 
 } // namespace mlb

@@ -203,6 +203,7 @@ constexpr int WCH = 512;    // rows per chunk of the wide Y^T C partial sums
 __global__ void __launch_bounds__(256) ytc_wide_kernel(const float* __restrict__ Y, size_t ldy,
                                                        const float* __restrict__ C, size_t ldc, uint32_t mp, uint32_t kw,
                                                        uint32_t nc, float* Zp, uint32_t ncp) {
+    dependency_wait_only();
     __shared__ __align__(16) float Ys[32][132];
     __shared__ __align__(16) float Cs[32][132];
     const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
@@ -252,6 +253,7 @@ __global__ void __launch_bounds__(256) ytc_wide_kernel(const float* __restrict__
 __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
                                                             uint32_t ncp, const float* __restrict__ T, int transposed,
                                                             float* Z) {
+    dependency_wait_only();
     extern __shared__ __align__(16) float dsm[];
     float (*Tt)[132] = reinterpret_cast<float (*)[132]>(dsm);                // Tt[k][i] = op(T)[i][k]
     float (*Zs)[36]  = reinterpret_cast<float (*)[36]>(dsm + 128 * 132);
@@ -300,6 +302,7 @@ __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restr
 __global__ void __launch_bounds__(256) reduce_t_narrow_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
                                                               uint32_t ncp, const float* __restrict__ T, int transposed,
                                                               float* Z) {
+    dependency_wait();
     __shared__ __align__(16) float Zs[128][8];
     const uint32_t j0 = blockIdx.x * 8;
     for (int idx = threadIdx.x; idx < 128 * 8; idx += 256) {
@@ -330,6 +333,7 @@ __global__ void __launch_bounds__(256) reduce_t_narrow_kernel(const float* __res
 __global__ void __launch_bounds__(256) yz_wide_kernel(const float* __restrict__ Y, size_t ldy,
                                                       const float* __restrict__ Z, uint32_t ncp, float* C, size_t ldc,
                                                       uint32_t mp, uint32_t kw, uint32_t nc) {
+    dependency_wait_only();
     __shared__ __align__(16) float Ys[32][132];   // [k][row]
     __shared__ __align__(16) float Zs[32][128];   // [k][col]
     const uint32_t j0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
@@ -389,6 +393,7 @@ __global__ void __launch_bounds__(256) yz_wide_kernel(const float* __restrict__ 
 // (the reference: bd_merge_t, shaders/Svd_Bidiag.metal:1131-1164). One block; dynamic shared memory.
 // The chunks' partial Gram matrices added up into the first one, an entry per thread.
 __global__ void gram_sum_kernel(float* zp, uint32_t chunks, uint32_t count) {
+    dependency_wait();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
@@ -412,6 +417,7 @@ struct MergeParams {
 };
 
 __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
+    dependency_wait();
     extern __shared__ __align__(16) float dsm[];
     float (*Ta)[129] = reinterpret_cast<float (*)[129]>(dsm);
     float (*G)[129]  = reinterpret_cast<float (*)[129]>(dsm + 128 * 129);
@@ -469,11 +475,11 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const uint32_t rows = narrow ? 128u : tc ? 256u : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
     const uint32_t chunks = (mp + rows - 1) / rows;
     if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
-    else ytc_wide_kernel<<<dim3((nc + 127) / 128, chunks), 256, 0, stream>>>(Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
-    if (narrow) reduce_t_narrow_kernel<<<(nc + 7) / 8, 256, 0, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    else reduce_t_wide_kernel<<<(nc + 31) / 32, 256, kReduceWideSmem, stream>>>(zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
+    if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 256, 0, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
-    else yz_wide_kernel<<<dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream>>>(Y, ldy, z, ncp, C, ldc, mp, kw, nc);
+    else launch_dependent(yz_wide_kernel, dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc);
     cuda_check(cudaGetLastError(), "aggregate reflector launch");
 }
 
@@ -487,11 +493,11 @@ void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t
         const uint32_t rows = use_tensor_cores() ? 128u : (uint32_t)WCH;
         const uint32_t chunks = (ma + rows - 1) / rows, gld = (wa + 3) & ~3u;
         if (use_tensor_cores()) launch_tc_ytc(stream, Y, ldy, Y, ldy, ma, wa, wa, zp, gld, rows, error);
-        else ytc_wide_kernel<<<dim3(1, chunks), 256, 0, stream>>>(Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
-        gram_sum_kernel<<<(AG * gld + 255) / 256, 256, 0, stream>>>(zp, chunks, AG * gld);
+        else launch_dependent(ytc_wide_kernel, dim3(1, chunks), 256, 0, stream, Y, ldy, Y, ldy, ma, wa, wa, zp, gld);
+        launch_dependent(gram_sum_kernel, (AG * gld + 255) / 256, 256, 0, stream, zp, chunks, AG * gld);
         mp.gram = zp; mp.chunks = chunks; mp.gld = gld;
     }
-    merge_t_kernel<<<1, 256, kMergeSmem, stream>>>(mp);
+    launch_dependent(merge_t_kernel, 1, 256, kMergeSmem, stream, mp);
     cuda_check(cudaGetLastError(), "aggregate T launch");
 }
 
@@ -523,6 +529,7 @@ __device__ __forceinline__ void inner_load_y(float (&y)[32], const float* yr, bo
 __global__ void __launch_bounds__(256) inner_z_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ C,
                                                       size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc, float* zpart,
                                                       uint32_t ncp) {
+    dependency_wait();
     __shared__ float red[8][32 * ICS];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint32_t c0 = blockIdx.x * ICS, ncb = min((uint32_t)ICS, nc - c0);
@@ -575,6 +582,7 @@ __global__ void __launch_bounds__(256) inner_apply_kernel(const float* __restric
                                                           const float* __restrict__ T, float* C, size_t ldc, uint32_t mp,
                                                           uint32_t jb, uint32_t nc, const float* __restrict__ zpart,
                                                           uint32_t ncp, uint32_t chunks) {
+    dependency_wait();
     __shared__ float Zs[32][ICS], Ws[32][ICS];
     __shared__ float Ts[32][33];
     const int t = threadIdx.x;
@@ -625,8 +633,8 @@ void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T
     if (nc == 0 || mp == 0) return;
     const uint32_t chunks = (mp + IRB - 1) / IRB, ncp = (nc + 3) & ~3u;
     const dim3 grid((nc + ICS - 1) / ICS, chunks);
-    inner_z_kernel<<<grid, 256, 0, stream>>>(Y, ldy, C, ldc, mp, jb, nc, zpart, ncp);
-    inner_apply_kernel<<<grid, 256, 0, stream>>>(Y, ldy, T, C, ldc, mp, jb, nc, zpart, ncp, chunks);
+    launch_dependent(inner_z_kernel, grid, 256, 0, stream, Y, ldy, C, ldc, mp, jb, nc, zpart, ncp);
+    launch_dependent(inner_apply_kernel, grid, 256, 0, stream, Y, ldy, T, C, ldc, mp, jb, nc, zpart, ncp, chunks);
     cuda_check(cudaGetLastError(), "inner update launch");
 }
 
@@ -669,11 +677,19 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_ts = take(tsqr_floats);
     const size_t o_pf = take(panel_fast_workspace_floats(std::min<uint32_t>(m, 16384)));
     const bool slow_panels = std::getenv("QR_PANEL_TREE") != nullptr;   // the general tree for every panel, for comparison
-    float* ws = static_cast<float*>(ctx.workspace(stream, off * sizeof(float)));
-    float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
-    float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
     const bool look_ahead = std::getenv("QR_NO_LOOKAHEAD") == nullptr;
-    MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
+    // A batch of large matrices is factored several at a time, each on its own pair of streams and
+    // its own slice of the workspace: one matrix's chain of panel kernels keeps a handful of
+    // multiprocessors busy, and the others' updates fill the rest.
+    uint32_t nlanes = 1;
+    if (pr.batch > 1 && naggs > 1) {
+        const char* e = std::getenv("QR_BLOCKED_LANES");
+        const size_t budget = (size_t)6 << 30;   // bytes of workspace
+        const size_t fit = std::max<size_t>(1, budget / (off * sizeof(float)));
+        nlanes = (uint32_t)std::min<size_t>({(size_t)pr.batch, (size_t)DeviceContext::kExtraLanes + 1, fit});
+        if (e && std::atoi(e) >= 1) nlanes = std::min<uint32_t>(nlanes, (uint32_t)std::atoi(e));
+    }
+    float* ws_all = static_cast<float*>(ctx.workspace(stream, (size_t)nlanes * off * sizeof(float)));
     static bool configured = false;
     if (!configured) {
         cuda_check(cudaFuncSetAttribute(reduce_t_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -682,11 +698,28 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                    "merge_t shared memory");
         configured = true;
     }
+    const cudaStream_t caller = stream;
+    if (nlanes > 1) {      // the extra lanes start after what the caller's stream holds
+        for (uint32_t l = 1; l < nlanes; ++l) ctx.lane(l - 1);
+        cuda_check(cudaEventRecord(ctx.ev_fork, caller), "cudaEventRecord");
+        for (uint32_t l = 1; l < nlanes; ++l)
+            cuda_check(cudaStreamWaitEvent(ctx.lane(l - 1).update, ctx.ev_fork, 0), "cudaStreamWaitEvent");
+    }
 
     for (uint32_t b = 0; b < pr.batch; ++b) {
         const float* A = pr.a + (size_t)b * m * n;
         float* Q = qc ? pr.q + (size_t)b * m * qc : nullptr;
         float* R = pr.r + (size_t)b * rr * n;
+        // this matrix's lane: streams, events, workspace
+        const uint32_t ln = b % nlanes;
+        const cudaStream_t stream = ln ? ctx.lane(ln - 1).update : caller;
+        const cudaStream_t panel_stream = ln ? ctx.lane(ln - 1).panel : ctx.aux;
+        cudaEvent_t* const ev_panel  = ln ? ctx.lane(ln - 1).ev_panel : ctx.ev_panel;
+        cudaEvent_t* const ev_update = ln ? ctx.lane(ln - 1).ev_update : ctx.ev_update;
+        float* ws = ws_all + (size_t)ln * off;
+        float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
+        float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
+        MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
 
         cuda_check(cudaMemsetAsync(info, 0, sizeof(MatInfo), stream), "cudaMemsetAsync");
         scan_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, (size_t)m * n, info);
@@ -701,11 +734,11 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // the next aggregate's columns, so that its panels can start; the columns beyond go to `us`
         // and run beside those panels. Updates of one column range stay in order: before its own
         // update `ps` waits for the previous update on `us`, which covered the same columns.
-        cudaStream_t ps = look_ahead && naggs > 1 ? ctx.aux : stream, us = stream;
+        cudaStream_t ps = look_ahead && naggs > 1 ? panel_stream : stream, us = stream;
         const bool two = ps != us;
         if (two) {
-            cuda_check(cudaEventRecord(ctx.ev_update[1], us), "cudaEventRecord");        // the working copy is ready
-            cuda_check(cudaStreamWaitEvent(ps, ctx.ev_update[1], 0), "cudaStreamWaitEvent");
+            cuda_check(cudaEventRecord(ev_update[1], us), "cudaEventRecord");        // the working copy is ready
+            cuda_check(cudaStreamWaitEvent(ps, ev_update[1], 0), "cudaStreamWaitEvent");
         }
         for (uint32_t ag = 0; ag < naggs; ++ag) {
             const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0, pans = (wa + NB - 1) / NB;
@@ -739,20 +772,20 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                                 W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z, &info->bad);
             } else if (right) {
                 const uint32_t next = std::min<uint32_t>(AG, right);
-                if (ag > 0) cuda_check(cudaStreamWaitEvent(ps, ctx.ev_update[(ag - 1) & 1], 0), "cudaStreamWaitEvent");
+                if (ag > 0) cuda_check(cudaStreamWaitEvent(ps, ev_update[(ag - 1) & 1], 0), "cudaStreamWaitEvent");
                 apply_aggregate(ps, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
                                 W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, next, Zp, Z, &info->bad);
-                cuda_check(cudaEventRecord(ctx.ev_panel[ag & 1], ps), "cudaEventRecord");
-                cuda_check(cudaStreamWaitEvent(us, ctx.ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
+                cuda_check(cudaEventRecord(ev_panel[ag & 1], ps), "cudaEventRecord");
+                cuda_check(cudaStreamWaitEvent(us, ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
                 if (right > next)
                     apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
                                     W + (size_t)j0 * ldw + j0 + wa + next, ldw, ma, wa, right - next, Zp2, Z2, &info->bad);
-                cuda_check(cudaEventRecord(ctx.ev_update[ag & 1], us), "cudaEventRecord");
+                cuda_check(cudaEventRecord(ev_update[ag & 1], us), "cudaEventRecord");
             }
         }
         if (two) {   // the caller's stream joins the panel stream
-            cuda_check(cudaEventRecord(ctx.ev_panel[0], ps), "cudaEventRecord");
-            cuda_check(cudaStreamWaitEvent(us, ctx.ev_panel[0], 0), "cudaStreamWaitEvent");
+            cuda_check(cudaEventRecord(ev_panel[0], ps), "cudaEventRecord");
+            cuda_check(cudaStreamWaitEvent(us, ev_panel[0], 0), "cudaStreamWaitEvent");
         }
         r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
         if (!qc) continue;
@@ -765,6 +798,10 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                             Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad);
         }
         nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);
+    }
+    for (uint32_t l = 1; l < nlanes; ++l) {      // the caller's stream waits for the extra lanes
+        cuda_check(cudaEventRecord(ctx.lane(l - 1).ev_done, ctx.lane(l - 1).update), "cudaEventRecord");
+        cuda_check(cudaStreamWaitEvent(caller, ctx.lane(l - 1).ev_done, 0), "cudaStreamWaitEvent");
     }
     cuda_check(cudaGetLastError(), "qr_blocked launch");
 }

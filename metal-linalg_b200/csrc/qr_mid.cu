@@ -546,8 +546,15 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
 
         // 3. Q = H_0 ... H_{K-1} [I; 0], block reflectors applied backward
         const int qc = p.qc;
-        for (int i = threadIdx.x / 32; i < m; i += NT / 32)
-            for (int j = threadIdx.x & 31; j < qc; j += 32) Q[(size_t)i * qc + j] = i == j ? 1.0f : 0.0f;
+        if ((qc & 3) == 0 && (reinterpret_cast<size_t>(Q) & 15) == 0) {
+            for (int i = threadIdx.x / 32; i < m; i += NT / 32)
+                for (int j = (threadIdx.x & 31) * 4; j < qc; j += 128)
+                    *reinterpret_cast<float4*>(Q + (size_t)i * qc + j) =
+                        make_float4(i == j ? 1.0f : 0.0f, i == j + 1 ? 1.0f : 0.0f, i == j + 2 ? 1.0f : 0.0f, i == j + 3 ? 1.0f : 0.0f);
+        } else {
+            for (int i = threadIdx.x / 32; i < m; i += NT / 32)
+                for (int j = threadIdx.x & 31; j < qc; j += 32) Q[(size_t)i * qc + j] = i == j ? 1.0f : 0.0f;
+        }
         __syncthreads();
         for (int pi = p.npanels - 1; pi >= 0; --pi) {
             const int k0 = pi * JB, jb = min(JB, K - k0), mp = m - k0;
@@ -555,17 +562,24 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
             {   // the reflectors back from the scratch matrix: rows relative to the panel
                 const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
                 const int nq = (mp + 3) >> 2;
-                for (int rq = warp; rq < nq; rq += NT / 32) {
-                    const int r = rq * 4;
-                    float e[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (c < jb) {
+                for (int rq0 = warp; rq0 < nq; rq0 += 2 * (NT / 32)) {      // two words a lane in flight
+                    float e[2][4];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int r = (rq0 + u * (NT / 32)) * 4;
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
                             const int rr = r + t;
-                            if (rr < mp) e[t] = rr > c ? W[(size_t)(k0 + rr) * n + k0 + c] : (rr == c ? 1.0f : 0.0f);
+                            e[u][t] = 0.0f;
+                            if (c < jb && rr < mp) e[u][t] = rr > c ? W[(size_t)(k0 + rr) * n + k0 + c] : (rr == c ? 1.0f : 0.0f);
                         }
                     }
-                    *reinterpret_cast<float4*>(s.Vs + c * ldv + r) = make_float4(e[0], e[1], e[2], e[3]);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int rq = rq0 + u * (NT / 32);
+                        if (rq < nq)
+                            *reinterpret_cast<float4*>(s.Vs + c * ldv + rq * 4) = make_float4(e[u][0], e[u][1], e[u][2], e[u][3]);
+                    }
                 }
             }
             for (int i = threadIdx.x; i < 32 * 32; i += NT) s.Ts[(i >> 5) * LDZ + (i & 31)] = Tg[(size_t)pi * 1024 + i];

@@ -194,6 +194,7 @@ struct LeafParams {
 
 template <int RPT>
 __global__ void __launch_bounds__(PT) panel_leaf_kernel(const LeafParams p) {
+    dependency_wait();
     __shared__ __align__(16) PanelSmem s;
     const int t = threadIdx.x;
     const uint32_t blk = blockIdx.x, row0 = blk * p.lr;
@@ -277,6 +278,7 @@ struct TopParams {
 // The stack of R's factored; out: its R (Rt) and the rows of its Q's first 32 columns (Bp).
 template <int RPT>
 __global__ void __launch_bounds__(PT, 1) panel_top_kernel(const TopParams p) {
+    dependency_wait();
     __shared__ __align__(16) PanelSmem s;
     __shared__ float V1[32][33];
     __shared__ __align__(16) float M4[32][36];   // read as 16-byte words
@@ -326,6 +328,7 @@ __global__ void __launch_bounds__(PT, 1) panel_top_kernel(const TopParams p) {
 // Householder reconstruction from the top's Q rows (Bp) and leaf 0's reflectors: the panel's T, R
 // and L1, and Bp <- Bp U^-1.
 __global__ void __launch_bounds__(PT) panel_finish_kernel(const TopParams p) {
+    dependency_wait();
     __shared__ float M[32][33], B0[32][33], X[32][33], V0[32][33], T0[32][33], Rm[32][33];
     __shared__ __align__(16) float Q[32][36];   // read as 16-byte words
     __shared__ float sgn[32];
@@ -434,6 +437,7 @@ __global__ void __launch_bounds__(PT) panel_finish_kernel(const TopParams p) {
 // ---------------------------------------------------------------------------
 template <int RW>
 __global__ void __launch_bounds__(PT, 1) panel_leaf_cols_kernel(const LeafParams p) {
+    dependency_wait();
     using namespace cols;
     __shared__ __align__(16) cols::Smem s;
     __shared__ __align__(16) float pub[kWarps * RW];
@@ -479,6 +483,7 @@ __global__ void __launch_bounds__(PT, 1) panel_leaf_cols_kernel(const LeafParams
 
 template <int RW>
 __global__ void __launch_bounds__(PT, 1) panel_top_cols_kernel(const TopParams p) {
+    dependency_wait();
     using namespace cols;
     constexpr int kRows = kWarps * RW;
     extern __shared__ __align__(16) float Us[];          // [32][kRows]: the reflectors' tails in the rows from 32 on
@@ -564,6 +569,7 @@ struct ApplyParams {
 
 template <int RPT>
 __global__ void __launch_bounds__(PT) panel_apply_kernel(const ApplyParams p) {
+    dependency_wait();
     __shared__ float Vt[32][33], Ti[32][33], Bi[32][33], X[32][33], M[32][33];
     const int t = threadIdx.x;
     const uint32_t blk = blockIdx.x;
@@ -645,22 +651,22 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
             return true;
         }();
         (void)configured;
-        if (rpt == 1) panel_leaf_cols_kernel<32><<<leaves, PT, 0, stream>>>(lp);
-        else panel_leaf_cols_kernel<64><<<leaves, PT, 0, stream>>>(lp);
-        if (leaves * 32 <= PT) panel_top_cols_kernel<32><<<1, PT, 32 * 256 * sizeof(float), stream>>>(tp);
-        else panel_top_cols_kernel<64><<<1, PT, 32 * 512 * sizeof(float), stream>>>(tp);
+        if (rpt == 1) launch_dependent(panel_leaf_cols_kernel<32>, leaves, PT, 0, stream, lp);
+        else launch_dependent(panel_leaf_cols_kernel<64>, leaves, PT, 0, stream, lp);
+        if (leaves * 32 <= PT) launch_dependent(panel_top_cols_kernel<32>, 1, PT, 32 * 256 * sizeof(float), stream, tp);
+        else launch_dependent(panel_top_cols_kernel<64>, 1, PT, 32 * 512 * sizeof(float), stream, tp);
     } else {
-        if (rpt == 1) panel_leaf_kernel<1><<<leaves, PT, 0, stream>>>(lp);
-        else if (rpt == 2) panel_leaf_kernel<2><<<leaves, PT, 0, stream>>>(lp);
-        else panel_leaf_kernel<4><<<leaves, PT, 0, stream>>>(lp);
-        if (leaves * 32 <= PT) panel_top_kernel<1><<<1, PT, 0, stream>>>(tp);
-        else panel_top_kernel<2><<<1, PT, 0, stream>>>(tp);
+        if (rpt == 1) launch_dependent(panel_leaf_kernel<1>, leaves, PT, 0, stream, lp);
+        else if (rpt == 2) launch_dependent(panel_leaf_kernel<2>, leaves, PT, 0, stream, lp);
+        else launch_dependent(panel_leaf_kernel<4>, leaves, PT, 0, stream, lp);
+        if (leaves * 32 <= PT) launch_dependent(panel_top_kernel<1>, 1, PT, 0, stream, tp);
+        else launch_dependent(panel_top_kernel<2>, 1, PT, 0, stream, tp);
     }
-    panel_finish_kernel<<<1, PT, 0, stream>>>(tp);
+    launch_dependent(panel_finish_kernel, 1, PT, 0, stream, tp);
     ApplyParams ap{Vl, Tl, Bp, y, ldy, mp, jb, lr};
-    if (rpt == 1) panel_apply_kernel<1><<<leaves, PT, 0, stream>>>(ap);
-    else if (rpt == 2) panel_apply_kernel<2><<<leaves, PT, 0, stream>>>(ap);
-    else panel_apply_kernel<4><<<leaves, PT, 0, stream>>>(ap);
+    if (rpt == 1) launch_dependent(panel_apply_kernel<1>, leaves, PT, 0, stream, ap);
+    else if (rpt == 2) launch_dependent(panel_apply_kernel<2>, leaves, PT, 0, stream, ap);
+    else launch_dependent(panel_apply_kernel<4>, leaves, PT, 0, stream, ap);
     cuda_check(cudaGetLastError(), "panel launch");
 }
 

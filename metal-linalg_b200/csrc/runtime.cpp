@@ -1,6 +1,7 @@
 // Per-GPU contexts, the calling thread's stream and device, workspaces.
 #include "runtime.h"
 
+#include <cstdlib>
 #include <memory>
 #include <new>
 #include <vector>
@@ -12,6 +13,14 @@ void cuda_check(cudaError_t e, const char* what) {
     cudaGetLastError();   // clear the sticky-less error so the next call starts clean
     if (e == cudaErrorMemoryAllocation) throw std::bad_alloc();
     throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+bool dependent_launches_enabled() {
+    static const bool v = [] {
+        const char* e = std::getenv("QR_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return v;
 }
 
 int device_count() {
@@ -71,6 +80,24 @@ DeviceContext& context(int device) {
         g_contexts[device] = std::move(c);
     }
     return *g_contexts[device];
+}
+
+DeviceContext::Lane& DeviceContext::lane(int i) {
+    Lane& l = lanes[i];
+    if (!l.update) {
+        DeviceGuard guard(device);
+        int least = 0, greatest = 0;
+        cuda_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
+        cuda_check(cudaStreamCreateWithFlags(&l.update, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithPriority(&l.panel, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        for (int k = 0; k < 2; ++k) {
+            cuda_check(cudaEventCreateWithFlags(&l.ev_panel[k], cudaEventDisableTiming), "cudaEventCreate");
+            cuda_check(cudaEventCreateWithFlags(&l.ev_update[k], cudaEventDisableTiming), "cudaEventCreate");
+        }
+        cuda_check(cudaEventCreateWithFlags(&l.ev_done, cudaEventDisableTiming), "cudaEventCreate");
+        if (!ev_fork) cuda_check(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming), "cudaEventCreate");
+    }
+    return l;
 }
 
 void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) {

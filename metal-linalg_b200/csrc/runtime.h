@@ -37,6 +37,16 @@ struct DeviceContext {
     // the blocked QR's second stream (trailing updates beside the next panels) and its events
     cudaStream_t   aux = nullptr;
     cudaEvent_t    ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr};
+    // further pairs of streams for a batch of large matrices, factored several at a time (the first
+    // matrix of a round runs on the caller's stream and `aux`); created on first use
+    struct Lane {
+        cudaStream_t update = nullptr, panel = nullptr;
+        cudaEvent_t  ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr}, ev_done = nullptr;
+    };
+    static constexpr int kExtraLanes = 3;
+    Lane           lanes[kExtraLanes];
+    cudaEvent_t    ev_fork = nullptr;
+    Lane&          lane(int i);         // i < kExtraLanes
 
     // At least `bytes` of device scratch for work on `stream`, 256-byte aligned,
     // kept for later calls. Growing it waits for the GPU (cudaFree does).
@@ -45,6 +55,25 @@ struct DeviceContext {
 
 int            device_count();
 DeviceContext& context(int device);   // created on first use; throws without a GPU
+
+// Launches `kernel`, whose first statement is dependency_wait() (common.cuh), so that it may be
+// brought onto the multiprocessors while the kernel before it in the stream still runs
+// (programmatic stream serialization). QR_NO_PDL=1 in the environment makes it an ordinary launch.
+bool dependent_launches_enabled();
+template <typename... Params, typename... Args>
+void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launches_enabled() ? 1 : 0;
+    cuda_check(cudaLaunchKernelEx(&cfg, kernel, Params(args)...), "cudaLaunchKernelEx");
+}
 
 // The calling thread's stream (device-pointer calls) and device (host-pointer calls).
 cudaStream_t thread_stream();

@@ -21,6 +21,7 @@
 // mbarrier; the accumulator (128 lanes x 128 columns of tensor memory) is read back with
 // tcgen05.ld for the epilogue. Every wait on an mbarrier is bounded: a wait that runs out sets
 // an error word, and the block frees its tensor memory and returns.
+#include "common.cuh"
 #include "kernels.h"
 
 #include <cuda_runtime.h>
@@ -145,6 +146,7 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity) {
 }
 
 __global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
+    dependency_wait_only();
     extern __shared__ __align__(1024) char smem[];
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ uint32_t tmem_base_slot;
@@ -333,7 +335,7 @@ void launch_tc_ytc(cudaStream_t stream, const float* Y, size_t ldy, const float*
     configure();
     TcParams p{Y, C, zp, ldy, ldc, ncp, kw, nc, mp, chunk_rows, 0, error};
     const dim3 grid((nc + 127) / 128, (mp + chunk_rows - 1) / chunk_rows);
-    tc_gemm_kernel<<<grid, TCT, kTcSmem, stream>>>(p);
+    launch_dependent(tc_gemm_kernel, grid, TCT, kTcSmem, stream, p);
     cuda_check(cudaGetLastError(), "tc_ytc launch");
 }
 
@@ -343,7 +345,7 @@ void launch_tc_yz(cudaStream_t stream, const float* Y, size_t ldy, const float* 
     configure();
     TcParams p{Y, Z, C, ldy, ncp, ldc, mp, nc, kw, 0, 1, error};
     const dim3 grid((nc + 127) / 128, (mp + 127) / 128);
-    tc_gemm_kernel<<<grid, TCT, kTcSmem, stream>>>(p);
+    launch_dependent(tc_gemm_kernel, grid, TCT, kTcSmem, stream, p);
     cuda_check(cudaGetLastError(), "tc_yz launch");
 }
 
