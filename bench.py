@@ -287,7 +287,7 @@ def run_ours(args, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "of": peak_kind,
                      "traffic": (MEASURED_TRAFFIC_PER_MATRIX * BATCH if MEASURED_TRAFFIC_PER_MATRIX else None),
-                     "kernel": "qr_small_kernel<32,32>", "algorithmic_bytes_per_launch": BATCH * BYTES_PER_MATRIX},
+                     "kernel": "qr_small_kernel<32,16,2,true>", "algorithmic_bytes_per_launch": BATCH * BYTES_PER_MATRIX},
         "clocks": clocks,
         "check": {"recon_max": recon, "orth_max": orth, "tolerance": workloads.tolerance(COLS)},
     }
@@ -354,6 +354,10 @@ def other_configs(torch, mlt, _lib, workloads, args):
         steps=min(args.steps, 5))
     add("c5b_8192x8192 (one of the eight matrices: one per GPU)",
         torch.rand(1, 8192, 8192, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=2)
+    add("c5a_4096x4096 x 8 (a batch: several matrices at a time)",
+        torch.rand(8, 4096, 4096, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=2)
+    add("c5b_8192x8192 x 8 (the whole configuration on one GPU)",
+        torch.rand(8, 8192, 8192, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=1)
     return out
 
 
