@@ -143,14 +143,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, min_blocks(R, C)) qr_small_ker
 }
 
 template <int R, int G, int C, bool Square>
-void launch(cudaStream_t stream, const SmallParams& p) {
+void launch(cudaStream_t stream, const SmallParams& p, int sm_count) {
     constexpr int per_warp = 32 / G;
     constexpr int steps = R < G * C ? R : G * C;
-    static const int warps_per_block = [] {
+    static const int max_warps = [] {
         const char* e = std::getenv("QR_SMALL_WARPS");
         const int w = e ? std::atoi(e) : kMaxWarps;
         return w >= 1 && w <= kMaxWarps ? w : kMaxWarps;
     }();
+    // a small batch in smaller blocks, so that it reaches every multiprocessor
+    int warps_per_block = max_warps;
+    while (warps_per_block > 1 && (p.batch + per_warp * warps_per_block - 1) / (per_warp * warps_per_block) < 2u * sm_count)
+        warps_per_block /= 2;
     const uint32_t per_block = per_warp * warps_per_block;
     const uint32_t blocks = (p.batch + per_block - 1) / per_block;
     const size_t smem = (size_t)per_block * slot_floats(R, steps) * sizeof(float);
@@ -196,14 +200,17 @@ void launch_qr_small(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p
     int C = forced_columns_a_lane() ? forced_columns_a_lane() : 2;
     while (C > 1 && cap / C < 4) C /= 2;
     if (cap == 8 && !forced_columns_a_lane()) C = 1;
+    // a batch too small to give every multiprocessor a warp at two columns a lane: one column a lane
+    // (twice the warps, each half as long)
+    if (!forced_columns_a_lane() && C == 2 && (uint64_t)pr.batch * (cap / 2) < (uint64_t)32 * 4 * ctx.sm_count) C = 1;
     const int G = cap / C;
     const bool square = pr.m == pr.n && (int)pr.m == R && cap == R && pr.rr == pr.m && (pr.qc == 0 || pr.qc == pr.m);
 #define MLB_SMALL(RR, GG, CC)                                                    \
     if (R == RR && G == GG && C == CC) {                                         \
         if constexpr (RR == GG * CC) {                                           \
-            if (square) launch<RR, GG, CC, true>(stream, p);                     \
-            else launch<RR, GG, CC, false>(stream, p);                           \
-        } else launch<RR, GG, CC, false>(stream, p);                             \
+            if (square) launch<RR, GG, CC, true>(stream, p, ctx.sm_count);       \
+            else launch<RR, GG, CC, false>(stream, p, ctx.sm_count);             \
+        } else launch<RR, GG, CC, false>(stream, p, ctx.sm_count);               \
     }
 #define MLB_SMALL_ROWS(RR)                                                                        \
     MLB_SMALL(RR, 8, 1) MLB_SMALL(RR, 16, 1) MLB_SMALL(RR, 32, 1) /* one column a lane */        \
