@@ -638,6 +638,30 @@ void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T
     cuda_check(cudaGetLastError(), "inner update launch");
 }
 
+// A square n x n row-major matrix transposed in place: a block swaps the 32 x 32 tile (bx, by) with
+// the tile (by, bx), through shared memory (by <= bx; the others leave at once).
+__global__ void __launch_bounds__(256) transpose_inplace_kernel(float* a, uint32_t n) {
+    __shared__ float t0[32][33], t1[32][33];
+    const uint32_t bx = blockIdx.x, by = blockIdx.y;
+    if (by > bx) return;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (uint32_t r = ty; r < 32; r += 8) {
+        const uint32_t i0 = by * 32 + r, j0 = bx * 32 + tx;      // tile (by, bx)
+        t0[r][tx] = (i0 < n && j0 < n) ? a[(size_t)i0 * n + j0] : 0.0f;
+        const uint32_t i1 = bx * 32 + r, j1 = by * 32 + tx;      // tile (bx, by)
+        t1[r][tx] = (i1 < n && j1 < n) ? a[(size_t)i1 * n + j1] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t r = ty; r < 32; r += 8) {
+        const uint32_t i0 = by * 32 + r, j0 = bx * 32 + tx;
+        if (i0 < n && j0 < n) a[(size_t)i0 * n + j0] = t1[tx][r];
+        const uint32_t i1 = bx * 32 + r, j1 = by * 32 + tx;
+        if (bx != by && i1 < n && j1 < n) a[(size_t)i1 * n + j1] = t0[tx][r];
+    }
+}
+
 unsigned grid_for(size_t count) { return (unsigned)std::min<size_t>((count + 255) / 256, 148 * 8); }
 
 } // namespace
@@ -740,6 +764,18 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
             cuda_check(cudaEventRecord(ev_update[1], us), "cudaEventRecord");        // the working copy is ready
             cuda_check(cudaStreamWaitEvent(ps, ev_update[1], 0), "cudaStreamWaitEvent");
         }
+        // A square Q is accumulated FORWARD, beside the panels: P = Q^T = H_{K-1}^T ... H_0^T I takes each
+        // aggregate's reflectors from the left as soon as they are formed (the same product as the
+        // trailing update's, on all m columns), on the update stream, which the chain of panels leaves
+        // idle most of the time; Q is P transposed in place at the end. It costs 2 m^3 flops where the
+        // backward accumulation below costs 4/3 m^3, but those ran after the last panel with nothing
+        // beside them (3 of 17 ms at 4096 x 4096; 15.2 ms with the forward accumulation). Not for a batch
+        // of matrices beyond 4096 rows, whose lanes keep the update streams full already (four 8192 x
+        // 8192: 34 ms a matrix backward, 38 ms forward). Orthogonality at 4096 x 4096 by 3xTF32: 8e-4
+        // against 4e-4 backward (bound 4.9e-3): every entry of P takes every aggregate's update.
+        // QR_BACKWARD_Q=1 keeps the backward accumulation.
+        const bool forward_q = two && qc == m && (nlanes == 1 || m <= 4096) && std::getenv("QR_BACKWARD_Q") == nullptr;
+        if (forward_q) launch_fill_identity(us, Q, 1, m, m);
         for (uint32_t ag = 0; ag < naggs; ++ag) {
             const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0, pans = (wa + NB - 1) / NB;
             for (uint32_t pp = 0; pp < pans; ++pp) {
@@ -781,6 +817,14 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                     apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
                                     W + (size_t)j0 * ldw + j0 + wa + next, ldw, ma, wa, right - next, Zp2, Z2, &info->bad);
                 cuda_check(cudaEventRecord(ev_update[ag & 1], us), "cudaEventRecord");
+                if (forward_q)
+                    apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                    Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad);
+            } else if (forward_q) {      // the last aggregate: nothing right of it, but P takes it too
+                cuda_check(cudaEventRecord(ev_panel[ag & 1], ps), "cudaEventRecord");
+                cuda_check(cudaStreamWaitEvent(us, ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
+                apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad);
             }
         }
         if (two) {   // the caller's stream joins the panel stream
@@ -790,12 +834,17 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
         if (!qc) continue;
 
-        // backward: Q = H_0 ... H_{K-1} [I; 0], an aggregate at a time
-        launch_fill_identity(stream, Q, 1, m, qc);
-        for (uint32_t ag = naggs; ag-- > 0;) {
-            const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0;
-            apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, false,
-                            Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad);
+        if (forward_q) {
+            const uint32_t tiles = (m + 31) / 32;
+            transpose_inplace_kernel<<<dim3(tiles, tiles), 256, 0, stream>>>(Q, m);
+        } else {
+            // backward: Q = H_0 ... H_{K-1} [I; 0], an aggregate at a time
+            launch_fill_identity(stream, Q, 1, m, qc);
+            for (uint32_t ag = naggs; ag-- > 0;) {
+                const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0;
+                apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, false,
+                                Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad);
+            }
         }
         nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);
     }

@@ -196,12 +196,16 @@ def test_blocked_kernel_shapes(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
-@pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1"])
+@pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
+                                    "QR_NO_PDL=1"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
-    the tensor cores, one stream instead of look-ahead, the general tree for every panel."""
+    the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
+    backward instead of forward, panels with a row per thread instead of a column per lane, ordinary
+    launches instead of programmatic dependent ones (QR_NO_PDL is read once per process: it takes
+    effect only when set before the first call)."""
     rng = np.random.default_rng(16)
-    a = rng.standard_normal((1, 900, 700)).astype(np.float32)
+    a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
     name, value = switch.split("=")
     os.environ[name] = value
@@ -213,6 +217,28 @@ def test_blocked_fallback_paths(switch):
     assert harness.r_parity(r1, r0) <= 1e-4
     _, r_ref = harness.oracle_qr(a)
     assert harness.r_parity(r1, r_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(256, 256), (200, 64), (250, 300), (300, 96)])
+def test_mid_panel_paths(shape):
+    """The mid kernel's panels of at most 256 rows with a column per lane (the default) and a thread per
+    entry (QR_MID_ROWS=1; panels above 256 rows always) give the same factorisation."""
+    m, n = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((5, m, n)).astype(np.float32)
+    a[3] = 1.5                                   # constant: rank one, every later reflector the identity
+    q0, r0 = gpu_qr(a, "reduced", kernel="mid")
+    os.environ["QR_MID_ROWS"] = "1"
+    try:
+        q1, r1 = gpu_qr(a, "reduced", kernel="mid")
+    finally:
+        os.environ.pop("QR_MID_ROWS", None)
+    check(a, q0, r0, "reduced")
+    check(a, q1, r1, "reduced")
+    good = [0, 1, 2, 4]
+    assert harness.r_parity(r0[good], r1[good]) <= 1e-4
+    _, r_ref = harness.oracle_qr(a[good])
+    assert harness.r_parity(r0[good], r_ref) <= 1e-4
 
 
 def test_blocked_panels_taller_than_the_register_kernels():
