@@ -41,7 +41,7 @@ BYTES_PER_MATRIX = 3 * ROWS * COLS * 4   # A read, Q and R written
 # DRAM bytes per matrix of the small kernel from the ncu capture summarised in
 # profiles/qr_small_32x32_batch65536.md: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on
 # 65 536 matrices / 65 536 = (268.51 MB + 477.52 MB) / 65 536. Traffic grows in proportion to the batch.
-MEASURED_TRAFFIC_PER_MATRIX = 11383
+MEASURED_TRAFFIC_PER_MATRIX = 11785
 FALLBACK_HBM_GBS = 6650.0
 
 
