@@ -39,14 +39,15 @@ struct TunedRow {
     unsigned    crossover_small_batch, crossover_large_batch, batch_threshold;
     unsigned    large_min_k, large_max_batch;
 };
-// Measured 2026-11 (CUDA events, N(0,1) matrices, batches 1..256). The block-per-matrix kernel takes
-// the same time for 1 as for 148 matrices: one k x k matrix 0.15 / 0.59 / 1.95 / 4.3 / 13.4 / 29.9 ms
-// at k = 128 / 256 / 384 / 512 / 768 / 1024. The grid-parallel QR takes 0.39 / 0.79 / 1.2 / 1.6 / 2.5 /
-// 3.4 ms for one and factors a batch up to four at a time, about 1.25 times that for 4 matrices and
-// 4.6 times for 16. It wins from sqrt(M k) of about 340 sqrt(max(1, batch / 3.5)). Beyond 1024 rows
-// a block cannot hold the matrix.
+// Measured 2026-11 by tuning/tune_qr.py (tuning/results/nvidia-b200: 235 (shape, batch) points, two
+// passes, shuffled; noise 0.2 % median). The block-per-matrix kernel takes the same time for 1 as for
+// 148 matrices (one k x k matrix: 0.15 / 0.61 / 1.95 / 4.3 / 13.4 / 29.9 ms at k = 128 / 256 / 384 /
+// 512 / 768 / 1024); the grid-parallel QR takes 0.39 / 0.78 / 1.2 / 1.6 / 2.5 / 3.4 ms for one and
+// factors a batch several at a time. The rule sqrt(M k) >= L sqrt(max(1, batch / 2)) fitted on two
+// thirds of the shapes gives L = 240 (flat from 200 to 360): geometric-mean regret 1.013 there,
+// 1.005 on the held-out third (worst point 1.29). Beyond 1024 rows a block cannot hold the matrix.
 constexpr TunedRow kTuned[] = {
-    {"NVIDIA B200", 148, 1025, 1025, 16, 340, 0},
+    {"NVIDIA B200", 148, 1025, 1025, 16, 240, 0},
 };
 
 bool env_value(const char* name, unsigned& out) {
@@ -127,11 +128,10 @@ QrBackend qr_gpu_backend(unsigned m, unsigned n, unsigned batch) {
     const unsigned k = std::min(m, n);
     const unsigned crossover = batch < p.batch_threshold ? p.m_crossover_small_batch : p.m_crossover_large_batch;
     if (k >= crossover) return QrBackend::streaming_reduced;
-    // the large clause on sqrt(M k), which grows with the batch: the grid-parallel QR takes a batch
-    // three or four matrices at a time, the block-per-matrix kernel a whole wave of matrices at once
+    // the large clause on sqrt(M k), which grows with the batch: the grid-parallel QR takes a batch a
+    // few matrices at a time, the block-per-matrix kernel a whole wave of matrices at once
     const unsigned long long L = p.gpu_large_min_k;
-    const unsigned long long b7 = std::max(7u, 2u * std::max(1u, batch));      // 7 max(1, batch / 3.5)
-    if (L && (unsigned long long)m * k * 7 >= L * L * b7 &&
+    if (L && (unsigned long long)m * k * 2 >= L * L * std::max(2u, batch) &&      // sqrt(M k) >= L sqrt(max(1, batch / 2))
         (p.gpu_large_max_batch == 0 || batch <= p.gpu_large_max_batch))
         return QrBackend::streaming_reduced;
     return QrBackend::unblocked;
@@ -180,11 +180,12 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     if (small) return QrKernel::small;
     const bool spread = qr_gpu_backend(m, n, batch) == QrBackend::streaming_reduced;
     if (mid && !spread) return QrKernel::mid;
-    // a lone tall thin matrix is faster through the blocked QR's register-resident panels (one
-    // 8192 x 128: 0.62 ms against 3.4 ms; 2048 x 32: a tie) where those hold its rows; a batch goes to
-    // the tree (16 of 8192 x 128: 4.4 ms against 9.6 ms)
-    const bool lone = batch == 1 && (uint64_t)m * std::min(m, n) >= 256 * 256 && mlb::panel_fast_fits(m, 1) &&
-                      mlb::qr_blocked_fits(m, n);
+    // a lone tall thin matrix is faster through the blocked QR's register-resident panels where those
+    // hold its rows (8192 x 128: 0.64 ms against 3.5 ms; 2048 x 32: 0.16 against 0.18), and so are two of
+    // 64 columns (4096 x 64: 0.59 against 0.73) or four of 128 (2.4 against 3.5); a batch goes to the
+    // tree (16 of 8192 x 128: 4.5 ms against 9.7 ms)
+    const uint32_t few = n >= 128 ? 4u : n >= 64 ? 2u : 1u;
+    const bool lone = batch <= few && mlb::panel_fast_fits(m, 1) && mlb::qr_blocked_fits(m, n);
     if (tsqr && !lone) return QrKernel::tsqr;
     if (mid && !mlb::qr_blocked_fits(m, n)) return QrKernel::mid;
     return QrKernel::blocked;
