@@ -20,10 +20,11 @@ import torch
 
 from . import _lib, _ops  # noqa: F401  (_ops registers torch.ops.metal_linalg.qr)
 from ._build import version as __version__
+from ._interop import qr_dlpack, qr_into, qr_shapes
 from ._sharded import qr_sharded, shard_batch
 
 __all__ = [
-    "qr", "qr_sharded", "shard_batch",
+    "qr", "qr_sharded", "shard_batch", "qr_into", "qr_dlpack", "qr_shapes",
     "device_name", "gpu_core_count", "device_count", "cpu_threads", "set_cpu_threads",
     "cpu_only", "set_cpu_only", "CpuOnly",
     "qr_backend", "qr_kernel", "qr_policy", "set_qr_policy", "qr_policy_source",

@@ -135,3 +135,33 @@ def test_binding_rejects_and_shapes():
     assert q.shape == (2, 5, 5) and r.shape == (2, 5, 3) and q.dtype == torch.float32
     q, r = torch.ops.metal_linalg.qr(torch.zeros(2, 3, 5, device="meta"), "r")
     assert q.shape == (0,) and r.shape == (2, 3, 5)
+
+
+def test_interop_shapes_and_argument_checks():
+    """qr_into's checks need no GPU: shapes per mode, dtype, contiguity, missing interface."""
+    assert mlt.qr_shapes((5, 7, 3)) == ((5, 7, 3), (5, 3, 3))
+    assert mlt.qr_shapes((7, 3), "complete") == ((7, 7), (7, 3))
+    assert mlt.qr_shapes((2, 2, 3, 7), "r") == (None, (2, 2, 3, 7))
+    with pytest.raises(ValueError):
+        mlt.qr_shapes((3,))
+    with pytest.raises(ValueError):
+        mlt.qr_shapes((3, 3), "full")
+
+    class Fake:
+        def __init__(self, shape, typestr="<f4", strides=None, ptr=4096):
+            self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3,
+                                             "strides": strides}
+
+    with pytest.raises(TypeError, match="__cuda_array_interface__"):
+        mlt.qr_into(torch.zeros(2, 2), Fake((2, 2)), Fake((2, 2)))
+    with pytest.raises(TypeError, match="float32"):
+        mlt.qr_into(Fake((4, 3), "<f8"), Fake((4, 3)), Fake((3, 3)))
+    with pytest.raises(ValueError, match="C-contiguous"):
+        mlt.qr_into(Fake((4, 3), strides=(4, 16)), Fake((4, 3)), Fake((3, 3)))
+    with pytest.raises(ValueError, match="expected shape"):
+        mlt.qr_into(Fake((4, 3)), Fake((4, 4)), Fake((3, 3)))
+    with pytest.raises(ValueError, match="None exactly"):
+        mlt.qr_into(Fake((4, 3)), Fake((4, 3)), Fake((3, 3)), mode="r")
+    # an empty batch is a no-op and touches no pointer
+    q, r = Fake((0, 4, 3), ptr=0), Fake((0, 3, 3), ptr=0)
+    assert mlt.qr_into(Fake((0, 4, 3), ptr=0), q, r) == (q, r)

@@ -657,3 +657,28 @@ def test_binding_threads():
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_interop_cuda_array_interface_and_dlpack():
+    """The C ABI through __cuda_array_interface__ (caller's buffers, the arrays' stream) and DLPack."""
+    rng = np.random.default_rng(23)
+    a = rng.standard_normal((6, 40, 24)).astype(np.float32)
+    t = torch.as_tensor(a).cuda()
+    for mode in ("reduced", "complete", "r"):
+        qs, rs = mlt.qr_shapes(t.shape, mode)
+        q = None if qs is None else torch.empty(qs, device="cuda")
+        r = torch.empty(rs, device="cuda")
+        mlt.qr_into(t, q, r, mode=mode)
+        torch.cuda.synchronize()
+        _, r_ref = harness.oracle_qr(a, mode)
+        check(a, None if q is None else q.cpu().numpy(), r.cpu().numpy(), mode, r_ref)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        q, r = torch.empty(6, 40, 24, device="cuda"), torch.empty(6, 24, 24, device="cuda")
+        mlt.qr_into(t, q, r, stream=side.cuda_stream)
+    side.synchronize()
+    check(a, q.cpu().numpy(), r.cpu().numpy(), "reduced")
+    _lib.lib.metal_linalg_set_stream(None)
+    Q, R = mlt.qr_dlpack(t)
+    torch.cuda.synchronize()
+    check(a, Q.cpu().numpy(), R.cpu().numpy(), "reduced")
