@@ -20,6 +20,8 @@
 // kept unnormalised, H = I - g v v^T with v = (alpha - beta; tail).
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace mlb {
 namespace small {
 
@@ -111,6 +113,16 @@ __host__ __device__ constexpr int slot_floats(int R, int steps) {
 }
 __host__ __device__ constexpr int steps_of(int R, int G, int C) { return R < G * C ? R : G * C; }
 
+// f(integral_constant<int, 0>) ... f(integral_constant<int, N - 1>): a loop whose index is a constant
+// in the body (for the steps, whose register indices must be)
+template <int N, int I = 0, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<N, I + 1>(f);
+    }
+}
+
 // 1. The largest magnitude of the group's matrix (a NaN or an Inf anywhere makes it non-finite),
 // and the matrix scaled into [0.5, 1). A non-finite matrix is computed on as it is (nothing
 // traps); its outputs are made NaN by the scale of R and the start value of Q.
@@ -161,28 +173,34 @@ __device__ __forceinline__ void factor(pair_t (&x2)[C][R / 2], float* slot, int 
     constexpr int NQ = R / 4;              // 16-byte words per column
     ulonglong2* V = reinterpret_cast<ulonglong2*>(slot);   // [kSteps][NQ] words
     float* Vg = slot + kSteps * R;
+    // the owner of column jn writes its tail (rows > jn; zeros in the rows <= jn of the first word)
+    auto publish = [&](auto jn_c) {
+        constexpr int jn = decltype(jn_c)::value;
+        constexpr int cn = jn / G, q0n = jn / 4, en = jn & 3;
+        if (l == jn % G) {
 #pragma unroll
-    for (int j = 0; j < kSteps; ++j) {
-        if (j < K) {
-            const int cj = j / G;          // the owner's column among its lane's
-            const int q0 = j / 4;          // the word that holds row j
-            const int qt = (j + 1) / 4;    // first word that holds a row > j
-            const int e  = j & 3;
-            const bool owner = l == j % G;
-            if (owner) {
-#pragma unroll
-                for (int q = q0; q < NQ; ++q) {
-                    pair_t a = x2[cj][2 * q], b = x2[cj][2 * q + 1];
-                    if (q == q0) {         // zeros in rows <= j
-                        if (e == 0) a = pack(0.0f, hi_of(a));
-                        else if (e == 1) a = pack(0.0f, 0.0f);
-                        else if (e == 2) { a = pack(0.0f, 0.0f); b = pack(0.0f, hi_of(b)); }
-                        else { a = pack(0.0f, 0.0f); b = pack(0.0f, 0.0f); }
-                    }
-                    V[j * NQ + q] = make_ulonglong2(a, b);
+            for (int q = q0n; q < NQ; ++q) {
+                pair_t a = x2[cn][2 * q], b = x2[cn][2 * q + 1];
+                if (q == q0n) {
+                    if (en == 0) a = pack(0.0f, hi_of(a));
+                    else if (en == 1) a = pack(0.0f, 0.0f);
+                    else if (en == 2) { a = pack(0.0f, 0.0f); b = pack(0.0f, hi_of(b)); }
+                    else { a = pack(0.0f, 0.0f); b = pack(0.0f, 0.0f); }
                 }
+                V[jn * NQ + q] = make_ulonglong2(a, b);
             }
-            __syncwarp();
+        }
+    };
+    if (0 < K) publish(std::integral_constant<int, 0>{});
+    __syncwarp();
+    static_for<kSteps>([&](auto j_c) {
+        constexpr int j = decltype(j_c)::value;
+        if (j < K) {
+            constexpr int cj = j / G;          // the owner's column among its lane's
+            constexpr int q0 = j / 4;          // the word that holds row j
+            constexpr int qt = (j + 1) / 4;    // first word that holds a row > j
+            constexpr int e  = j & 3;
+            const bool owner = l == j % G;
             ulonglong2 u[NQ];
 #pragma unroll
             for (int q = qt; q < NQ; ++q) u[q] = V[j * NQ + q];
@@ -217,8 +235,7 @@ __device__ __forceinline__ void factor(pair_t (&x2)[C][R / 2], float* slot, int 
             else if (e == 1) w0.x = pack(0.0f, v1);
             else if (e == 2) w0.y = pack(v1, hi_of(w0.y));
             else w0.y = pack(0.0f, v1);
-#pragma unroll
-            for (int c = cj; c < C; ++c) {
+            auto update = [&](int c) {
                 const float  t  = fmaf(v1, xj[c], d[c]) * gneg;
                 const pair_t t2 = pack(t, t);
                 if (e < 2) x2[c][2 * q0] = fma2(t2, w0.x, x2[c][2 * q0]);
@@ -228,9 +245,20 @@ __device__ __forceinline__ void factor(pair_t (&x2)[C][R / 2], float* slot, int 
                     x2[c][2 * q]     = fma2(t2, u[q].x, x2[c][2 * q]);
                     x2[c][2 * q + 1] = fma2(t2, u[q].y, x2[c][2 * q + 1]);
                 }
+            };
+            // the next owner's column first, so that its tail is on its way to shared memory while
+            // the other columns are updated
+            constexpr int jn = j + 1, cn = jn < kSteps ? jn / G : C;
+            if (cn < C) update(cn);
+            if (jn < kSteps) {
+                if (jn < K) publish(std::integral_constant<int, (jn < kSteps ? jn : 0)>{});
             }
+#pragma unroll
+            for (int c = cj; c < C; ++c)
+                if (c != cn) update(c);
+            __syncwarp();
         }
-    }
+    });
     __syncwarp();      // the last v1 and -g are in shared memory before the Q pass reads them
 }
 
