@@ -558,6 +558,72 @@ __global__ void __launch_bounds__(PT, 1) panel_top_cols_kernel(const TopParams p
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// The whole panel in ONE launch: a thread-block cluster whose blocks hold 8 * RW rows each, the
+// column steps' sums exchanged through distributed shared memory (cols::ClusterSync). This is
+// LAPACK's own Householder panel (no row blocks, no tree, no reconstruction): out come R (into the
+// working copy's upper triangle), Y with its unit diagonal, and T. Up to 8 blocks of 512 rows
+// (4096 rows) with the portable cluster size, 16 blocks (8192 rows) with the non-portable one.
+// ---------------------------------------------------------------------------
+struct ClusterPanelParams {
+    float*   panel;     // the panel's first entry in the working copy: in the panel, out R
+    size_t   ldw;
+    float*   y;         // the panel's first entry in Y
+    size_t   ldy;
+    float*   t;         // [32][32] out
+    uint32_t mp, jb;
+};
+
+template <int RW>
+__global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanelParams p) {
+    using namespace cols;
+    dependency_wait();
+    __shared__ __align__(16) cols::Smem s;
+    __shared__ __align__(16) cols::ClusterShared cs;
+    __shared__ __align__(16) float pub[kWarps * RW];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t rank = cluster_rank(), ncta = cluster_size();
+    const uint32_t row0 = (rank * kWarps + warp) * RW;
+    pair_t x2[RW / 2];
+#pragma unroll
+    for (int i = 0; i < RW / 2; ++i) {
+        const uint32_t ra = row0 + 2 * i;
+        float a = 0.0f, b = 0.0f;
+        if ((uint32_t)lane < p.jb) {
+            if (ra < p.mp) a = p.panel[(size_t)ra * p.ldw + lane];
+            if (ra + 1 < p.mp) b = p.panel[(size_t)(ra + 1) * p.ldw + lane];
+        }
+        x2[i] = pack(a, b);
+    }
+    cluster_barrier();          // every block of the cluster is running before any writes into another's shared memory
+    float my_sc;
+    factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
+    __syncthreads();
+    if (rank == 0 && warp == 0) {
+        // T straight to global memory; rows and columns from jb on are zero (their reflectors are the identity)
+        build_t_to(s, p.t, 32);
+        // the first 32 rows: R into the working copy, the reflectors with a unit diagonal into Y
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const float v = s.rows[r][lane];
+            if ((uint32_t)lane < p.jb && (uint32_t)r < p.mp) {
+                if (lane >= r) p.panel[(size_t)r * p.ldw + lane] = v;
+                p.y[(size_t)r * p.ldy + lane] = r > lane ? v * my_sc : (r == lane ? 1.0f : 0.0f);
+            }
+        }
+    }
+    if ((uint32_t)lane < p.jb) {
+        const bool first = rank == 0 && warp == 0;       // its rows below 32 (64 rows a lane) are ordinary rows
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const uint32_t row = row0 + r;
+            if ((!first || r >= 32) && row < p.mp) p.y[(size_t)row * p.ldy + lane] = row_of<RW>(x2, r) * my_sc;
+        }
+    }
+    cluster_barrier();          // no block leaves while another could still write into its shared memory
+}
+
 struct ApplyParams {
     const float* Vl;        // [leaves][lr][32]
     const float* Tl;        // [leaves][32][32]
@@ -639,6 +705,30 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     // a column per lane up to 8192 rows; a row per thread beyond, and for both with QR_PANEL_ROWS=1
     const char* env = std::getenv("QR_PANEL_ROWS");
     const bool by_columns = rpt <= 2 && !(env && env[0] == '1');
+    // up to 4096 rows the whole panel in one cluster launch (QR_PANEL_CLUSTER=0: the tree of row blocks)
+    const char* envc = std::getenv("QR_PANEL_CLUSTER");
+    if (by_columns && mp <= 4096 && !(envc && envc[0] == '0')) {
+        const uint32_t rw = mp <= 2048 ? 32 : 64;
+        uint32_t ncta = 1;
+        while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4 or 8 blocks; blocks beyond the rows hold zeros
+        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb};
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(ncta);
+        cfg.blockDim = dim3(PT);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = ncta;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = dependent_launches_enabled() ? 2 : 1;
+        if (rw == 32) cuda_check(cudaLaunchKernelEx(&cfg, panel_cluster_kernel<32>, cp), "panel_cluster launch");
+        else cuda_check(cudaLaunchKernelEx(&cfg, panel_cluster_kernel<64>, cp), "panel_cluster launch");
+        return;
+    }
     LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
     TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp, Rt};
     if (by_columns) {

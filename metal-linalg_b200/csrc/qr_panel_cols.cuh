@@ -62,13 +62,87 @@ __device__ __forceinline__ float recip(float x) {
 // __syncthreads()).
 __device__ __forceinline__ void step_barrier(int threads) { asm volatile("bar.sync 1, %0;" :: "r"(threads) : "memory"); }
 
+// How the partial products of a step become the sums over all rows.
+//
+// BlockSync: the rows are held by the first nw warps of ONE block: a named barrier, then every warp
+// adds up the nw partial products.
+struct BlockSync {
+    int nw;
+    __device__ __forceinline__ bool pivot(int warp) const { return warp == 0; }      // the warp that holds the triangle
+    __device__ __forceinline__ bool leader(int warp) const { return warp == 0; }     // the warp that records tau, sc and G
+    __device__ __forceinline__ void exchange(Smem& s, int buf, int lane, int warp) const {
+        (void)s; (void)buf; (void)lane; (void)warp;
+        step_barrier(32 * nw);
+    }
+    __device__ __forceinline__ float total(const Smem& s, int buf, int lane) const {
+        float d = s.red[buf][0][lane];
+        for (int w = 1; w < nw; ++w) d += s.red[buf][w][lane];
+        return d;
+    }
+};
+
+// ClusterSync: the rows are held by the eight warps of each block of a thread-block CLUSTER (block
+// `rank` of `ncta` holds rows rank * 8 RW ...). After the block's barrier every warp adds up the
+// block's eight partial products and stores the sum into the shared memory of two of the blocks
+// (distributed shared memory: mapa + st.shared::cluster); block 0 sends the pivot row along. One
+// cluster barrier (a hardware barrier: arrive.release / wait.acquire) makes them visible, and every
+// warp adds up the ncta block sums. The buffers alternate with the step's parity, and a block reads
+// a step's sums before it arrives at the next step's cluster barrier, so nothing is overwritten early.
+constexpr int kMaxCluster = 16;
+struct ClusterShared {
+    float cred[2][kMaxCluster][32];      // the blocks' sums, by step parity
+};
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a float into the same place of block `rank`'s shared memory
+__device__ __forceinline__ void store_to_block(const float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(remote), "f"(v) : "memory");
+}
+struct ClusterSync {
+    uint32_t       rank, ncta;
+    ClusterShared* cs;
+    __device__ __forceinline__ bool pivot(int warp) const { return rank == 0 && warp == 0; }
+    __device__ __forceinline__ bool leader(int warp) const { return rank == 0 && warp == 0; }
+    __device__ __forceinline__ void exchange(Smem& s, int buf, int lane, int warp) const {
+        step_barrier(32 * kWarps);
+        float d = s.red[buf][0][lane];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) d += s.red[buf][w][lane];
+        for (uint32_t r = warp; r < ncta; r += kWarps) {
+            store_to_block(&cs->cred[buf][rank][lane], r, d);
+            if (rank == 0 && r != 0) store_to_block(&s.prow[buf][lane], r, s.prow[buf][lane]);
+        }
+        cluster_barrier();
+    }
+    __device__ __forceinline__ float total(const Smem& s, int buf, int lane) const {
+        (void)s;
+        float d = cs->cred[buf][0][lane];
+        for (uint32_t r = 1; r < ncta; ++r) d += cs->cred[buf][r][lane];
+        return d;
+    }
+};
+
 // What every warp does after the step barrier: the block's sums, the reflector (the same numbers
 // in every warp), the Gram entries and tau. Returns t, the coefficient of this lane's update
 // (0 for the columns left of j, which keep their reflectors), and v1, alpha.
-__device__ __forceinline__ float step_reflector(Smem& s, int j, int buf, int lane, int warp, int nw, float& my_sc,
-                                                float& v1, float& alpha) {
-    float d = s.red[buf][0][lane];
-    for (int w = 1; w < nw; ++w) d += s.red[buf][w][lane];
+template <typename Sync>
+__device__ __forceinline__ float step_reflector(Smem& s, int j, int buf, int lane, int warp, const Sync& sync,
+                                                float& my_sc, float& v1, float& alpha) {
+    const float d = sync.total(s, buf, lane);
     const float xj = s.prow[buf][lane];
     alpha = s.prow[buf][j];
     const float ss = __shfl_sync(0xffffffffu, d, j);
@@ -76,7 +150,7 @@ __device__ __forceinline__ float step_reflector(Smem& s, int j, int buf, int lan
     fast_reflector(alpha, ss, v1, gneg);
     const float sv  = fmaf(v1, xj, d);                    // u^T (this lane's column), u = (v1; tail)
     const float scj = gneg != 0.0f ? recip(v1) : 0.0f;
-    if (warp == 0) {
+    if (sync.leader(warp)) {
         if (lane < j) s.G[lane][j] = sv * my_sc * scj;
         if (lane == 0) {
             s.taus[j] = -gneg * v1 * v1;
@@ -92,9 +166,9 @@ __device__ __forceinline__ float step_reflector(Smem& s, int j, int buf, int lan
 // one), and after the odd step the two finished rows leave for s.rows and the pairs move up one
 // place (zeros come in at the end), so the step loop is not unrolled, every register index is a
 // constant and the code stays small enough to be fetched once and run from the instruction cache.
-template <int RW, int P>
-__device__ __forceinline__ void step_warp0(pair_t (&x2)[RW / 2], Smem& s, ulonglong2* pj, int it, int lane, int nw,
-                                           float& my_sc) {
+template <int RW, int P, typename Sync>
+__device__ __forceinline__ void step_warp0(pair_t (&x2)[RW / 2], Smem& s, ulonglong2* pj, int it, int lane,
+                                           const Sync& sync, float& my_sc) {
     constexpr int NQ = RW / 4, NP = RW / 2;
     const int j = 2 * it + P, buf = P;
     const pair_t zero2 = pack(0.0f, 0.0f);
@@ -120,9 +194,9 @@ __device__ __forceinline__ void step_warp0(pair_t (&x2)[RW / 2], Smem& s, ulongl
         s.red[buf][0][lane] = hsum2(s2, s2b);
     }
     s.prow[buf][lane] = P == 0 ? lo_of(x2[0]) : hi_of(x2[0]);
-    step_barrier(32 * nw);
+    sync.exchange(s, buf, lane, 0);
     float v1, alpha;
-    const float  t  = step_reflector(s, j, buf, lane, 0, nw, my_sc, v1, alpha);
+    const float  t  = step_reflector(s, j, buf, lane, 0, sync, my_sc, v1, alpha);
     const pair_t t2 = pack(t, t);
     const pair_t w0 = P == 0 ? pack(v1, hi_of(u[0].x)) : pack(0.0f, v1);    // the reflector's first pair: v1 in the pivot's row
     pair_t head = fma2(t2, w0, x2[0]);
@@ -147,19 +221,20 @@ __device__ __forceinline__ void step_warp0(pair_t (&x2)[RW / 2], Smem& s, ulongl
 // Afterwards: s.rows[r][c] holds the block's first 32 rows, R on and above the diagonal and the
 // reflectors' tails below it; warp 0's rotating pairs are zero, its other rows (RW = 64) and every
 // other warp's hold the tails of their rows; my_sc of lane l is s.sc[l].
-// nw: the warps that hold rows (the first nw; the others do not take part and may not call).
-template <int RW, bool Keep>
+// sync: BlockSync{nw} (the first nw warps of the block hold rows; the others do not take part and may
+// not call) or ClusterSync (all eight warps of every block of the cluster).
+template <int RW, bool Keep, typename Sync>
 __device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float* pub, float* keep, float& my_sc,
-                                            int nw = kWarps) {
+                                            const Sync& sync) {
     constexpr int NQ = RW / 4;           // 16-byte words of a warp's piece of a column
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     my_sc = 0.0f;
-    if (warp == 0) {
+    if (sync.pivot(warp)) {
         ulonglong2* pj = reinterpret_cast<ulonglong2*>(pub);
 #pragma unroll 1
         for (int it = 0; it < 16; ++it) {
-            step_warp0<RW, 0>(x2, s, pj, it, lane, nw, my_sc);
-            step_warp0<RW, 1>(x2, s, pj, it, lane, nw, my_sc);
+            step_warp0<RW, 0>(x2, s, pj, it, lane, sync, my_sc);
+            step_warp0<RW, 1>(x2, s, pj, it, lane, sync, my_sc);
         }
     } else {
 #pragma unroll 1
@@ -184,9 +259,9 @@ __device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float
                 }
                 s.red[buf][warp][lane] = hsum2(s2, s2b);
             }
-            step_barrier(32 * nw);
+            sync.exchange(s, buf, lane, warp);
             float v1, alpha;
-            const float  t  = step_reflector(s, j, buf, lane, warp, nw, my_sc, v1, alpha);
+            const float  t  = step_reflector(s, j, buf, lane, warp, sync, my_sc, v1, alpha);
             const pair_t t2 = pack(t, t);
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
@@ -195,6 +270,12 @@ __device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float
             }
         }
     }
+}
+
+template <int RW, bool Keep>
+__device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float* pub, float* keep, float& my_sc,
+                                            int nw = kWarps) {
+    factor_cols<RW, Keep>(x2, s, pub, keep, my_sc, BlockSync{nw});
 }
 
 // T from s.G and s.taus (slarft's forward recurrence) by one warp, a row of T per lane, to
