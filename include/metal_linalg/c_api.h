@@ -166,7 +166,7 @@ typedef struct metal_linalg_qr_policy {
     uint32_t gpu_min_batch;
     uint32_t gpu_cores;                 /* informational: multiprocessors */
     uint32_t concurrent_matrices;       /* informational: thread blocks of the mid kernel resident at once */
-    uint32_t gpu_large_min_k;           /* a matrix is spread over the grid also from sqrt(rows k) >= this x sqrt(max(1, batch / 2)) */
+    uint32_t gpu_large_min_k;           /* a matrix is spread over the grid also from sqrt(rows k) >= this x sqrt(max(1, batch / 3)) */
     uint32_t gpu_large_max_batch;       /* (0: never) in a batch of at most this (0: any) */
     uint32_t gpu_min_k;                 /* without effect */
     uint32_t share_min_batch;           /* without effect (no CPU to share a batch with) */

@@ -45,7 +45,7 @@ namespace metal_linalg {
     //                       matrix, the TSQR tree ("tsqr")
     //
     // streaming_reduced iff k >= m_crossover_* (by batch), or sqrt(M k) >=
-    // gpu_large_min_k sqrt(max(1, batch / 2)) in a batch of at most
+    // gpu_large_min_k sqrt(max(1, batch / 3)) in a batch of at most
     // gpu_large_max_batch (the grid-parallel kernels factor a batch a few
     // matrices at a time, so the size from which they win grows with it), or the matrix is
     // beyond what a thread block holds. The reference's GPU-or-CPU fields

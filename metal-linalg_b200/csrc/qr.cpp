@@ -43,11 +43,13 @@ struct TunedRow {
 // passes, shuffled; noise 0.2 % median). The block-per-matrix kernel takes the same time for 1 as for
 // 148 matrices (one k x k matrix: 0.15 / 0.61 / 1.95 / 4.3 / 13.4 / 29.9 ms at k = 128 / 256 / 384 /
 // 512 / 768 / 1024); the grid-parallel QR takes 0.39 / 0.78 / 1.2 / 1.6 / 2.5 / 3.4 ms for one and
-// factors a batch several at a time. The rule sqrt(M k) >= L sqrt(max(1, batch / 2)) fitted on two
-// thirds of the shapes gives L = 240 (flat from 200 to 360): geometric-mean regret 1.013 there,
-// 1.005 on the held-out third (worst point 1.29). Beyond 1024 rows a block cannot hold the matrix.
+// factors a batch several at a time (those were its times before its panels became one cluster
+// launch; it is about a quarter faster now). The rule sqrt(M k) >= L sqrt(max(1, batch / F)) fitted
+// on two thirds of the shapes is flat over L = 200 ... 250 and F = 2.5 ... 4; L = 220, F = 3 is taken:
+// geometric-mean regret 1.013 on the training shapes, 1.02 on the held-out third. Beyond 1024 rows
+// a block cannot hold the matrix.
 constexpr TunedRow kTuned[] = {
-    {"NVIDIA B200", 148, 1025, 1025, 16, 240, 0},
+    {"NVIDIA B200", 148, 1025, 1025, 16, 220, 0},
 };
 
 bool env_value(const char* name, unsigned& out) {
@@ -131,7 +133,7 @@ QrBackend qr_gpu_backend(unsigned m, unsigned n, unsigned batch) {
     // the large clause on sqrt(M k), which grows with the batch: the grid-parallel QR takes a batch a
     // few matrices at a time, the block-per-matrix kernel a whole wave of matrices at once
     const unsigned long long L = p.gpu_large_min_k;
-    if (L && (unsigned long long)m * k * 2 >= L * L * std::max(2u, batch) &&      // sqrt(M k) >= L sqrt(max(1, batch / 2))
+    if (L && (unsigned long long)m * k * 3 >= L * L * std::max(3u, batch) &&      // sqrt(M k) >= L sqrt(max(1, batch / 3))
         (p.gpu_large_max_batch == 0 || batch <= p.gpu_large_max_batch))
         return QrBackend::streaming_reduced;
     return QrBackend::unblocked;

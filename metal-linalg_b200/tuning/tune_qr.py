@@ -43,7 +43,7 @@ BATCHES = [1, 2, 4, 8, 16, 32, 64, 128]
 THIN = [(2048, 32), (4096, 64), (8192, 64), (8192, 128), (16384, 32)]       # tsqr against blocked
 THIN_BATCHES = [1, 2, 4, 16]
 MAX_ELEMENTS = 96 << 20          # batch * M * N of one point
-LIBRARY_F = 2.0                  # the batch divisor in the library's rule (csrc/qr.cpp: qr_gpu_backend)
+LIBRARY_F = 3.0                  # the batch divisor in the library's rule (csrc/qr.cpp: qr_gpu_backend)
 
 
 def shapes():

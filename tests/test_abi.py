@@ -94,8 +94,8 @@ def test_policy_round_trip_and_routing():
         assert mlt.qr_backend(8192, 64, 5) == "unblocked"              # beyond gpu_large_max_batch
         assert mlt.qr_backend(4000, 64, 1) == "unblocked"
         mlt.set_qr_policy(gpu_large_min_k=512, gpu_large_max_batch=0)
-        assert mlt.qr_backend(8192, 64, 4) == "streaming_reduced"      # 8192 * 64 >= 512^2 * 4 / 2
-        assert mlt.qr_backend(8192, 64, 5) == "unblocked"              # the size grows with the batch
+        assert mlt.qr_backend(8192, 64, 6) == "streaming_reduced"      # 8192 * 64 >= 512^2 * 6 / 3
+        assert mlt.qr_backend(8192, 64, 7) == "unblocked"              # the size grows with the batch
         # fields the GPU-only build carries without using are read back as set
         mlt.set_qr_policy(gpu_max_k=0, share_min_batch=5)
         assert mlt.qr_policy()["gpu_max_k"] == 0 and mlt.qr_policy()["share_min_batch"] == 5
