@@ -84,6 +84,14 @@ void launch_tc_ytc(cudaStream_t stream, const float* Y, size_t ldy, const float*
                    uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, unsigned* error);
 void launch_tc_yz(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
                   uint32_t mp, uint32_t kw, uint32_t nc, unsigned* error);
+// The same with Y and Z split into their tf32 parts once, ahead of the product, and fetched by bulk
+// asynchronous copies (tc_gemm2.cu); ysp and zsp: scratch of tc_split_floats(mp) and tc_split_floats(nc) floats.
+size_t tc_split_floats(uint32_t extent);
+size_t tc_split_t_floats(uint32_t rows);
+void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp,
+                         uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, float* ytsp, unsigned* error);
+void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
+                        uint32_t mp, uint32_t kw, uint32_t nc, float* ysp, float* zsp, unsigned* error);
 
 // Blocked compact-WY QR over the whole grid, any shape.
 bool qr_blocked_fits(uint32_t m, uint32_t n);

@@ -465,8 +465,11 @@ constexpr size_t kReduceWideSmem = (128 * 132 + 128 * 36) * sizeof(float);
 constexpr size_t kMergeSmem = (2 * 128 * 129 + 96 * 33) * sizeof(float);
 
 // C (mp rows, nc columns) <- (I - Y op(T) Y^T) C for an aggregate: Y mp x kw (kw <= 128), T 128 x 128.
+// ysp, zsp: scratch for the split operands of a wide update's second product (null: the product splits
+// its operands as it goes; QR_TC_SPLIT=0 asks for that everywhere).
 void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const float* T, bool transposed, float* C,
-                     size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z, unsigned* error) {
+                     size_t ldc, uint32_t mp, uint32_t kw, uint32_t nc, float* zp, float* z, unsigned* error,
+                     float* ysp = nullptr, float* zsp = nullptr, float* ytsp = nullptr) {
     if (nc == 0 || mp == 0) return;
     const uint32_t ncp = (nc + 3) & ~3u;
     const bool tc = use_tensor_cores();
@@ -474,11 +477,16 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const bool narrow = tc && nc <= 256;
     const uint32_t rows = narrow ? 128u : tc ? 256u : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
     const uint32_t chunks = (mp + rows - 1) / rows;
-    if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
+    // QR_TC_SPLIT=0: the products whose blocks split their operands as they load them
+    const char* split_env = std::getenv("QR_TC_SPLIT");
+    const bool split = tc && !narrow && ysp && zsp && ytsp && !(split_env && split_env[0] == '0');
+    if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, ytsp, error);
+    else if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
     if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 256, 0, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
+    if (split) launch_tc_yz_split(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, ysp, zsp, error);
+    else if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
     else launch_dependent(yz_wide_kernel, dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc);
     cuda_check(cudaGetLastError(), "aggregate reflector launch");
 }
@@ -693,6 +701,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_zp = take(zp_floats);
     const size_t o_z = take((size_t)AG * ncp);
     const size_t o_zp2 = take(zp_floats), o_z2 = take((size_t)AG * ncp);   // the second stream's
+    const size_t o_ysp = take(tc_split_floats(m)), o_zsp = take(tc_split_floats(ncp)), o_ytsp = take(tc_split_t_floats(m));   // split operands of the wide updates
     const size_t o_info = take(64);
     size_t tsqr_floats = 0;
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
@@ -743,6 +752,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         float* ws = ws_all + (size_t)ln * off;
         float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
         float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
+        float *Ysp = ws + o_ysp, *Zsp = ws + o_zsp, *Ytsp = ws + o_ytsp;
         MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
 
         cuda_check(cudaMemsetAsync(info, 0, sizeof(MatInfo), stream), "cudaMemsetAsync");
@@ -805,7 +815,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                                   Ta + (size_t)ag * AG * AG, Zp, &info->bad);
             if (right && !two) {
                 apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
-                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z, &info->bad);
+                                W + (size_t)j0 * ldw + j0 + wa, ldw, ma, wa, right, Zp, Z, &info->bad, Ysp, Zsp, Ytsp);
             } else if (right) {
                 const uint32_t next = std::min<uint32_t>(AG, right);
                 if (ag > 0) cuda_check(cudaStreamWaitEvent(ps, ev_update[(ag - 1) & 1], 0), "cudaStreamWaitEvent");
@@ -815,16 +825,17 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                 cuda_check(cudaStreamWaitEvent(us, ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
                 if (right > next)
                     apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
-                                    W + (size_t)j0 * ldw + j0 + wa + next, ldw, ma, wa, right - next, Zp2, Z2, &info->bad);
+                                    W + (size_t)j0 * ldw + j0 + wa + next, ldw, ma, wa, right - next, Zp2, Z2, &info->bad,
+                                    Ysp, Zsp, Ytsp);
                 cuda_check(cudaEventRecord(ev_update[ag & 1], us), "cudaEventRecord");
                 if (forward_q)
                     apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
-                                    Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad);
+                                    Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad, Ysp, Zsp, Ytsp);
             } else if (forward_q) {      // the last aggregate: nothing right of it, but P takes it too
                 cuda_check(cudaEventRecord(ev_panel[ag & 1], ps), "cudaEventRecord");
                 cuda_check(cudaStreamWaitEvent(us, ev_panel[ag & 1], 0), "cudaStreamWaitEvent");
                 apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
-                                Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad);
+                                Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad, Ysp, Zsp, Ytsp);
             }
         }
         if (two) {   // the caller's stream joins the panel stream
@@ -843,7 +854,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
             for (uint32_t ag = naggs; ag-- > 0;) {
                 const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0;
                 apply_aggregate(stream, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, false,
-                                Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad);
+                                Q + (size_t)j0 * qc + j0, qc, ma, wa, qc - j0, Zp, Z, &info->bad, Ysp, Zsp, Ytsp);
             }
         }
         nan_fill_kernel<<<grid_for((size_t)m * qc), 256, 0, stream>>>(Q, (size_t)m * qc, info);

@@ -197,13 +197,14 @@ def test_blocked_kernel_shapes(shape, mode):
 
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
-                                    "QR_NO_PDL=1"])
+                                    "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
     backward instead of forward, panels with a row per thread instead of a column per lane, ordinary
     launches instead of programmatic dependent ones (QR_NO_PDL is read once per process: it takes
-    effect only when set before the first call)."""
+    effect only when set before the first call), panels by the tree of row blocks instead of one
+    cluster launch, tensor-core products that split their operands in every block instead of once."""
     rng = np.random.default_rng(16)
     a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
