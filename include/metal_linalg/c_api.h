@@ -94,6 +94,33 @@ metal_linalg_status metal_linalg_qr_no_alloc(const float* a, uint32_t batch, uin
 uint64_t            metal_linalg_qr_no_alloc_scratch_bytes(void);
 
 /* ---------------------------------------------------------------------------
+ * SVD: the QR's first caller inside the library
+ * ------------------------------------------------------------------------- */
+
+/* include/metal_linalg/c_api.h:59-63. Thin SVD A = U diag(s) Vt with K =
+ * min(rows, cols): u [batch, rows, K], s [batch, K] descending, vt [batch, K,
+ * cols]; u and vt both NULL for the singular values alone; info [batch] or
+ * NULL. Pointers as for metal_linalg_qr: all on the host or all on one GPU.
+ * Of the reference's SVD backends this library holds the QR-preconditioned
+ * one alone (A = Q R by the QR above, then one-sided Jacobi on R), for K <= 32:
+ * a larger K fails with METAL_LINALG_INVALID_ARGUMENT. */
+metal_linalg_status metal_linalg_svd(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
+                                     float* u, float* s, float* vt, uint32_t* info);
+
+/* include/metal_linalg/c_api.h:96-102. An `info` word: bits 0-15 the sweeps
+ * taken, bit 16 converged, bit 17 the matrix held a NaN or an infinity (its
+ * outputs are all NaN), bit 18 rank-deficient. */
+#define METAL_LINALG_INFO_SWEEPS(info)         ((info) & 0xFFFFu)
+#define METAL_LINALG_INFO_CONVERGED(info)      (((info) >> 16) & 1u)
+#define METAL_LINALG_INFO_NONFINITE(info)      (((info) >> 17) & 1u)
+#define METAL_LINALG_INFO_RANK_DEFICIENT(info) (((info) >> 18) & 1u)
+
+/* include/metal_linalg/c_api.h:175-176. "qr_jacobi", or "unavailable" for a
+ * shape metal_linalg_svd refuses. The strings are static. */
+const char* metal_linalg_svd_backend(uint32_t rows, uint32_t cols, uint32_t batch);
+const char* metal_linalg_svdvals_backend(uint32_t rows, uint32_t cols, uint32_t batch);   /* values alone */
+
+/* ---------------------------------------------------------------------------
  * CUDA placement (no counterpart in the reference, whose memory is unified)
  * ------------------------------------------------------------------------- */
 

@@ -78,6 +78,13 @@ namespace metal_linalg {
     bool      qr_uses_gpu(unsigned m, unsigned n, unsigned batch);      // always true
     bool      qr_shares_batch(unsigned m, unsigned n, unsigned batch);  // always false
 
+    // The SVD's one backend here: the QR of this library, then one-sided Jacobi on the small factor
+    // (reference: SvdBackend, core.h:550-574, of which qr_jacobi is one of ten). `unavailable`: a shape
+    // beyond it (min(M, N) > 32), which core::svd refuses.
+    enum class SvdBackend { qr_jacobi, unavailable };
+    SvdBackend svd_backend(unsigned m, unsigned n, unsigned batch);
+    SvdBackend svdvals_backend(unsigned m, unsigned n, unsigned batch);
+
     namespace core {
 
         // `batch` matrices of rows x cols (reference: core.h:776-781).
@@ -107,6 +114,16 @@ namespace metal_linalg {
         // std::bad_alloc when device memory runs out.
         void qr(const Matrices& a, float* q, float* r, QrMode mode);
         void qr(const Matrices& a, float* q, float* r);   // QrMode::reduced
+
+        // Thin SVD A = U diag(s) Vt, K = min(M, N): u [batch, M, K], s [batch, K] descending,
+        // vt [batch, K, N]; u and vt both null for the singular values alone (then Q is never
+        // formed: the QR runs in mode r). info [batch] or null: bits 0-15 the sweeps taken, bit 16
+        // converged, bit 17 the matrix held a NaN or an infinity (its outputs are NaN), bit 18
+        // rank-deficient (reference: core.h:811-814, c_api.h:96-102). The QR-preconditioned route
+        // of the reference's svd_qr_jacobi (src/svd.mm:614-661), for min(M, N) <= 32; anything
+        // larger throws std::invalid_argument. Pointers as for qr: all on the host or all on one GPU.
+        void svd(const Matrices& a, float* u, float* s, float* vt, uint32_t* info = nullptr);
+        bool svd_fits(uint32_t m, uint32_t n);
 
         // The kernel a call of that shape and mode runs.
         enum class QrKernel { small, mid, tsqr, blocked };

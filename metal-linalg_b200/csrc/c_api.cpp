@@ -104,6 +104,22 @@ metal_linalg_status metal_linalg_qr_no_alloc(const float* a, uint32_t batch, uin
 
 uint64_t metal_linalg_qr_no_alloc_scratch_bytes(void) { return mlb::qr_mid_static_capacity_bytes(); }
 
+metal_linalg_status metal_linalg_svd(const float* a, uint32_t batch, uint32_t rows, uint32_t cols, float* u, float* s,
+                                     float* vt, uint32_t* info) {
+    return guarded([&] {
+        require(present(a, (uint64_t)batch * rows * cols), "[svd] a is NULL");
+        require(present(s, (uint64_t)batch * std::min(rows, cols)), "[svd] s is NULL");
+        require((u == nullptr) == (vt == nullptr), "[svd] u and vt must both be given or both be NULL");
+        core::svd({a, batch, rows, cols}, u, s, vt, info);
+    });
+}
+const char* metal_linalg_svd_backend(uint32_t rows, uint32_t cols, uint32_t batch) {
+    return svd_backend(rows, cols, batch) == SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+}
+const char* metal_linalg_svdvals_backend(uint32_t rows, uint32_t cols, uint32_t batch) {
+    return svdvals_backend(rows, cols, batch) == SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+}
+
 void  metal_linalg_set_stream(void* cuda_stream) { set_stream(cuda_stream); }
 void* metal_linalg_stream(void) { return stream(); }
 

@@ -100,4 +100,18 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
 // Small utilities shared by the launchers.
 void launch_fill_identity(cudaStream_t stream, float* q, uint32_t batch, uint32_t m, uint32_t cols);
 
+// The small SVD behind a QR (svd_small.cu): one-sided Jacobi on the k x k factors r [batch, k, k],
+// k <= 32. s [batch, k] descending; with ur non-null also the factors' left vectors ur [batch, k, k]
+// (as columns) and the right vectors v [batch, k, k] (V^T, or V itself with v_as_columns);
+// info [batch] or null. `effective_rows`: the rows of the matrix the factor came from (the rotation
+// tolerance is sqrt(max(rows, 64)) eps).
+bool svd_small_fits(uint32_t k);
+void launch_svd_small(cudaStream_t stream, const float* r, uint32_t batch, uint32_t k, uint32_t effective_rows,
+                      float* s, float* ur, float* v, bool v_as_columns, uint32_t* info);
+// out = Q U_R per matrix (q [batch, l, k], ur [batch, k, k]); out [batch, l, k], or [batch, k, l] when transposed.
+void launch_svd_left_vectors(cudaStream_t stream, const float* q, const float* ur, float* out, uint32_t batch, uint32_t l,
+                             uint32_t k, bool transposed);
+// out [batch, cols, rows] = in [batch, rows, cols] transposed.
+void launch_transpose_batched(cudaStream_t stream, const float* in, float* out, uint32_t batch, uint32_t rows, uint32_t cols);
+
 } // namespace mlb

@@ -5,6 +5,7 @@
 #include <metal_linalg/core.h>
 
 #include "kernels.h"
+#include "qr_enqueue.h"
 #include "runtime.h"
 
 #include <algorithm>
@@ -204,6 +205,14 @@ void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices&
         case QrKernel::blocked: mlb::launch_qr_blocked(ctx, stream, p); break;
     }
 }
+
+} // namespace
+
+void qr_enqueue(mlb::DeviceContext& ctx, cudaStream_t stream, const core::Matrices& a, float* q, float* r, core::QrMode mode) {
+    run_on_device(ctx, stream, a, q, r, mode, -1);
+}
+
+namespace {
 
 // Host pointers: the batch in chunks through two sets of device buffers, the
 // copy in of chunk i+1 and the copy out of chunk i-1 running beside the

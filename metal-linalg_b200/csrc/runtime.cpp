@@ -100,8 +100,8 @@ DeviceContext::Lane& DeviceContext::lane(int i) {
     return l;
 }
 
-void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) {
-    Workspace& w = workspaces[stream];
+namespace {
+void* grown(Workspace& w, int device, size_t bytes) {
     if (w.bytes < bytes) {
         DeviceGuard guard(device);
         if (w.data) cuda_check(cudaFree(w.data), "cudaFree");   // waits for the work that may still use it
@@ -112,6 +112,12 @@ void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) {
         w.bytes = want;
     }
     return w.data;
+}
+} // namespace
+
+void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) { return grown(workspaces[stream], device, bytes); }
+void* DeviceContext::outer_workspace(cudaStream_t stream, size_t bytes) {
+    return grown(outer_workspaces[stream], device, bytes);
 }
 
 cudaStream_t thread_stream() { return t_stream; }

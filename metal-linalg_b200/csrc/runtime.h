@@ -31,6 +31,7 @@ struct DeviceContext {
     std::string    name;
     std::mutex     mutex;               // held while a call enqueues on this GPU
     std::map<cudaStream_t, Workspace> workspaces;
+    std::map<cudaStream_t, Workspace> outer_workspaces;   // of a caller of the QR (the SVD), beside the QR's own
     cudaStream_t   copy_in = nullptr, copy_out = nullptr, compute = nullptr;   // host-pointer staging
     cudaEvent_t    ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr},
                    ev_out[2] = {nullptr, nullptr};
@@ -51,6 +52,8 @@ struct DeviceContext {
     // At least `bytes` of device scratch for work on `stream`, 256-byte aligned,
     // kept for later calls. Growing it waits for the GPU (cudaFree does).
     void* workspace(cudaStream_t stream, size_t bytes);
+    // The same for a routine that calls the QR on `stream` and needs scratch that outlives that call.
+    void* outer_workspace(cudaStream_t stream, size_t bytes);
 };
 
 int            device_count();

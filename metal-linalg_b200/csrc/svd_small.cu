@@ -1,0 +1,354 @@
+// The small SVD on the far side of the QR: Hestenes' one-sided Jacobi on the K x K triangular factor
+// of a QR-preconditioned SVD (reference: svd_qr_jacobi, src/svd.mm:614-661, whose inner kernel is
+// shaders/Svd_Jacobi.metal), K <= 32, and the product U = Q U_R that follows it.
+//
+// Layout: a matrix belongs to a group of R lanes (R = 4, 8, 16 or 32 >= K; 32 / R matrices a warp),
+// lane c holding column c of G (= the factor R, scaled by a power of two so that its largest entry
+// lies in [0.5, 1)) and column c of V in registers. A round pairs every column with one partner
+// (the circle method: R - 1 rounds visit every pair once); the partner's column comes by R
+// shuffles, both lanes of a pair form the same three inner products in the same order, hence the
+// same rotation, and each applies its own half. No shared memory, no barrier.
+//
+// The rules of the reference's kernel are kept: a pair is rotated iff |gamma| > tol sqrt(alpha beta)
+// with tol = sqrt(max(rows, 64)) eps; two numerically null columns (below 32 eps of the largest
+// column) are never rotated against each other, and a null column against another keeps the sweeps
+// going only while the angle is gross and the column not negligible; a sweep that rotates nothing
+// ends the solve; singular values descending (ties by column index); left vectors of null columns
+// are replaced by an orthonormal completion; a matrix with a NaN or an infinity gives NaN outputs;
+// info = sweeps | converged << 16 | non-finite << 17 | rank-deficient << 18.
+#include "common.cuh"
+#include "kernels.h"
+#include "runtime.h"
+
+#include <cfloat>
+
+namespace mlb {
+namespace {
+
+constexpr float kNullTol        = 32.0f * FLT_EPSILON;   // src/svd.mm:65
+constexpr float kNegligible     = 1.2e-7f;               // shaders/Svd_Jacobi.metal:82
+constexpr float kCleanCos       = 0.05f;                 // shaders/Svd_Jacobi.metal:78
+constexpr float kZetaAsymptotic = 1e15f;                 // shaders/Svd_Jacobi.metal:75
+
+struct SvdSmallParams {
+    const float* r;        // [batch, k, k] row-major
+    float*       s;        // [batch, k]
+    float*       ur;       // [batch, k, k] left vectors of the factor as columns, or null
+    float*       v;        // [batch, k, k]: V^T (row t = right vector t), or V itself when v_as_columns
+    uint32_t*    info;     // [batch] or null
+    uint32_t     batch, k;
+    uint32_t     max_sweeps;
+    float        tol;
+    int          v_as_columns;
+};
+
+template <int R>
+__device__ __forceinline__ float group_max(float v, unsigned mask) {
+#pragma unroll
+    for (int o = R / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o, R));
+    return v;
+}
+template <int R>
+__device__ __forceinline__ float group_sum(float v, unsigned mask) {
+#pragma unroll
+    for (int o = R / 2; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o, R);
+    return v;
+}
+
+// A fixed pseudo-random number in [-0.5, 0.5) for entry i of candidate `seed`.
+__device__ __forceinline__ float candidate_entry(uint32_t seed, uint32_t i) {
+    uint32_t x = seed * 0x9E3779B9u + i * 0x85EBCA6Bu + 0x27D4EB2Fu;
+    x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+    return (float)(x >> 8) * (1.0f / 16777216.0f) - 0.5f;
+}
+
+template <int R, bool Vectors>
+__global__ void __launch_bounds__(128) svd_small_kernel(const SvdSmallParams p) {
+    dependency_wait_only();
+    const int lane = threadIdx.x & 31, col = lane & (R - 1);
+    constexpr int kPerWarp = 32 / R;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t mat = warp * kPerWarp + (lane / R);
+    if (mat >= p.batch) return;      // a whole group leaves together
+    const unsigned mask = R == 32 ? 0xffffffffu : (((1u << (R & 31)) - 1u) << (lane & ~(R - 1)));
+    const uint32_t k = p.k;
+
+    float g[R], v[Vectors ? R : 1];
+    const float* src = p.r + (size_t)mat * k * k;
+    float amax = 0.0f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        g[i] = ((uint32_t)i < k && (uint32_t)col < k) ? src[i * k + col] : 0.0f;
+        bad |= nonfinite(g[i]);
+        amax = fmaxf(amax, fabsf(g[i]));
+    }
+    const bool nonfin = __ballot_sync(mask, bad) != 0;
+    amax = group_max<R>(amax, mask);
+    const int expo = nonfin ? 0 : amax_exponent(amax);
+    {
+        const Pow2 down(-expo);
+#pragma unroll
+        for (int i = 0; i < R; ++i) g[i] = down(g[i]);
+    }
+    if (Vectors) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) v[i] = i == col ? 1.0f : 0.0f;
+    }
+
+    uint32_t sweeps = 0;
+    bool converged = false;
+    while (!nonfin && sweeps < p.max_sweeps) {
+        float own = 0.0f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) own = fmaf(g[i], g[i], own);
+        const float cmax2 = group_max<R>(own, mask);
+        const float null2 = kNullTol * kNullTol * cmax2, negl2 = kNegligible * kNegligible * cmax2;
+        bool rotated = false;
+#pragma unroll 1
+        for (int round = 0; round < R - 1; ++round) {
+            // the circle method: columns i, j < R - 1 meet when i + j = round (mod R - 1); the one
+            // that would meet itself meets column R - 1
+            int partner;
+            if (col == R - 1) {
+                partner = (round * (R / 2)) % (R - 1);
+            } else {
+                partner = (round + (R - 1) - col) % (R - 1);
+                if (partner == col) partner = R - 1;
+            }
+            const bool lower = col < partner;
+            float pg[R];
+            float mine = 0.0f, theirs = 0.0f, gamma = 0.0f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                pg[i] = __shfl_sync(mask, g[i], partner, R);
+                mine = fmaf(g[i], g[i], mine);
+                theirs = fmaf(pg[i], pg[i], theirs);
+                gamma = fmaf(g[i], pg[i], gamma);
+            }
+            const float alpha = lower ? mine : theirs, beta = lower ? theirs : mine;   // of columns p < q
+            const float ab = alpha * beta;
+            // both lanes of a pair decide alike: they saw the same numbers. The updates below run for
+            // every pair, with the identity where nothing is rotated, so that the shuffles stay uniform.
+            const bool rotate = !(alpha <= null2 && beta <= null2) && fabsf(gamma) > p.tol * sqrtf(ab);
+            float c = 1.0f, cs = 0.0f;
+            if (rotate) {
+                const float zeta = (beta - alpha) / (2.0f * gamma);
+                float t;
+                if (fabsf(zeta) > kZetaAsymptotic) {
+                    t = 0.5f / zeta;
+                } else {
+                    t = 1.0f / (fabsf(zeta) + sqrtf(fmaf(zeta, zeta, 1.0f)));
+                    if (zeta < 0.0f) t = -t;
+                }
+                c = 1.0f / sqrtf(fmaf(t, t, 1.0f));
+                const float sn = c * t;
+                cs = lower ? -sn : sn;       // p: x' = c x - s y;   q: y' = s x + c y
+                const bool one_null = alpha <= null2 || beta <= null2;
+                if (!one_null) rotated = true;
+                else if (fminf(alpha, beta) > negl2 && gamma * gamma > kCleanCos * kCleanCos * ab) rotated = true;
+            }
+#pragma unroll
+            for (int i = 0; i < R; ++i) g[i] = fmaf(cs, pg[i], c * g[i]);
+            if (Vectors) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    const float other = __shfl_sync(mask, v[i], partner, R);
+                    v[i] = fmaf(cs, other, c * v[i]);
+                }
+            }
+        }
+        ++sweeps;
+        if (__ballot_sync(mask, rotated) == 0) { converged = true; break; }
+    }
+
+    // singular values, their order, the null threshold
+    float sig = 0.0f;
+#pragma unroll
+    for (int i = 0; i < R; ++i) sig = fmaf(g[i], g[i], sig);
+    sig = sqrtf(sig);
+    uint32_t rank = 0;
+#pragma unroll
+    for (int c = 0; c < R; ++c) {
+        const float sc = __shfl_sync(mask, sig, c, R);
+        rank += (sc > sig || (sc == sig && c < col)) ? 1u : 0u;
+    }
+    if (nonfin) rank = col;      // NaN compares false with everything
+    const float smax = group_max<R>(sig, mask);
+    const float thr = kNullTol * smax;
+    const bool real = (uint32_t)col < k;
+    const bool deficient = (__ballot_sync(mask, real && !(sig > thr)) != 0) && !nonfin;
+
+    const size_t kk = (size_t)k * k;
+    if (real) p.s[(size_t)mat * k + rank] = nonfin ? qnan() : Pow2(expo)(sig);
+    if (col == 0 && p.info)
+        p.info[mat] = sweeps | (converged ? 1u << 16 : 0u) | (nonfin ? 1u << 17 : 0u) | (deficient ? 1u << 18 : 0u);
+    if (!Vectors) return;
+
+    float* out_v = p.v + (size_t)mat * kk;
+    float* out_u = p.ur + (size_t)mat * kk;
+    if (nonfin) {
+        if (real)
+            for (uint32_t i = 0; i < k; ++i) { out_v[i * k + col] = qnan(); out_u[i * k + col] = qnan(); }
+        return;
+    }
+    if (real) {
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+            if ((uint32_t)i < k) out_v[p.v_as_columns ? (size_t)i * k + rank : (size_t)rank * k + i] = v[i];
+    }
+    // left vectors: the normalised columns; a null column is completed below
+    bool valid = real && sig > thr;
+    {
+        const float inv = valid ? 1.0f / sig : 0.0f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) g[i] *= inv;
+    }
+    if (deficient) {
+        // Every null column in turn takes a fixed pseudo-random vector made orthogonal (three
+        // passes) to the columns in place: any unit vector orthogonal to the others is a valid
+        // left vector there (reference: complete_columns_impl, src/svd.mm:148-186).
+        uint32_t seed = 1;
+        for (uint32_t c = 0; c < k; ++c) {
+            const bool needs = __shfl_sync(mask, valid ? 0 : 1, c, R) != 0;
+            if (!needs) continue;
+            for (int attempt = 0; attempt < 8; ++attempt, ++seed) {
+                float w[R];
+                float start = 0.0f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    w[i] = (uint32_t)i < k ? candidate_entry(seed, i) : 0.0f;
+                    start = fmaf(w[i], w[i], start);
+                }
+                for (int pass = 0; pass < 3; ++pass) {
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < R; ++i) dot = fmaf(g[i], w[i], dot);
+                    if (!valid) dot = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < R; ++i) w[i] -= group_sum<R>(dot * g[i], mask);
+                }
+                float nrm = 0.0f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) nrm = fmaf(w[i], w[i], nrm);
+                if (nrm > 1e-6f * start) {        // squares: a residual above 1e-3 of the start
+                    if (col == c) {
+                        const float inv = rsqrtf(nrm);
+#pragma unroll
+                        for (int i = 0; i < R; ++i) g[i] = w[i] * inv;
+                        valid = true;
+                    }
+                    break;
+                }
+            }
+        }
+    }
+    if (real) {
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+            if ((uint32_t)i < k) out_u[(size_t)i * k + rank] = g[i];
+    }
+}
+
+// out = Q U_R for every matrix: Q [batch, l, k] row-major, U_R [batch, k, k]; a thread a row of Q.
+// `transposed`: out is [batch, k, l] (the right vectors of a wide matrix), else [batch, l, k].
+template <int KP>
+__global__ void __launch_bounds__(256) svd_left_vectors_kernel(const float* __restrict__ q, const float* __restrict__ ur,
+                                                               float* __restrict__ out, uint32_t batch, uint32_t l, uint32_t k,
+                                                               int transposed) {
+    dependency_wait_only();
+    const size_t row = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= (size_t)batch * l) return;
+    const uint32_t b = (uint32_t)(row / l), i = (uint32_t)(row % l);
+    const float* qr = q + row * k;
+    const float* u = ur + (size_t)b * k * k;
+    float acc[KP];
+#pragma unroll
+    for (int j = 0; j < KP; ++j) acc[j] = 0.0f;
+    for (uint32_t t = 0; t < k; ++t) {
+        const float x = qr[t];
+#pragma unroll
+        for (int j = 0; j < KP; ++j)
+            if ((uint32_t)j < k) acc[j] = fmaf(x, u[t * k + j], acc[j]);
+    }
+    if (transposed) {
+        float* o = out + (size_t)b * k * l + i;
+#pragma unroll
+        for (int j = 0; j < KP; ++j)
+            if ((uint32_t)j < k) o[(size_t)j * l] = acc[j];
+    } else {
+        float* o = out + row * k;
+#pragma unroll
+        for (int j = 0; j < KP; ++j)
+            if ((uint32_t)j < k) o[j] = acc[j];
+    }
+}
+
+// out[b][j][i] = in[b][i][j]: in [batch, rows, cols].
+__global__ void __launch_bounds__(256) transpose_batched_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                                uint32_t rows, uint32_t cols) {
+    dependency_wait_only();
+    __shared__ float tile[32][33];
+    const size_t base = (size_t)blockIdx.z * rows * cols;
+    const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (uint32_t r = ty; r < 32; r += 8)
+        if (r0 + r < rows && c0 + tx < cols) tile[r][tx] = in[base + (size_t)(r0 + r) * cols + c0 + tx];
+    __syncthreads();
+    for (uint32_t c = ty; c < 32; c += 8)
+        if (c0 + c < cols && r0 + tx < rows) out[base + (size_t)(c0 + c) * rows + r0 + tx] = tile[tx][c];
+}
+
+template <int R>
+void launch_jacobi(cudaStream_t stream, const SvdSmallParams& p, bool vectors) {
+    const uint32_t per_block = 4 * (32 / R);
+    const uint32_t blocks = (p.batch + per_block - 1) / per_block;
+    if (vectors) launch_dependent(svd_small_kernel<R, true>, blocks, 128, 0, stream, p);
+    else launch_dependent(svd_small_kernel<R, false>, blocks, 128, 0, stream, p);
+}
+
+} // namespace
+
+bool svd_small_fits(uint32_t k) { return k >= 1 && k <= 32; }
+
+void launch_svd_small(cudaStream_t stream, const float* r, uint32_t batch, uint32_t k, uint32_t effective_rows,
+                      float* s, float* ur, float* v, bool v_as_columns, uint32_t* info) {
+    SvdSmallParams p{};
+    p.r = r; p.s = s; p.ur = ur; p.v = v; p.info = info;
+    p.batch = batch; p.k = k;
+    p.max_sweeps = 30;                                           // SvdOptions::max_sweeps, core.h:705
+    const float rows = (float)(effective_rows > 64u ? effective_rows : 64u);   // kMinEffectiveRows, src/svd.mm:60
+    p.tol = sqrtf(rows) * FLT_EPSILON;
+    p.v_as_columns = v_as_columns ? 1 : 0;
+    const bool vectors = ur != nullptr;
+    if (k <= 4) launch_jacobi<4>(stream, p, vectors);
+    else if (k <= 8) launch_jacobi<8>(stream, p, vectors);
+    else if (k <= 16) launch_jacobi<16>(stream, p, vectors);
+    else launch_jacobi<32>(stream, p, vectors);
+    cuda_check(cudaGetLastError(), "svd_small launch");
+}
+
+void launch_svd_left_vectors(cudaStream_t stream, const float* q, const float* ur, float* out, uint32_t batch, uint32_t l,
+                             uint32_t k, bool transposed) {
+    const size_t rows = (size_t)batch * l;
+    const uint32_t blocks = (uint32_t)((rows + 255) / 256);
+    const int t = transposed ? 1 : 0;
+    if (k <= 4) launch_dependent(svd_left_vectors_kernel<4>, blocks, 256, 0, stream, q, ur, out, batch, l, k, t);
+    else if (k <= 8) launch_dependent(svd_left_vectors_kernel<8>, blocks, 256, 0, stream, q, ur, out, batch, l, k, t);
+    else if (k <= 16) launch_dependent(svd_left_vectors_kernel<16>, blocks, 256, 0, stream, q, ur, out, batch, l, k, t);
+    else launch_dependent(svd_left_vectors_kernel<32>, blocks, 256, 0, stream, q, ur, out, batch, l, k, t);
+    cuda_check(cudaGetLastError(), "svd_left_vectors launch");
+}
+
+void launch_transpose_batched(cudaStream_t stream, const float* in, float* out, uint32_t batch, uint32_t rows, uint32_t cols) {
+    // the batch along z in slices of at most 65535
+    for (uint32_t b0 = 0; b0 < batch; b0 += 65535) {
+        const uint32_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
+        const size_t off = (size_t)b0 * rows * cols;
+        launch_dependent(transpose_batched_kernel, dim3((cols + 31) / 32, (rows + 31) / 32, nb), 256, 0, stream, in + off,
+                         out + off, rows, cols);
+    }
+    cuda_check(cudaGetLastError(), "transpose launch");
+}
+
+} // namespace mlb

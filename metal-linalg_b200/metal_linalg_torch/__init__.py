@@ -12,7 +12,8 @@ metal-linalg's torch binding (reference: python-torch/metal_linalg_torch/__init_
 the input's device. It supports autograd (torch.linalg's formula) and
 torch.compile: underneath it is the custom operator torch.ops.metal_linalg.qr.
 Computation is in float32: other real dtypes are converted, results are float32.
-Only QR exists in this build; the reference's other decompositions do not.
+Beside QR this build holds the SVD that calls it (`svd`, `svdvals`: the QR-preconditioned
+Jacobi route, min(M, N) <= 32); the reference's other decompositions do not exist here.
 """
 from collections import namedtuple
 
@@ -24,7 +25,7 @@ from ._interop import qr_dlpack, qr_into, qr_shapes
 from ._sharded import qr_sharded, shard_batch
 
 __all__ = [
-    "qr", "qr_sharded", "shard_batch", "qr_into", "qr_dlpack", "qr_shapes",
+    "qr", "svd", "svdvals", "svd_backend", "svdvals_backend", "qr_sharded", "shard_batch", "qr_into", "qr_dlpack", "qr_shapes",
     "device_name", "gpu_core_count", "device_count", "cpu_threads", "set_cpu_threads",
     "cpu_only", "set_cpu_only", "CpuOnly",
     "qr_backend", "qr_kernel", "qr_policy", "set_qr_policy", "qr_policy_source",
@@ -54,7 +55,8 @@ def _needs_grad(a):
     return torch.is_grad_enabled() and a.requires_grad
 
 
-_TRACED = {"linalg_qr": namedtuple("linalg_qr", ["Q", "R"])}
+_TRACED = {"linalg_qr": namedtuple("linalg_qr", ["Q", "R"]),
+           "linalg_svd": namedtuple("linalg_svd", ["U", "S", "Vh"])}
 
 
 def _result(kind, values):
@@ -85,6 +87,35 @@ def qr(A, mode="reduced"):
         return _result("linalg_qr", (R.new_empty(0), R))
     Q, R = torch.ops.metal_linalg.qr(a, mode)
     return _result("linalg_qr", (Q, R))
+
+
+def svd(A, full_matrices=False):
+    """Thin SVD of a batch of matrices, like ``torch.linalg.svd(A, full_matrices=False)``:
+    ``A = U @ diag(S) @ Vh`` with ``U`` ``[..., M, K]``, ``S`` ``[..., K]`` descending and ``Vh``
+    ``[..., K, N]``, ``K = min(M, N)`` (reference: python-torch/metal_linalg_torch/__init__.py:144-160).
+    ``full_matrices=True`` is refused, as by the reference. The route is A = Q R by this library's
+    QR, then one-sided Jacobi on R: ``K <= 32`` (a larger K raises ValueError)."""
+    if full_matrices:
+        raise NotImplementedError("metal_linalg_torch.svd: full_matrices=True is not supported; the thin "
+                                  "decomposition is what the library computes")
+    a = _prepare(A, "svd")
+    return _result("linalg_svd", torch.ops.metal_linalg.svd(a))
+
+
+def svdvals(A):
+    """The singular values alone, descending, like ``torch.linalg.svdvals``: the QR runs in mode "r",
+    so Q is never formed."""
+    a = _prepare(A, "svdvals")
+    return torch.ops.metal_linalg.svdvals(a)
+
+
+def svd_backend(m, n, batch=1):
+    """"qr_jacobi", or "unavailable" for a shape `svd` refuses."""
+    return _lib.lib.metal_linalg_svd_backend(m, n, batch).decode()
+
+
+def svdvals_backend(m, n, batch=1):
+    return _lib.lib.metal_linalg_svdvals_backend(m, n, batch).decode()
 
 
 # ---------------------------------------------------------------------------

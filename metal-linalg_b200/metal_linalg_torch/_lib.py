@@ -1,7 +1,7 @@
 """The C ABI through ctypes (reference: python-torch/metal_linalg_torch/_lib.py).
 
-Only the QR, device and policy entry points exist in this build, and only they
-are bound. The library is lib/libmetal_linalg.so beside this package, or the
+Only the QR, the SVD that calls it, and the device and policy entry points exist
+in this build, and only they are bound. The library is lib/libmetal_linalg.so beside this package, or the
 file METAL_LINALG_TORCH_LIBRARY names. Calls release the GIL (ctypes does); the
 C side keeps the stream and the device per thread, so no lock is needed here.
 """
@@ -40,6 +40,9 @@ def _load():
         "metal_linalg_qr_with_mode": (ctypes.c_int, [_ptr, _u32, _u32, _u32, ctypes.c_int, _ptr, _ptr]),
         "metal_linalg_qr_no_alloc": (ctypes.c_int, [_ptr, _u32, _u32, _u32, ctypes.c_int, _ptr, _ptr]),
         "metal_linalg_qr_no_alloc_scratch_bytes": (ctypes.c_uint64, []),
+        "metal_linalg_svd": (ctypes.c_int, [_ptr, _u32, _u32, _u32, _ptr, _ptr, _ptr, _ptr]),
+        "metal_linalg_svd_backend": (ctypes.c_char_p, [_u32, _u32, _u32]),
+        "metal_linalg_svdvals_backend": (ctypes.c_char_p, [_u32, _u32, _u32]),
         "metal_linalg_set_stream": (None, [_ptr]),
         "metal_linalg_stream": (_ptr, []),
         "metal_linalg_set_device": (ctypes.c_int, [ctypes.c_int]),
@@ -93,3 +96,10 @@ def qr(a, batch, rows, cols, q, r, mode="reduced", stream=None):
     if stream is not None:
         lib.metal_linalg_set_stream(stream)
     check(lib.metal_linalg_qr_with_mode(a, batch, rows, cols, MODES[mode], q, r))
+
+
+def svd(a, batch, rows, cols, u, s, vt, info=None, stream=None):
+    """metal_linalg_svd on addresses (ints; None for NULL: u and vt both, for the values alone)."""
+    if stream is not None:
+        lib.metal_linalg_set_stream(stream)
+    check(lib.metal_linalg_svd(a, batch, rows, cols, u, s, vt, info))

@@ -3,6 +3,7 @@ float64 checks the parity tests share. Imported by tests/, by the smoke check an
 by the bench's CPU-baseline leg; never by the product package.
 
   oracle_qr(a, mode)     the plain-C restatement, oracle/libqr_oracle.so
+  oracle_svd(a, vectors) the plain-C restatement of the QR-preconditioned Jacobi SVD, same library
   ref_qr(a, mode)        the reference's own src/qr_cpu.mm, oracle/_ref/libqr_cpu_ref.so
                          (None if that library was not built)
 
@@ -54,6 +55,9 @@ def _load_oracle():
         lib = ctypes.CDLL(path)
         lib.oracle_qr.restype = ctypes.c_int
         lib.oracle_qr.argtypes = [_f32p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, _f32p, _f32p]
+        _u32p = ctypes.POINTER(ctypes.c_uint32)
+        lib.oracle_svd.restype = ctypes.c_int
+        lib.oracle_svd.argtypes = [_f32p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, _f32p, _f32p, _f32p, _u32p]
         _oracle = lib
     return _oracle
 
@@ -96,6 +100,39 @@ def oracle_qr(a, mode="reduced"):
         if lib.oracle_qr(*args):
             raise MemoryError("oracle_qr")
     return _run(call, a, mode)
+
+
+def oracle_svd(a, vectors=True):
+    """(u, s, vt, info) of the thin SVD by the restatement; u and vt None without vectors."""
+    lib = _load_oracle()
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    *lead, m, n = a.shape
+    k = min(m, n)
+    batch = int(np.prod(lead)) if lead else 1
+    s = np.empty((*lead, k), np.float32)
+    info = np.zeros(tuple(lead) if lead else (1,), np.uint32)
+    u = np.empty((*lead, m, k), np.float32) if vectors else None
+    vt = np.empty((*lead, k, n), np.float32) if vectors else None
+    if lib.oracle_svd(_ptr(a), batch, m, n, _ptr(u), _ptr(s), _ptr(vt),
+                      info.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))):
+        raise MemoryError("oracle_svd")
+    return u, s, vt, info
+
+
+def svd_metrics(a, u, s, vt):
+    """Per matrix, in float64 on the unit-scale problem: ||A - U S Vt||_F / ||A||_F, ||U^T U - I||_F,
+    ||Vt Vt^T - I||_F (the reference's checks: tests/test_svd.cpp reconstruction and orthogonality)."""
+    a = np.asarray(a, np.float64)
+    u, s, vt = np.asarray(u, np.float64), np.asarray(s, np.float64), np.asarray(vt, np.float64)
+    scale = np.maximum(np.abs(a).max(axis=(-2, -1), keepdims=True), 1e-300)
+    an = a / scale
+    rec = np.linalg.norm(an - (u * (s / scale[..., 0])[..., None, :]) @ vt, axis=(-2, -1)) / \
+        np.maximum(np.linalg.norm(an, axis=(-2, -1)), 1e-300)
+    k = s.shape[-1]
+    eye = np.eye(k)
+    ou = np.linalg.norm(np.swapaxes(u, -1, -2) @ u - eye, axis=(-2, -1))
+    ov = np.linalg.norm(vt @ np.swapaxes(vt, -1, -2) - eye, axis=(-2, -1))
+    return rec, ou, ov
 
 
 def ref_qr(a, mode="reduced", threads=0):
