@@ -18,6 +18,7 @@ as N grows (weak scaling). Rank 0 prints one JSON line.
   cpu_baseline  the reference's own CPU path (src/qr_cpu.mm compiled into
              oracle/_ref; all host cores) on a bounded sample of the same workload
   others     (1 GPU only) the remaining benchmark configurations, each timed the same way
+  svd        (1 GPU only) the SVD that calls the QR, on tall and small batches
 
 --impl reference times the reference's CPU path alone, on the host cores.
 """
@@ -294,6 +295,7 @@ def run_ours(args, rank, world, local_rank):
 
     if world == 1 and not args.headline_only:
         line["others"] = other_configs(torch, mlt, _lib, workloads, args)
+        line["svd"] = svd_configs(torch, mlt, _lib, args)
         rate, cores, kind, best = cpu_reference(4096, 1)
         sample = int(min(BATCH, max(4096, rate * 3.0)))
         rate, cores, kind, best = cpu_reference(sample, 3)
@@ -358,6 +360,68 @@ def other_configs(torch, mlt, _lib, workloads, args):
         torch.rand(8, 4096, 4096, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=2)
     add("c5b_8192x8192 x 8 (the whole configuration on one GPU)",
         torch.rand(8, 8192, 8192, generator=g, device="cuda") * 2 - 1, "reduced", False, steps=1)
+    return out
+
+
+def svd_configs(torch, mlt, _lib, args):
+    """The SVD that calls the QR (min(M, N) <= 32), on one GPU: seconds per call by CUDA events through
+    the C ABI on device pointers, matrices/s, and GB/s from the algorithmic bytes (A read once; s, and with
+    vectors U and Vt, written once). Beside each, LAPACK's sgesdd (the routine the reference's CPU SVD calls)
+    on one host core over a bounded sample."""
+    import numpy as np
+    import scipy.linalg
+    out = []
+    g = torch.Generator(device="cuda").manual_seed(11)
+
+    def add(name, b, m, n, vectors):
+        try:
+            a = torch.randn(b, m, n, generator=g, device="cuda")
+            k = min(m, n)
+            s = torch.empty(b, k, device="cuda")
+            u = torch.empty(b, m, k, device="cuda") if vectors else None
+            vt = torch.empty(b, k, n, device="cuda") if vectors else None
+            info = torch.zeros(b, dtype=torch.int32, device="cuda")
+            stream = torch.cuda.current_stream().cuda_stream
+
+            def call():
+                _lib.svd(a.data_ptr(), b, m, n, u.data_ptr() if vectors else None, s.data_ptr(),
+                         vt.data_ptr() if vectors else None, info.data_ptr(), stream)
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            steps = max(2, min(args.steps, 5))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                call()
+            e1.record()
+            e1.synchronize()
+            sec = e0.elapsed_time(e1) / 1e3 / steps
+            ref = torch.linalg.svdvals(a[:64].double())
+            err = ((s[:64].double() - ref).abs().amax(-1) / torch.linalg.matrix_norm(a[:64].double())).max().item()
+            converged = bool(((info >> 16) & 1).all().item())
+            bytes_ = 4 * b * (m * n + k + ((m * k + k * n) if vectors else 0))
+            host = a[:max(1, min(b, 200000 // (m * n) + 1))].cpu().numpy()
+            t0 = time.perf_counter()
+            for x in host:
+                scipy.linalg.svd(x, compute_uv=vectors, full_matrices=False, lapack_driver="gesdd")
+            cpu = len(host) / (time.perf_counter() - t0)
+            out.append({"config": name, "vectors": vectors, "backend": mlt.svd_backend(m, n, b),
+                        "qr_kernel": mlt.qr_kernel(max(m, n), k, b, "reduced" if vectors else "r"),
+                        "batch": b, "rows": m, "cols": n, "ms": sec * 1e3, "matrices_per_s": b / sec,
+                        "gbs": bytes_ / sec / 1e9, "sval_err_max": err, "converged": converged,
+                        "cpu_sgesdd_matrices_per_s": cpu, "cpu_cores": 1, "cpu_sample": len(host)})
+            del a, s, u, vt
+        except Exception as e:
+            out.append({"config": name, "error": f"{type(e).__name__}: {e}"})
+        torch.cuda.synchronize()
+
+    add("svdvals 4096 x 2048x32 (tall: R alone, then Jacobi)", 4096, 2048, 32, False)
+    add("svd 4096 x 2048x32", 4096, 2048, 32, True)
+    add("svd 262144 x 32x32", 262144, 32, 32, True)
+    add("svdvals 262144 x 32x32", 262144, 32, 32, False)
+    add("svd 262144 x 16x16", 262144, 16, 16, True)
+    add("svdvals 64 x 65536x32", 64, 65536, 32, False)
     return out
 
 
