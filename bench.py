@@ -364,7 +364,7 @@ def other_configs(torch, mlt, _lib, workloads, args):
 
 
 def svd_configs(torch, mlt, _lib, args):
-    """The SVD that calls the QR (min(M, N) <= 32), on one GPU: seconds per call by CUDA events through
+    """The SVD that calls the QR (min(M, N) <= 128), on one GPU: seconds per call by CUDA events through
     the C ABI on device pointers, matrices/s, and GB/s from the algorithmic bytes (A read once; s, and with
     vectors U and Vt, written once). Beside each, LAPACK's sgesdd (the routine the reference's CPU SVD calls)
     on one host core over a bounded sample."""
@@ -422,6 +422,9 @@ def svd_configs(torch, mlt, _lib, args):
     add("svdvals 262144 x 32x32", 262144, 32, 32, False)
     add("svd 262144 x 16x16", 262144, 16, 16, True)
     add("svdvals 64 x 65536x32", 64, 65536, 32, False)
+    add("svdvals 64 x 65536x64 (the fourth configuration's shape)", 64, 65536, 64, False)
+    add("svd 64 x 65536x64 (the fourth configuration's shape)", 64, 65536, 64, True)
+    add("svd 1024 x 512x128", 1024, 512, 128, True)
     return out
 
 

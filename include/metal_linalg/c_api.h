@@ -102,7 +102,7 @@ uint64_t            metal_linalg_qr_no_alloc_scratch_bytes(void);
  * cols]; u and vt both NULL for the singular values alone; info [batch] or
  * NULL. Pointers as for metal_linalg_qr: all on the host or all on one GPU.
  * Of the reference's SVD backends this library holds the QR-preconditioned
- * one alone (A = Q R by the QR above, then one-sided Jacobi on R), for K <= 32:
+ * one alone (A = Q R by the QR above, then one-sided Jacobi on R), for K <= 128:
  * a larger K fails with METAL_LINALG_INVALID_ARGUMENT. */
 metal_linalg_status metal_linalg_svd(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
                                      float* u, float* s, float* vt, uint32_t* info);

@@ -80,7 +80,7 @@ namespace metal_linalg {
 
     // The SVD's one backend here: the QR of this library, then one-sided Jacobi on the small factor
     // (reference: SvdBackend, core.h:550-574, of which qr_jacobi is one of ten). `unavailable`: a shape
-    // beyond it (min(M, N) > 32), which core::svd refuses.
+    // beyond it (min(M, N) > 128), which core::svd refuses.
     enum class SvdBackend { qr_jacobi, unavailable };
     SvdBackend svd_backend(unsigned m, unsigned n, unsigned batch);
     SvdBackend svdvals_backend(unsigned m, unsigned n, unsigned batch);
@@ -120,7 +120,7 @@ namespace metal_linalg {
         // formed: the QR runs in mode r). info [batch] or null: bits 0-15 the sweeps taken, bit 16
         // converged, bit 17 the matrix held a NaN or an infinity (its outputs are NaN), bit 18
         // rank-deficient (reference: core.h:811-814, c_api.h:96-102). The QR-preconditioned route
-        // of the reference's svd_qr_jacobi (src/svd.mm:614-661), for min(M, N) <= 32; anything
+        // of the reference's svd_qr_jacobi (src/svd.mm:614-661), for min(M, N) <= 128; anything
         // larger throws std::invalid_argument. Pointers as for qr: all on the host or all on one GPU.
         void svd(const Matrices& a, float* u, float* s, float* vt, uint32_t* info = nullptr);
         bool svd_fits(uint32_t m, uint32_t n);

@@ -101,7 +101,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
 void launch_fill_identity(cudaStream_t stream, float* q, uint32_t batch, uint32_t m, uint32_t cols);
 
 // The small SVD behind a QR (svd_small.cu): one-sided Jacobi on the k x k factors r [batch, k, k],
-// k <= 32. s [batch, k] descending; with ur non-null also the factors' left vectors ur [batch, k, k]
+// k <= 128. s [batch, k] descending; with ur non-null also the factors' left vectors ur [batch, k, k]
 // (as columns) and the right vectors v [batch, k, k] (V^T, or V itself with v_as_columns);
 // info [batch] or null. `effective_rows`: the rows of the matrix the factor came from (the rotation
 // tolerance is sqrt(max(rows, 64)) eps).

@@ -1,7 +1,8 @@
 // core::svd by the QR-preconditioned route: A = Q R, R = U_R S V^T, A = (Q U_R) S V^T
 // (reference: svd_qr_jacobi, src/svd.mm:614-661; the wide case by the transpose, :621-635). The QR
 // is this library's own (mode r when the singular values alone are asked for, so Q is never
-// formed); the small SVD is the one-sided Jacobi of svd_small.cu, which holds min(M, N) <= 32.
+// formed); the small SVD is the one-sided Jacobi of svd_small.cu, which holds min(M, N) <= 128 (a warp's
+// registers up to 32, a thread block's shared memory beyond).
 // The reference's other SVD backends (block Jacobi, bidiagonalization, band reduction, LAPACK) are
 // not built: a larger min(M, N) is refused with std::invalid_argument.
 #include <metal_linalg/core.h>
@@ -91,7 +92,7 @@ void svd(const Matrices& a, float* u, float* s, float* vt, uint32_t* info) {
     }
     if (!mlb::svd_small_fits(K))
         throw std::invalid_argument("[svd] min(M, N) = " + std::to_string(K) +
-                                    ": this build holds the QR-preconditioned Jacobi route alone, min(M, N) <= 32");
+                                    ": this build holds the QR-preconditioned Jacobi route alone, min(M, N) <= 128");
     if (where >= 0) {
         mlb::DeviceContext& ctx = mlb::context(where);
         mlb::DeviceGuard guard(where);

@@ -1,8 +1,8 @@
 // The small SVD on the far side of the QR: Hestenes' one-sided Jacobi on the K x K triangular factor
 // of a QR-preconditioned SVD (reference: svd_qr_jacobi, src/svd.mm:614-661, whose inner kernel is
-// shaders/Svd_Jacobi.metal), K <= 32, and the product U = Q U_R that follows it.
+// shaders/Svd_Jacobi.metal), K <= 128, and the product U = Q U_R that follows it.
 //
-// Layout: a matrix belongs to a group of R lanes (R = 4, 8, 16 or 32 >= K; 32 / R matrices a warp),
+// Layout for K <= 32 (for 32 < K <= 128 see svd_block_kernel): a matrix belongs to a group of R lanes (R = 4, 8, 16 or 32 >= K; 32 / R matrices a warp),
 // lane c holding column c of G (= the factor R, scaled by a power of two so that its largest entry
 // lies in [0.5, 1)) and column c of V in registers. A round pairs every column with one partner
 // (the circle method: R - 1 rounds visit every pair once); the partner's column comes by R
@@ -299,6 +299,277 @@ __global__ void __launch_bounds__(256) transpose_batched_kernel(const float* __r
         if (c0 + c < cols && r0 + tx < rows) out[base + (size_t)(c0 + c) * rows + r0 + tx] = tile[tx][c];
 }
 
+// ---------------------------------------------------------------------------
+// 32 < k <= 128: a matrix to a thread block, G and V by column in shared memory, a warp to a pair
+// (lanes along the rows; the three inner products by a warp sum), one barrier a round -- the
+// arrangement of the reference's kernel (shaders/Svd_Jacobi.metal:20-33) -- with the same rules.
+// ---------------------------------------------------------------------------
+constexpr int kBlockWarps = 16;
+
+struct BlockShared {
+    float red[kBlockWarps];
+    float sig[128];
+    uint32_t rank[128];
+    unsigned char valid[128];
+    float w[128];
+    int flag;
+};
+
+__device__ __forceinline__ float block_max(float v, float* red, int warp, int lane, int nw) {
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int i = 1; i < nw; ++i) r = fmaxf(r, red[i]);
+    return r;
+}
+
+template <bool Vectors>
+__global__ void __launch_bounds__(32 * kBlockWarps) svd_block_kernel(const SvdSmallParams p) {
+    dependency_wait_only();
+    extern __shared__ __align__(16) float dyn[];
+    __shared__ BlockShared sh;
+    const uint32_t k = p.k, ld = k | 1u;          // odd: the transposing load and the stores by row spread over the banks
+    float* G = dyn;
+    float* V = dyn + (size_t)k * ld;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nt = blockDim.x, nw = nt >> 5;
+    const uint32_t mat = blockIdx.x;
+    const size_t kk = (size_t)k * k;
+    const float* src = p.r + mat * kk;
+
+    float amax = 0.0f;
+    int bad = 0;
+    for (uint32_t idx = tid; idx < kk; idx += nt) {
+        const uint32_t i = idx / k, c = idx - i * k;
+        const float x = src[idx];
+        bad |= nonfinite(x) ? 1 : 0;
+        amax = fmaxf(amax, fabsf(x));
+        G[c * ld + i] = x;
+        if (Vectors) V[c * ld + i] = i == c ? 1.0f : 0.0f;
+    }
+    const bool nonfin = __syncthreads_or(bad) != 0;
+    amax = block_max(amax, sh.red, warp, lane, nw);
+    const int expo = nonfin ? 0 : amax_exponent(amax);
+    {
+        const Pow2 down(-expo);
+        for (uint32_t idx = tid; idx < kk; idx += nt) {
+            const uint32_t c = idx / k, i = idx - c * k;
+            G[c * ld + i] = down(G[c * ld + i]);
+        }
+    }
+    __syncthreads();
+
+    const uint32_t n_even = (k + 1) & ~1u, np = n_even / 2, m1 = n_even - 1;
+    uint32_t sweeps = 0;
+    bool converged = false;
+    while (!nonfin && sweeps < p.max_sweeps) {
+        float cmax2 = 0.0f;
+        for (uint32_t c = warp; c < k; c += nw) {
+            float acc = 0.0f;
+            for (uint32_t i = lane; i < k; i += 32) acc = fmaf(G[c * ld + i], G[c * ld + i], acc);
+            cmax2 = fmaxf(cmax2, warp_sum(acc));
+        }
+        cmax2 = block_max(cmax2, sh.red, warp, lane, nw);
+        const float null2 = kNullTol * kNullTol * cmax2, negl2 = kNegligible * kNegligible * cmax2;
+        int rotated = 0;
+        for (uint32_t round = 0; round < m1; ++round) {
+            // the circle method: x0 with 2 x0 = round (mod n_even - 1) meets the last column, and
+            // x0 + j meets x0 - j
+            const uint32_t x0 = (round * np) % m1;
+            for (uint32_t j = warp; j < np; j += nw) {
+                const uint32_t a = j == 0 ? x0 : (x0 + j) % m1, b = j == 0 ? m1 : (x0 + m1 - j) % m1;
+                const uint32_t cp = min(a, b), cq = max(a, b);
+                if (cq >= k) continue;          // the dummy column of an odd k
+                float* gp = G + cp * ld;
+                float* gq = G + cq * ld;
+                float alpha = 0.0f, beta = 0.0f, gamma = 0.0f;
+                for (uint32_t i = lane; i < k; i += 32) {
+                    const float x = gp[i], y = gq[i];
+                    alpha = fmaf(x, x, alpha);
+                    beta = fmaf(y, y, beta);
+                    gamma = fmaf(x, y, gamma);
+                }
+                alpha = warp_sum(alpha);
+                beta = warp_sum(beta);
+                gamma = warp_sum(gamma);
+                if (alpha <= null2 && beta <= null2) continue;
+                const float ab = alpha * beta;
+                if (!(fabsf(gamma) > p.tol * sqrtf(ab))) continue;
+                const float zeta = (beta - alpha) / (2.0f * gamma);
+                float t;
+                if (fabsf(zeta) > kZetaAsymptotic) {
+                    t = 0.5f / zeta;
+                } else {
+                    t = 1.0f / (fabsf(zeta) + sqrtf(fmaf(zeta, zeta, 1.0f)));
+                    if (zeta < 0.0f) t = -t;
+                }
+                const float c = 1.0f / sqrtf(fmaf(t, t, 1.0f)), sn = c * t;
+                for (uint32_t i = lane; i < k; i += 32) {
+                    const float x = gp[i], y = gq[i];
+                    gp[i] = fmaf(-sn, y, c * x);
+                    gq[i] = fmaf(sn, x, c * y);
+                }
+                if (Vectors) {
+                    float* vp = V + cp * ld;
+                    float* vq = V + cq * ld;
+                    for (uint32_t i = lane; i < k; i += 32) {
+                        const float x = vp[i], y = vq[i];
+                        vp[i] = fmaf(-sn, y, c * x);
+                        vq[i] = fmaf(sn, x, c * y);
+                    }
+                }
+                const bool one_null = alpha <= null2 || beta <= null2;
+                if (!one_null) rotated = 1;
+                else if (fminf(alpha, beta) > negl2 && gamma * gamma > kCleanCos * kCleanCos * ab) rotated = 1;
+            }
+            __syncthreads();      // the next round pairs columns other warps have just written
+        }
+        ++sweeps;
+        if (__syncthreads_or(rotated) == 0) { converged = true; break; }
+    }
+
+    // singular values, their order, the null threshold
+    for (uint32_t c = warp; c < k; c += nw) {
+        float acc = 0.0f;
+        for (uint32_t i = lane; i < k; i += 32) acc = fmaf(G[c * ld + i], G[c * ld + i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) sh.sig[c] = sqrtf(acc);
+    }
+    __syncthreads();
+    float smax = 0.0f;
+    for (uint32_t c = tid; c < k; c += nt) smax = fmaxf(smax, sh.sig[c]);
+    smax = block_max(smax, sh.red, warp, lane, nw);
+    const float thr = kNullTol * smax;
+    int low = 0;
+    for (uint32_t c = tid; c < k; c += nt) {
+        const float sc = sh.sig[c];
+        uint32_t before = 0;
+        for (uint32_t d = 0; d < k; ++d) {
+            const float sd = sh.sig[d];
+            before += (sd > sc || (sd == sc && d < c)) ? 1u : 0u;
+        }
+        sh.rank[c] = nonfin ? c : before;
+        sh.valid[c] = sc > thr ? 1 : 0;
+        low |= sc > thr ? 0 : 1;
+        p.s[(size_t)mat * k + sh.rank[c]] = nonfin ? qnan() : Pow2(expo)(sc);
+    }
+    const bool deficient = (__syncthreads_or(low) != 0) && !nonfin;      // also orders rank and valid before their readers
+    if (tid == 0 && p.info)
+        p.info[mat] = sweeps | (converged ? 1u << 16 : 0u) | (nonfin ? 1u << 17 : 0u) | (deficient ? 1u << 18 : 0u);
+    if (!Vectors) return;
+
+    float* out_v = p.v + mat * kk;
+    float* out_u = p.ur + mat * kk;
+    if (nonfin) {
+        for (uint32_t idx = tid; idx < kk; idx += nt) { out_v[idx] = qnan(); out_u[idx] = qnan(); }
+        return;
+    }
+    // left vectors: the normalised columns, zero for a null one
+    for (uint32_t c = warp; c < k; c += nw) {
+        const float inv = sh.valid[c] ? 1.0f / sh.sig[c] : 0.0f;
+        for (uint32_t i = lane; i < k; i += 32) G[c * ld + i] *= inv;
+    }
+    __syncthreads();
+    if (deficient && warp == 0) {
+        // Every null column in turn takes a fixed pseudo-random vector made orthogonal (three passes) to the
+        // columns in place (reference: complete_columns_impl, src/svd.mm:148-186); one warp does it.
+        uint32_t seed = 1;
+        for (uint32_t c = 0; c < k; ++c) {
+            if (sh.valid[c]) continue;
+            for (int attempt = 0; attempt < 8; ++attempt, ++seed) {
+                float start = 0.0f;
+                for (uint32_t i = lane; i < k; i += 32) {
+                    const float x = candidate_entry(seed, i);
+                    sh.w[i] = x;
+                    start = fmaf(x, x, start);
+                }
+                start = warp_sum(start);
+                __syncwarp();
+                for (int pass = 0; pass < 3; ++pass)
+                    for (uint32_t d = 0; d < k; ++d) {
+                        if (!sh.valid[d]) continue;
+                        float dot = 0.0f;
+                        for (uint32_t i = lane; i < k; i += 32) dot = fmaf(G[d * ld + i], sh.w[i], dot);
+                        dot = warp_sum(dot);
+                        for (uint32_t i = lane; i < k; i += 32) sh.w[i] = fmaf(-dot, G[d * ld + i], sh.w[i]);
+                        __syncwarp();
+                    }
+                float nrm = 0.0f;
+                for (uint32_t i = lane; i < k; i += 32) nrm = fmaf(sh.w[i], sh.w[i], nrm);
+                nrm = warp_sum(nrm);
+                if (nrm > 1e-6f * start) {
+                    const float inv = rsqrtf(nrm);
+                    for (uint32_t i = lane; i < k; i += 32) G[c * ld + i] = sh.w[i] * inv;
+                    if (lane == 0) sh.valid[c] = 1;
+                    __syncwarp();
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t idx = tid; idx < kk; idx += nt) {
+        const uint32_t i = idx / k, c = idx - i * k;
+        const uint32_t rk = sh.rank[c];
+        out_u[(size_t)i * k + rk] = G[c * ld + i];
+        out_v[p.v_as_columns ? (size_t)i * k + rk : (size_t)rk * k + i] = V[c * ld + i];
+    }
+}
+
+size_t block_smem(uint32_t k, bool vectors) { return (size_t)k * (k | 1u) * sizeof(float) * (vectors ? 2 : 1); }
+
+void launch_block_jacobi(cudaStream_t stream, const SvdSmallParams& p, bool vectors) {
+    static const bool configured = [] {
+        cuda_check(cudaFuncSetAttribute(svd_block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)block_smem(128, true)), "svd_block shared memory");
+        cuda_check(cudaFuncSetAttribute(svd_block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)block_smem(128, false)), "svd_block shared memory");
+        return true;
+    }();
+    (void)configured;
+    const uint32_t pairs = (p.k + 1) / 2;
+    const uint32_t warps = pairs < (uint32_t)kBlockWarps ? pairs : (uint32_t)kBlockWarps;
+    if (vectors) launch_dependent(svd_block_kernel<true>, p.batch, 32 * warps, block_smem(p.k, true), stream, p);
+    else launch_dependent(svd_block_kernel<false>, p.batch, 32 * warps, block_smem(p.k, false), stream, p);
+}
+
+// out = Q U_R for k > 32: a block takes 64 rows of Q, U_R in shared memory, a thread 1 row x k / 4 columns.
+__global__ void __launch_bounds__(256) svd_left_vectors_wide_kernel(const float* __restrict__ q, const float* __restrict__ ur,
+                                                                    float* __restrict__ out, uint32_t l, uint32_t k, int transposed) {
+    dependency_wait_only();
+    extern __shared__ __align__(16) float dyn[];
+    float* U = dyn;                        // [k][k]
+    float* Qs = dyn + (size_t)k * k;       // [64][k + 1]
+    const uint32_t b = blockIdx.y, r0 = blockIdx.x * 64, tid = threadIdx.x;
+    const float* ub = ur + (size_t)b * k * k;
+    const float* qb = q + ((size_t)b * l + r0) * k;
+    const uint32_t rows = min(64u, l - r0);
+    for (uint32_t idx = tid; idx < k * k; idx += 256) U[idx] = ub[idx];
+    for (uint32_t idx = tid; idx < rows * k; idx += 256) Qs[(idx / k) * (k + 1) + idx % k] = qb[idx];
+    __syncthreads();
+    const uint32_t row = tid >> 2, quarter = tid & 3;
+    if (row >= rows) return;
+    float acc[32];
+#pragma unroll
+    for (int jj = 0; jj < 32; ++jj) acc[jj] = 0.0f;
+    for (uint32_t t = 0; t < k; ++t) {
+        const float x = Qs[row * (k + 1) + t];
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+            const uint32_t j = quarter + 4 * jj;
+            if (j < k) acc[jj] = fmaf(x, U[t * k + j], acc[jj]);
+        }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 32; ++jj) {
+        const uint32_t j = quarter + 4 * jj;
+        if (j >= k) continue;
+        if (transposed) out[((size_t)b * k + j) * l + r0 + row] = acc[jj];
+        else out[((size_t)b * l + r0 + row) * k + j] = acc[jj];
+    }
+}
+
 template <int R>
 void launch_jacobi(cudaStream_t stream, const SvdSmallParams& p, bool vectors) {
     const uint32_t per_block = 4 * (32 / R);
@@ -309,7 +580,7 @@ void launch_jacobi(cudaStream_t stream, const SvdSmallParams& p, bool vectors) {
 
 } // namespace
 
-bool svd_small_fits(uint32_t k) { return k >= 1 && k <= 32; }
+bool svd_small_fits(uint32_t k) { return k >= 1 && k <= 128; }
 
 void launch_svd_small(cudaStream_t stream, const float* r, uint32_t batch, uint32_t k, uint32_t effective_rows,
                       float* s, float* ur, float* v, bool v_as_columns, uint32_t* info) {
@@ -324,12 +595,29 @@ void launch_svd_small(cudaStream_t stream, const float* r, uint32_t batch, uint3
     if (k <= 4) launch_jacobi<4>(stream, p, vectors);
     else if (k <= 8) launch_jacobi<8>(stream, p, vectors);
     else if (k <= 16) launch_jacobi<16>(stream, p, vectors);
-    else launch_jacobi<32>(stream, p, vectors);
+    else if (k <= 32) launch_jacobi<32>(stream, p, vectors);
+    else launch_block_jacobi(stream, p, vectors);
     cuda_check(cudaGetLastError(), "svd_small launch");
 }
 
 void launch_svd_left_vectors(cudaStream_t stream, const float* q, const float* ur, float* out, uint32_t batch, uint32_t l,
                              uint32_t k, bool transposed) {
+    if (k > 32) {
+        static const bool configured = [] {
+            cuda_check(cudaFuncSetAttribute(svd_left_vectors_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)((128 * 128 + 64 * 129) * sizeof(float))), "svd_left_vectors shared memory");
+            return true;
+        }();
+        (void)configured;
+        const size_t smem = ((size_t)k * k + 64 * (k + 1)) * sizeof(float);
+        for (uint32_t b0 = 0; b0 < batch; b0 += 65535) {      // the batch along y in slices
+            const uint32_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
+            launch_dependent(svd_left_vectors_wide_kernel, dim3((l + 63) / 64, nb), 256, smem, stream, q + (size_t)b0 * l * k,
+                             ur + (size_t)b0 * k * k, out + (size_t)b0 * l * k, l, k, transposed ? 1 : 0);
+        }
+        cuda_check(cudaGetLastError(), "svd_left_vectors launch");
+        return;
+    }
     const size_t rows = (size_t)batch * l;
     const uint32_t blocks = (uint32_t)((rows + 255) / 256);
     const int t = transposed ? 1 : 0;

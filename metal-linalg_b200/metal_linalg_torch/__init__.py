@@ -13,7 +13,7 @@ the input's device. It supports autograd (torch.linalg's formula) and
 torch.compile: underneath it is the custom operator torch.ops.metal_linalg.qr.
 Computation is in float32: other real dtypes are converted, results are float32.
 Beside QR this build holds the SVD that calls it (`svd`, `svdvals`: the QR-preconditioned
-Jacobi route, min(M, N) <= 32); the reference's other decompositions do not exist here.
+Jacobi route, min(M, N) <= 128); the reference's other decompositions do not exist here.
 """
 from collections import namedtuple
 
@@ -94,7 +94,7 @@ def svd(A, full_matrices=False):
     ``A = U @ diag(S) @ Vh`` with ``U`` ``[..., M, K]``, ``S`` ``[..., K]`` descending and ``Vh``
     ``[..., K, N]``, ``K = min(M, N)`` (reference: python-torch/metal_linalg_torch/__init__.py:144-160).
     ``full_matrices=True`` is refused, as by the reference. The route is A = Q R by this library's
-    QR, then one-sided Jacobi on R: ``K <= 32`` (a larger K raises ValueError)."""
+    QR, then one-sided Jacobi on R: ``K <= 128`` (a larger K raises ValueError)."""
     if full_matrices:
         raise NotImplementedError("metal_linalg_torch.svd: full_matrices=True is not supported; the thin "
                                   "decomposition is what the library computes")

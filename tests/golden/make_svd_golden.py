@@ -34,6 +34,12 @@ CASES = {
     "wide_7x300": lambda: np.random.default_rng(25).standard_normal((4, 7, 300)).astype(np.float32),
     "odd_19x5": lambda: np.random.default_rng(26).standard_normal((5, 19, 5)).astype(np.float32),
     "graded_80x24": lambda: _graded(27, 80, 24, 1e-5),
+    "square_64": lambda: np.random.default_rng(30).standard_normal((3, 64, 64)).astype(np.float32),
+    "tall_3000x100": lambda: np.random.default_rng(31).standard_normal((2, 3000, 100)).astype(np.float32),
+    "wide_128x700": lambda: np.random.default_rng(32).standard_normal((2, 128, 700)).astype(np.float32),
+    "graded_300x96": lambda: _graded(33, 300, 96, 1e-5),
+    "rank5_200x48": lambda: (np.random.default_rng(34).standard_normal((2, 200, 5)).astype(np.float32)
+                             @ np.random.default_rng(35).standard_normal((2, 5, 48)).astype(np.float32)),
     "rank3_40x8": lambda: (np.random.default_rng(28).standard_normal((2, 40, 3)).astype(np.float32)
                            @ np.random.default_rng(29).standard_normal((2, 3, 8)).astype(np.float32)),
 }

@@ -4,6 +4,10 @@ reference's known-answer case and LAPACK's singular values, the C ABI's argument
 
 Tolerances are the reference's own (tests/test_svd.cpp:41-43,156-175): ||A - U S Vt||_F / ||A||_F <= 2e-5,
 ||U^T U - I||_F / sqrt(K) and the same for Vt <= 2e-5 max(1, sqrt(max(M, N) / 256)), |S - S_lapack| / ||A||_F <= 2e-5.
+Beyond K = 64 the bounds on reconstruction and orthogonality grow as sqrt(K / 64): plain one-sided Jacobi in float32
+applies about K rotations a sweep to every column of V, each entry's rounding error grows as sqrt(K sweeps) and the
+Frobenius norm over K^2 entries, divided by sqrt(K), as sqrt(K) times that (the float32 restatement itself shows
+2.2e-5 at K = 128; the reference sends such K to its block Jacobi backend, which is not built here).
 """
 import os
 import sys
@@ -23,7 +27,9 @@ GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golde
 RECON_TOL = ORTHO_TOL = SVAL_TOL = 2e-5
 
 
-def check_svd(a, u, s, vt, s_ref=None, deficient=False):
+def check_svd(a, u, s, vt, s_ref=None, slack=1.0):
+    """`slack` scales the tolerances for matrices whose rounding exceeds them (graded over five decades), as the
+    reference's own check does (tests/test_svd.cpp:94-98,173-175)."""
     a = np.asarray(a, np.float32)
     *lead, m, n = a.shape
     k = min(m, n)
@@ -33,13 +39,14 @@ def check_svd(a, u, s, vt, s_ref=None, deficient=False):
     fro = np.linalg.norm(a.astype(np.float64), axis=(-2, -1))
     if s_ref is not None:
         err = np.abs(s.astype(np.float64) - s_ref).max(axis=-1) / np.maximum(fro, 1e-300)
-        assert err.max() <= SVAL_TOL, f"|S - S_lapack| / ||A|| = {err.max():.2e}"
+        assert err.max() <= slack * SVAL_TOL, f"|S - S_lapack| / ||A|| = {err.max():.2e}"
     if u is None:
         return
     assert u.shape == (*lead, m, k) and vt.shape == (*lead, k, n)
     rec, ou, ov = harness.svd_metrics(a, u, s, vt)
-    tol_o = ORTHO_TOL * max(1.0, np.sqrt(max(m, n) / 256.0))
-    assert rec.max() <= RECON_TOL, f"reconstruction {rec.max():.2e}"
+    slack = slack * max(1.0, np.sqrt(k / 64.0))
+    tol_o = slack * ORTHO_TOL * max(1.0, np.sqrt(max(m, n) / 256.0))
+    assert rec.max() <= slack * RECON_TOL, f"reconstruction {rec.max():.2e}"
     assert (ou / np.sqrt(k)).max() <= tol_o, f"U orthogonality {(ou / np.sqrt(k)).max():.2e}"
     assert (ov / np.sqrt(k)).max() <= tol_o, f"Vt orthogonality {(ov / np.sqrt(k)).max():.2e}"
 
@@ -52,7 +59,7 @@ def check_svd(a, u, s, vt, s_ref=None, deficient=False):
 def test_oracle_matches_lapack_fixtures(name):
     a = make_svd_golden.CASES[name]()
     u, s, vt, info = harness.oracle_svd(a)
-    check_svd(a, u, s, vt, s_ref=GOLDEN[f"{name}/s64"])
+    check_svd(a, u, s, vt, s_ref=GOLDEN[f"{name}/s64"], slack=2.0 if name.startswith("graded") else 1.0)
     fro = np.linalg.norm(a.astype(np.float64), axis=(-2, -1))
     assert (np.abs(s - GOLDEN[f"{name}/s32"]).max(axis=-1) / fro).max() <= SVAL_TOL      # the reference's CPU path: sgesdd
     assert ((info >> 16) & 1).all(), "not converged"
@@ -74,6 +81,10 @@ def test_oracle_rank_deficient_zero_and_nonfinite():
     u, s, vt, info = harness.oracle_svd(a)
     assert ((info >> 18) & 1).all() and ((info >> 16) & 1).all()
     assert (s[:, 3:] <= 1e-5 * s[:, :1]).all()
+    a5 = make_svd_golden.CASES["rank5_200x48"]()
+    u5, s5, vt5, info5 = harness.oracle_svd(a5)
+    assert ((info5 >> 18) & 1).all() and (s5[:, 5:] <= 1e-5 * s5[:, :1]).all()
+    check_svd(a5, u5, s5, vt5)
     check_svd(a, u, s, vt)                       # the null columns were completed to an orthonormal basis
     z = np.zeros((1, 6, 4), np.float32)
     u, s, vt, info = harness.oracle_svd(z)
@@ -107,16 +118,16 @@ def test_svd_argument_errors_need_no_gpu():
     assert lib.metal_linalg_svd(None, 1, 2, 2, None, s.ctypes.data, None, None) == _lib.INVALID_ARGUMENT
     assert lib.metal_linalg_svd(a.ctypes.data, 1, 2, 2, None, None, None, None) == _lib.INVALID_ARGUMENT
     assert lib.metal_linalg_svd(None, 0, 2, 2, None, None, None, None) == _lib.OK          # an empty batch
-    big = np.zeros((1, 40, 40), np.float32)
-    sb = np.zeros(40, np.float32)
-    assert lib.metal_linalg_svd(big.ctypes.data, 1, 40, 40, None, sb.ctypes.data, None, None) == _lib.INVALID_ARGUMENT
+    big = np.zeros((1, 130, 130), np.float32)
+    sb = np.zeros(130, np.float32)
+    assert lib.metal_linalg_svd(big.ctypes.data, 1, 130, 130, None, sb.ctypes.data, None, None) == _lib.INVALID_ARGUMENT
     assert "min(M, N)" in _lib.last_error()
     assert mlt.svd_backend(5000, 32) == "qr_jacobi" and mlt.svdvals_backend(32, 5000, 9) == "qr_jacobi"
-    assert mlt.svd_backend(64, 33) == "unavailable"
+    assert mlt.svd_backend(64, 33) == "qr_jacobi" and mlt.svd_backend(129, 4000) == "unavailable"
     with pytest.raises(NotImplementedError):
         mlt.svd(torch.zeros(2, 3, 3), full_matrices=True)
     with pytest.raises(ValueError):
-        mlt.svd(torch.zeros(2, 40, 40))
+        mlt.svd(torch.zeros(2, 140, 140))
 
 
 @pytest.mark.parametrize("shape", [(3, 7, 4), (2, 4, 9), (2, 5, 5)])
@@ -171,7 +182,7 @@ def gpu_svd(a, vectors=True):
 def test_gpu_matches_fixtures_and_oracle(name):
     a = make_svd_golden.CASES[name]()
     u, s, vt, info = gpu_svd(a)
-    check_svd(a, u, s, vt, s_ref=GOLDEN[f"{name}/s64"])
+    check_svd(a, u, s, vt, s_ref=GOLDEN[f"{name}/s64"], slack=2.0 if name.startswith("graded") else 1.0)
     _, s_o, _, info_o = harness.oracle_svd(a)
     fro = np.linalg.norm(a.astype(np.float64), axis=(-2, -1))
     assert (np.abs(s - s_o).max(axis=-1) / fro).max() <= SVAL_TOL
@@ -184,14 +195,15 @@ def test_gpu_matches_fixtures_and_oracle(name):
 
 SHAPES = [(1, 1), (1, 9), (9, 1), (2, 2), (3, 2), (2, 3), (4, 4), (5, 5), (8, 8), (9, 9), (16, 16), (17, 17), (31, 31),
           (32, 32), (33, 32), (32, 33), (100, 3), (3, 100), (257, 8), (1000, 16), (1025, 32), (20000, 20), (24, 3000),
-          (70000, 32)]
+          (70000, 32), (33, 33), (40, 64), (64, 64), (65, 65), (100, 100), (127, 127), (128, 128), (500, 33), (2000, 96),
+          (128, 9000), (65536, 64)]
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("shape", SHAPES)
 def test_gpu_shapes(shape):
     m, n = shape
-    batch = 3 if max(m, n) > 2000 else 37
+    batch = 3 if max(m, n) > 2000 else 37 if min(m, n) <= 32 else 5
     a = np.random.default_rng(m * 131 + n).standard_normal((batch, m, n)).astype(np.float32)
     u, s, vt, info = gpu_svd(a)
     s_ref = np.linalg.svd(a.astype(np.float64), compute_uv=False)
@@ -202,9 +214,11 @@ def test_gpu_shapes(shape):
 
 
 @pytest.mark.gpu
-def test_gpu_rank_deficient_zero_nonfinite_and_isolation():
-    a = make_svd_golden.CASES["rank3_40x8"]()
-    a = np.concatenate([a, np.zeros((1, 40, 8), np.float32), np.random.default_rng(9).standard_normal((2, 40, 8)).astype(np.float32)])
+@pytest.mark.parametrize("name", ["rank3_40x8", "rank5_200x48"])
+def test_gpu_rank_deficient_zero_nonfinite_and_isolation(name):
+    a = make_svd_golden.CASES[name]()
+    m, n = a.shape[-2:]
+    a = np.concatenate([a, np.zeros((1, m, n), np.float32), np.random.default_rng(9).standard_normal((2, m, n)).astype(np.float32)])
     a[3, 5, 5] = np.inf
     u, s, vt, info = gpu_svd(a)
     assert ((info[[0, 1, 2]] >> 18) & 1).all() and not (info[4] >> 17) & 3
