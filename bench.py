@@ -436,6 +436,9 @@ PROFILE_CASES = {
     "tsqr": (8, 65536, 64, "reduced"),
     "blocked4096": (1, 4096, 4096, "reduced"),
     "blocked8192": (1, 8192, 8192, "reduced"),
+    # the SVD that calls the QR (mode "svd": U, S and Vt)
+    "svd32": (65536, 32, 32, "svd"),
+    "svd128": (592, 512, 128, "svd"),
 }
 
 
@@ -448,6 +451,18 @@ def run_profile_case(name, launches):
     b, m, n, mode = PROFILE_CASES[name]
     g = torch.Generator(device="cuda").manual_seed(5)
     a = torch.randn(b, m, n, generator=g, device="cuda")
+    if mode == "svd":
+        mlt.svd(a)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(launches):
+            mlt.svd(a)
+        e1.record()
+        e1.synchronize()
+        print(json.dumps({"profile_case": name, "backend": mlt.svd_backend(m, n, b), "batch": b, "rows": m, "cols": n,
+                          "ms_per_launch": e0.elapsed_time(e1) / launches}), flush=True)
+        return
     sec, _ = time_config(torch, mlt, _lib, a, mode, launches, 1, None)
     print(json.dumps({"profile_case": name, "kernel": mlt.qr_kernel(m, n, b, mode), "batch": b, "rows": m, "cols": n,
                       "ms_per_launch": sec * 1e3}), flush=True)

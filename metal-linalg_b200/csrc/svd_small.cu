@@ -6,8 +6,9 @@
 // lane c holding column c of G (= the factor R, scaled by a power of two so that its largest entry
 // lies in [0.5, 1)) and column c of V in registers. A round pairs every column with one partner
 // (the circle method: R - 1 rounds visit every pair once); the partner's column comes by R
-// shuffles, both lanes of a pair form the same three inner products in the same order, hence the
-// same rotation, and each applies its own half. No shared memory, no barrier.
+// shuffles, both lanes of a pair form the same three inner products in the same order (rows packed two
+// to a 64-bit register: fma.rn.f32x2), hence the same rotation, and each applies its own half. No
+// shared memory, no barrier.
 //
 // The rules of the reference's kernel are kept: a pair is rotated iff |gamma| > tol sqrt(alpha beta)
 // with tol = sqrt(max(rows, 64)) eps; two numerically null columns (below 32 eps of the largest
@@ -18,6 +19,7 @@
 // info = sweeps | converged << 16 | non-finite << 17 | rank-deficient << 18.
 #include "common.cuh"
 #include "kernels.h"
+#include "qr_small_steps.cuh"
 #include "runtime.h"
 
 #include <cfloat>
@@ -53,6 +55,12 @@ __device__ __forceinline__ float group_sum(float v, unsigned mask) {
 #pragma unroll
     for (int o = R / 2; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o, R);
     return v;
+}
+
+__device__ __forceinline__ small::pair_t shuffle_pair(unsigned mask, small::pair_t v, int src, int width) {
+    float lo, hi;
+    small::unpack(v, lo, hi);
+    return small::pack(__shfl_sync(mask, lo, src, width), __shfl_sync(mask, hi, src, width));
 }
 
 // A fixed pseudo-random number in [-0.5, 0.5) for entry i of candidate `seed`.
@@ -96,12 +104,31 @@ __global__ void __launch_bounds__(128) svd_small_kernel(const SvdSmallParams p) 
         for (int i = 0; i < R; ++i) v[i] = i == col ? 1.0f : 0.0f;
     }
 
+    // The sweeps work on rows packed two to a 64-bit register (fma.rn.f32x2: half the arithmetic
+    // instructions); the partner's column comes by shuffles. (The same exchange through shared memory as
+    // 16-byte words takes a quarter of the instructions but measured slower with vectors, 45 against 36 ms
+    // for 262 144 matrices of 32 x 32: the round is a latency chain, and the registers it costs leave three
+    // warps a scheduler.)
+    using small::pair_t;
+    constexpr int H = R / 2;
+    pair_t gp[H], vp[Vectors ? H : 1];
+#pragma unroll
+    for (int i = 0; i < H; ++i) gp[i] = small::pack(g[2 * i], g[2 * i + 1]);
+    if (Vectors) {
+#pragma unroll
+        for (int i = 0; i < H; ++i) vp[i] = small::pack(v[2 * i], v[2 * i + 1]);
+    }
+
     uint32_t sweeps = 0;
     bool converged = false;
     while (!nonfin && sweeps < p.max_sweeps) {
-        float own = 0.0f;
+        float own;
+        {
+            pair_t acc = small::mul2(gp[0], gp[0]);
 #pragma unroll
-        for (int i = 0; i < R; ++i) own = fmaf(g[i], g[i], own);
+            for (int i = 1; i < H; ++i) acc = small::fma2(gp[i], gp[i], acc);
+            own = small::hsum(acc);
+        }
         const float cmax2 = group_max<R>(own, mask);
         const float null2 = kNullTol * kNullTol * cmax2, negl2 = kNegligible * kNegligible * cmax2;
         bool rotated = false;
@@ -117,19 +144,21 @@ __global__ void __launch_bounds__(128) svd_small_kernel(const SvdSmallParams p) 
                 if (partner == col) partner = R - 1;
             }
             const bool lower = col < partner;
-            float pg[R];
-            float mine = 0.0f, theirs = 0.0f, gamma = 0.0f;
+            pair_t pg[H];
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                pg[i] = __shfl_sync(mask, g[i], partner, R);
-                mine = fmaf(g[i], g[i], mine);
-                theirs = fmaf(pg[i], pg[i], theirs);
-                gamma = fmaf(g[i], pg[i], gamma);
+            for (int i = 0; i < H; ++i) pg[i] = shuffle_pair(mask, gp[i], partner, R);
+            pair_t am = small::mul2(gp[0], gp[0]), at = small::mul2(pg[0], pg[0]), ag = small::mul2(gp[0], pg[0]);
+#pragma unroll
+            for (int i = 1; i < H; ++i) {
+                am = small::fma2(gp[i], gp[i], am);
+                at = small::fma2(pg[i], pg[i], at);
+                ag = small::fma2(gp[i], pg[i], ag);
             }
+            const float mine = small::hsum(am), theirs = small::hsum(at), gamma = small::hsum(ag);
             const float alpha = lower ? mine : theirs, beta = lower ? theirs : mine;   // of columns p < q
             const float ab = alpha * beta;
-            // both lanes of a pair decide alike: they saw the same numbers. The updates below run for
-            // every pair, with the identity where nothing is rotated, so that the shuffles stay uniform.
+            // both lanes of a pair decide alike: they saw the same numbers, summed in the same order. The
+            // updates below run for every pair, with the identity where nothing is rotated.
             const bool rotate = !(alpha <= null2 && beta <= null2) && fabsf(gamma) > p.tol * sqrtf(ab);
             float c = 1.0f, cs = 0.0f;
             if (rotate) {
@@ -148,18 +177,23 @@ __global__ void __launch_bounds__(128) svd_small_kernel(const SvdSmallParams p) 
                 if (!one_null) rotated = true;
                 else if (fminf(alpha, beta) > negl2 && gamma * gamma > kCleanCos * kCleanCos * ab) rotated = true;
             }
+            const pair_t c2 = small::pack(c, c), cs2 = small::pack(cs, cs);
 #pragma unroll
-            for (int i = 0; i < R; ++i) g[i] = fmaf(cs, pg[i], c * g[i]);
+            for (int i = 0; i < H; ++i) gp[i] = small::fma2(cs2, pg[i], small::mul2(c2, gp[i]));
             if (Vectors) {
 #pragma unroll
-                for (int i = 0; i < R; ++i) {
-                    const float other = __shfl_sync(mask, v[i], partner, R);
-                    v[i] = fmaf(cs, other, c * v[i]);
-                }
+                for (int i = 0; i < H; ++i)
+                    vp[i] = small::fma2(cs2, shuffle_pair(mask, vp[i], partner, R), small::mul2(c2, vp[i]));
             }
         }
         ++sweeps;
         if (__ballot_sync(mask, rotated) == 0) { converged = true; break; }
+    }
+#pragma unroll
+    for (int i = 0; i < H; ++i) small::unpack(gp[i], g[2 * i], g[2 * i + 1]);
+    if (Vectors) {
+#pragma unroll
+        for (int i = 0; i < H; ++i) small::unpack(vp[i], v[2 * i], v[2 * i + 1]);
     }
 
     // singular values, their order, the null threshold
