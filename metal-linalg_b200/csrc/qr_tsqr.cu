@@ -188,7 +188,7 @@ Layout layout(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, 
     }
     size_t mid_floats = qr_mid_workspace_floats(ctx, L.top_rows, n, batch);
     for (const Level& lv : L.levels) {
-        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, lv.c, n, batch * (lv.blocks - 1)));
+        mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, lv.c, n, batch * lv.blocks));
         mid_floats = std::max(mid_floats, qr_mid_workspace_floats(ctx, lv.last_rows, n, batch));
     }
     L.mid_off = L.total;
@@ -225,6 +225,12 @@ void tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t
         o.lda = in_ld;
         o.a_stride = (uint64_t)lv.c * in_ld; o.q_stride = (uint64_t)lv.c * n; o.r_stride = (uint64_t)n * n;
         o.a_outer = in_outer; o.q_outer = (uint64_t)lv.rows * n; o.r_outer = (uint64_t)lv.blocks * n * n;
+        if (lv.last_rows == lv.c) {   // no remainder: every block of every matrix in one launch
+            QrProblem p{in, qout, rout, batch * lv.blocks, lv.c, n, qc, n};
+            o.inner_count = lv.blocks;
+            launch_qr_mid(ctx, stream, p, o);
+            continue;
+        }
         if (lv.blocks > 1) {   // the full blocks of every matrix in one launch
             QrProblem p{in, qout, rout, batch * (lv.blocks - 1), lv.c, n, qc, n};
             o.inner_count = lv.blocks - 1;
