@@ -26,6 +26,7 @@
 // the top-level Q and with it every entry of the matrix's Q and R are NaN.
 #include "common.cuh"
 #include "kernels.h"
+#include "qr_small_steps.cuh"
 
 #include <algorithm>
 #include <vector>
@@ -35,7 +36,6 @@ namespace mlb {
 namespace {
 
 constexpr int TR = 64;          // rows of Q per thread block of the apply kernel
-constexpr int LDX = TR + 4;     // leading dimension of the transposed tile
 
 struct ApplyParams {
     const float* q;             // blocks of rows (ld n): block i of matrix b at b * q_outer + i * q_stride
@@ -50,69 +50,89 @@ struct ApplyParams {
     unsigned long long total;   // matrices * blocks * tiles
 };
 
-// Q_block <- Q_block * B in place: TR rows at a time, the tile transposed in
-// shared memory so that four rows of a column are one 16-byte word, B row-major.
+// Q_block <- Q_block * B in place. A thread block takes a whole row block: B (n x n, row-major) is
+// loaded once, then TR rows of Q at a time, kept row-major in shared memory as they come (16-byte
+// copies); a thread holds 4 x 4 outputs and reads four k's of its four rows and of B's rows as
+// 16-byte words, so that the products run on packed FMAs two columns at a time.
 __global__ void __launch_bounds__(256) tsqr_apply_kernel(const ApplyParams p) {
     extern __shared__ __align__(16) float sm[];
-    float* Xs = sm;                      // [n][LDX]
-    float* Bs = sm + (size_t)p.n * LDX;  // [n][np]
-    const int n = p.n, np = p.np;
+    const int n = p.n, np = p.np, kp = (n + 3) & ~3, ldx = kp + 4;
+    float* Xs = sm;                       // [TR][ldx]
+    float* Bs = sm + (size_t)TR * ldx;    // [kp][np], rows and columns beyond n zero
     const int rg = threadIdx.x >> 4, cg = threadIdx.x & 15;   // 16 row quads x 16 column quads (per 64 columns)
-    for (unsigned long long work = blockIdx.x; work < p.total; work += gridDim.x) {
-        const unsigned tile = (unsigned)(work % p.tiles);
-        const unsigned long long blk = work / p.tiles;
+    const unsigned long long blocks_total = p.total / p.tiles;
+    for (unsigned long long blk = blockIdx.x; blk < blocks_total; blk += gridDim.x) {
         const unsigned i = (unsigned)(blk % p.blocks);
         const unsigned long long b = blk / p.blocks;
         const unsigned rows = i + 1 == p.blocks ? p.last_rows : p.rows;
-        const unsigned r0 = tile * TR;
-        if (r0 >= rows) continue;
-        const unsigned nr = min((unsigned)TR, rows - r0);
-        const float* Q = p.q + b * p.q_outer + (unsigned long long)i * p.q_stride + (size_t)r0 * n;
-        float* O = p.out + b * p.out_outer + (unsigned long long)i * p.out_stride + (size_t)r0 * p.out_ld;
-        const size_t ldo = (size_t)p.out_ld;
-        const bool vec = (ldo & 3) == 0 && (reinterpret_cast<size_t>(O) & 15) == 0;
         const float* B = p.up + (p.shared_up ? b : blk) * (unsigned long long)n * n;
         __syncthreads();
-        for (int idx = threadIdx.x; idx < n * np; idx += 256) {
+        for (int idx = threadIdx.x; idx < kp * np; idx += 256) {
             const int k = idx / np, c = idx % np;
-            Bs[idx] = c < n ? B[(size_t)k * n + c] : 0.0f;
+            Bs[idx] = (c < n && k < n) ? B[(size_t)k * n + c] : 0.0f;
         }
-        for (int idx = threadIdx.x; idx < TR * n; idx += 256) {
-            const int r = idx / n, k = idx % n;
-            Xs[k * LDX + r] = (unsigned)r < nr ? Q[(size_t)r * n + k] : 0.0f;
-        }
-        __syncthreads();
-        for (int c0 = 0; c0 < np; c0 += 64) {
-            float acc[4][4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[a][e] = 0.0f;
-#pragma unroll 4
-            for (int k = 0; k < n; ++k) {
-                const float4 x = *reinterpret_cast<const float4*>(Xs + k * LDX + 4 * rg);
-                const float4 w = *reinterpret_cast<const float4*>(Bs + k * np + c0 + 4 * cg);
-                const float xv[4] = {x.x, x.y, x.z, x.w}, wv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int a = 0; a < 4; ++a)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[a][e] = fmaf(xv[a], wv[e], acc[a][e]);
+        for (unsigned r0 = 0; r0 < rows; r0 += TR) {
+            const unsigned nr = min((unsigned)TR, rows - r0);
+            const float* Q = p.q + b * p.q_outer + (unsigned long long)i * p.q_stride + (size_t)r0 * n;
+            float* O = p.out + b * p.out_outer + (unsigned long long)i * p.out_stride + (size_t)r0 * p.out_ld;
+            const size_t ldo = (size_t)p.out_ld;
+            const bool vec = (ldo & 3) == 0 && (reinterpret_cast<size_t>(O) & 15) == 0;
+            if ((n & 3) == 0 && (reinterpret_cast<size_t>(Q) & 15) == 0) {
+                const int nq = n >> 2;
+                for (int idx = threadIdx.x; idx < TR * nq; idx += 256) {
+                    const int r = idx / nq, kq = idx % nq;
+                    const float4 v = (unsigned)r < nr ? *reinterpret_cast<const float4*>(Q + (size_t)r * n + 4 * kq)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4*>(Xs + r * ldx + 4 * kq) = v;
+                }
+            } else {
+                for (int idx = threadIdx.x; idx < TR * kp; idx += 256) {
+                    const int r = idx / kp, k = idx % kp;
+                    Xs[r * ldx + k] = ((unsigned)r < nr && k < n) ? Q[(size_t)r * n + k] : 0.0f;
+                }
             }
+            __syncthreads();
+            for (int c0 = 0; c0 < np; c0 += 64) {
+                using small::pair_t;
+                pair_t acc[4][2];
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const unsigned r = 4 * rg + a;
-                if (r < nr) {
-                    const int c = c0 + 4 * cg;
-                    if (vec && c + 3 < n) {   // the rows are 16-byte aligned: one word a thread
-                        *reinterpret_cast<float4*>(O + (size_t)r * ldo + c) =
-                            make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
-                    } else {
+                for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = small::pack(0.0f, 0.0f);
+#pragma unroll 2
+                for (int k0 = 0; k0 < kp; k0 += 4) {
+                    float4 x[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (c + e < n) O[(size_t)r * ldo + c + e] = acc[a][e];
+                    for (int a = 0; a < 4; ++a) x[a] = *reinterpret_cast<const float4*>(Xs + (4 * rg + a) * ldx + k0);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(Bs + (k0 + kk) * np + c0 + 4 * cg);
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) {
+                            const float xv = kk == 0 ? x[a].x : kk == 1 ? x[a].y : kk == 2 ? x[a].z : x[a].w;
+                            const pair_t xx = small::pack(xv, xv);
+                            acc[a][0] = small::fma2(xx, w.x, acc[a][0]);
+                            acc[a][1] = small::fma2(xx, w.y, acc[a][1]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const unsigned r = 4 * rg + a;
+                    if (r < nr) {
+                        const int c = c0 + 4 * cg;
+                        float o[4];
+                        small::unpack(acc[a][0], o[0], o[1]);
+                        small::unpack(acc[a][1], o[2], o[3]);
+                        if (vec && c + 3 < n) {   // the rows are 16-byte aligned: one word a thread
+                            *reinterpret_cast<float4*>(O + (size_t)r * ldo + c) = make_float4(o[0], o[1], o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (c + e < n) O[(size_t)r * ldo + c + e] = o[e];
+                        }
                     }
                 }
             }
+            __syncthreads();      // the tile has been read: the next one may overwrite it
         }
     }
 }
@@ -147,7 +167,8 @@ void launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q, 
                        bool shared_up, uint32_t batch, uint32_t blocks, uint32_t rows, uint32_t last_rows, uint32_t n) {
     if (batch == 0 || blocks == 0 || n == 0 || std::max(rows, last_rows) == 0) return;
     const int np = (int)((n + 63) / 64 * 64);
-    const size_t smem = ((size_t)n * LDX + (size_t)n * np) * sizeof(float);
+    const int kp = ((int)n + 3) & ~3;
+    const size_t smem = ((size_t)TR * (kp + 4) + (size_t)kp * np) * sizeof(float);
     cuda_check(cudaFuncSetAttribute(tsqr_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                "tsqr_apply shared memory");
     ApplyParams a{};
@@ -159,7 +180,7 @@ void launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q, 
     a.q_outer = q_outer; a.q_stride = q_stride;
     a.out_outer = out_outer; a.out_stride = out_stride; a.out_ld = out_ld;
     a.total = (uint64_t)batch * blocks * a.tiles;
-    const unsigned grid = (unsigned)std::min<uint64_t>(a.total, (uint64_t)ctx.sm_count * 8);
+    const unsigned grid = (unsigned)std::min<uint64_t>((uint64_t)batch * blocks, (uint64_t)ctx.sm_count * 8);
     tsqr_apply_kernel<<<grid, 256, smem, stream>>>(a);
     cuda_check(cudaGetLastError(), "tsqr_apply launch");
 }
