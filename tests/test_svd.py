@@ -271,3 +271,48 @@ def test_gpu_qr_workspace_is_not_clobbered():
     u1, s1, vt1, _ = gpu_svd(a)
     assert np.array_equal(s0, s1) and np.array_equal(u0, u1) and np.array_equal(vt0, vt1)
     check_svd(a, u1, s1, vt1, s_ref=np.linalg.svd(a.astype(np.float64), compute_uv=False))
+
+
+@pytest.mark.gpu
+def test_gpu_binding_opcheck_compile_and_threads():
+    """The operators under torch.library.opcheck and torch.compile (full graph), and from several threads at once
+    on their own streams (the library keeps stream and device per thread, the SVD's scratch per stream)."""
+    import threading
+    a = torch.randn(3, 40, 6, device="cuda")
+    torch.library.opcheck(torch.ops.metal_linalg.svd, (a,), test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(torch.ops.metal_linalg.svdvals, (a,), test_utils=("test_schema", "test_faketensor"))
+
+    @torch.compile(backend="aot_eager", fullgraph=True)
+    def f(x):
+        u, s, vh = mlt.svd(x)
+        return (u * s.unsqueeze(-2)) @ vh, mlt.svdvals(x)
+
+    rec, vals = f(a)
+    assert (rec - a).abs().max().item() < 1e-4
+    assert (vals.double() - torch.linalg.svdvals(a.double())).abs().max().item() < 1e-4
+
+    b = torch.randn(512, 200, 24, device="cuda")
+    ref = torch.linalg.svdvals(b.double())
+    torch.cuda.synchronize()
+    errors = []
+
+    def work():
+        try:
+            with torch.cuda.stream(torch.cuda.Stream()):
+                for _ in range(4):
+                    s = mlt.svdvals(b)
+                    u, s2, vh = mlt.svd(b)
+                torch.cuda.current_stream().synchronize()
+                if (s.double() - ref).abs().max().item() > 1e-3 or (s2 - s).abs().max().item() > 1e-4:
+                    errors.append("values differ")
+                if ((u * s2.unsqueeze(-2)) @ vh - b).norm().item() / b.norm().item() > RECON_TOL:
+                    errors.append("reconstruction")
+        except Exception as e:      # surfaced below
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=work) for _ in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
