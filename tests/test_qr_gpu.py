@@ -8,7 +8,6 @@ binding), with the tolerances of the benchmark definition: ||A - QR||_F / ||A||_
 and ||Q^T Q - I||_F at most 10 n eps (eps = 2^-23), R within 1e-4 relative of
 the oracle's after sign normalisation, R's strict lower triangle exactly zero.
 """
-import ctypes
 import os
 import sys
 
