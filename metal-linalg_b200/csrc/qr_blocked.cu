@@ -416,7 +416,10 @@ struct MergeParams {
     float*       tagg;      // [128][128]
 };
 
-__global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
+// One block: its time is the latency of its loads and stores, so it is given every thread a block may have.
+constexpr int kMergeThreads = 1024;
+
+__global__ void __launch_bounds__(kMergeThreads) merge_t_kernel(const MergeParams p) {
     dependency_wait();
     extern __shared__ __align__(16) float dsm[];
     float (*Ta)[129] = reinterpret_cast<float (*)[129]>(dsm);
@@ -424,7 +427,7 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
     float (*X)[33]   = reinterpret_cast<float (*)[33]>(dsm + 2 * 128 * 129);
     const int t = threadIdx.x;
     const int width = 32 * (int)p.panels;
-    for (int idx = t; idx < 128 * 128; idx += 256) {
+    for (int idx = t; idx < 128 * 128; idx += kMergeThreads) {
         const int i = idx >> 7, j = idx & 127;
         float v = 0.0f;
         if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) v = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
@@ -435,7 +438,7 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
     __syncthreads();
     for (uint32_t q = 1; q < p.panels; ++q) {
         const int c0 = 32 * (int)q;
-        for (int idx = t; idx < c0 * 32; idx += 256) {      // X = G(0:c0, c0:c0+32) T_q
+        for (int idx = t; idx < c0 * 32; idx += kMergeThreads) {      // X = G(0:c0, c0:c0+32) T_q
             const int i = idx >> 5, c = idx & 31;
             float a = 0.0f;
 #pragma unroll 8
@@ -443,7 +446,7 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
             X[i][c] = a;
         }
         __syncthreads();
-        for (int idx = t; idx < c0 * 32; idx += 256) {
+        for (int idx = t; idx < c0 * 32; idx += kMergeThreads) {
             const int i = idx >> 5, c = idx & 31;
             float a = 0.0f;
             for (int k = i; k < c0; ++k) a = fmaf(Ta[i][k], X[k][c], a);   // T is upper triangular
@@ -451,7 +454,7 @@ __global__ void __launch_bounds__(256) merge_t_kernel(const MergeParams p) {
         }
         __syncthreads();
     }
-    for (int idx = t; idx < 128 * 128; idx += 256) p.tagg[idx] = Ta[idx >> 7][idx & 127];
+    for (int idx = t; idx < 128 * 128; idx += kMergeThreads) p.tagg[idx] = Ta[idx >> 7][idx & 127];
 }
 
 // The two large products run on the tensor cores (3xTF32, tc_gemm.cu) unless QR_TENSOR=0 asks for
@@ -505,7 +508,7 @@ void build_aggregate_t(cudaStream_t stream, const float* Y, size_t ldy, uint32_t
         launch_dependent(gram_sum_kernel, (AG * gld + 255) / 256, 256, 0, stream, zp, chunks, AG * gld);
         mp.gram = zp; mp.chunks = chunks; mp.gld = gld;
     }
-    launch_dependent(merge_t_kernel, 1, 256, kMergeSmem, stream, mp);
+    launch_dependent(merge_t_kernel, 1, kMergeThreads, kMergeSmem, stream, mp);
     cuda_check(cudaGetLastError(), "aggregate T launch");
 }
 
