@@ -299,20 +299,33 @@ __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restr
 // The same for a narrow update (the look-ahead's 128 columns): eight columns a block, so that a
 // narrow Z still spreads over many blocks; T is read from global memory (L2) as it is.
 // Grid ceil(nc / 8); thread (i, half) computes Z[i][4 half .. + 3] of the block's eight columns.
-__global__ void __launch_bounds__(256) reduce_t_narrow_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
+__global__ void __launch_bounds__(1024) reduce_t_narrow_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
                                                               uint32_t ncp, const float* __restrict__ T, int transposed,
                                                               float* Z) {
     dependency_wait();
     __shared__ __align__(16) float Zs[128][8];
     const uint32_t j0 = blockIdx.x * 8;
-    for (int idx = threadIdx.x; idx < 128 * 8; idx += 256) {
+    {   // 1024 threads, an entry each, eight loads in flight; the chunks are added in order
+        const int idx = threadIdx.x;
         const uint32_t k = idx >> 3, j = j0 + (idx & 7);
         float sum = 0.0f;
-        if (j < nc)
-            for (uint32_t ch = 0; ch < chunks; ++ch) sum += Zp[((size_t)ch * AG + k) * ncp + j];
+        if (j < nc) {
+            const float* src = Zp + (size_t)k * ncp + j;
+            const size_t step = (size_t)AG * ncp;
+            uint32_t ch = 0;
+            for (; ch + 8 <= chunks; ch += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(ch + u) * step];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) sum += v[u];
+            }
+            for (; ch < chunks; ++ch) sum += src[(size_t)ch * step];
+        }
         Zs[k][idx & 7] = sum;
     }
     __syncthreads();
+    if (threadIdx.x >= 256) return;
     const int i = threadIdx.x & 127, h = threadIdx.x >> 7;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 8
@@ -486,7 +499,7 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, ytsp, error);
     else if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
-    if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 256, 0, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 1024, 0, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     if (split) launch_tc_yz_split(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, ysp, zsp, error);
     else if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
