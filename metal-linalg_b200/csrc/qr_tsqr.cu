@@ -13,7 +13,7 @@
 //             by the block-per-matrix kernel (qr_mid.cu), its Q written in place
 //             into the output Q and its n x n R onto a stack;
 //   level l   the stack of R's (itself a tall matrix, c/n times shorter) is cut
-//             and factored the same way, until at most 1024 rows remain, which
+//             and factored the same way, until fewer than two blocks' rows remain, which
 //             one block factors: its R is the matrix's R;
 //   down      Q's blocks are multiplied from the right by the n x n blocks of
 //             the level above, level by level (tsqr_apply_kernel below).
@@ -151,7 +151,9 @@ std::vector<Level> plan(uint32_t m, uint32_t n) {
     std::vector<Level> levels;
     const uint32_t c = block_rows(n);
     uint32_t rows = m;
-    while (rows > 1024) {
+    // down to fewer than two blocks' worth of rows: the top is then at most 2c - 1 rows, 256 x n after a level of
+    // four blocks (a block of 1024 rows, the most a thread block holds, takes five times as long as one of 256)
+    while (rows >= 2 * c) {
         Level L{rows, c, rows / c, 0};
         L.last_rows = rows - (L.blocks - 1) * c;
         levels.push_back(L);
