@@ -184,11 +184,11 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     const bool spread = qr_gpu_backend(m, n, batch) == QrBackend::streaming_reduced;
     if (mid && !spread) return QrKernel::mid;
     // a lone tall thin matrix of 64 columns or more is faster through the blocked QR's cluster panels where
-    // those hold its rows (8192 x 128: 0.59 ms against 2.2 ms; 4096 x 64: 0.22 against 0.31; 16384 x 64: 0.37
-    // against 0.42), and so are up to three of 128 columns (four: 2.35 against 2.20); two of 64 columns
+    // those hold its rows (8192 x 128: 0.59 ms against 1.56 ms; 4096 x 64: 0.22 against 0.31; 16384 x 64: 0.37
+    // against 0.42), and so are two of 128 columns (1.22 against 1.57; three: 1.8 against 1.57); two of 64 columns
     // (4096 x 64: 0.43 against 0.31) and any of 32 (16384 x 32: 0.20 against 0.16) go to the tree, as every
     // batch does (16 of 8192 x 128: 4.5 ms against 9.7 ms)
-    const uint32_t few = n >= 128 ? 3u : n >= 64 ? 1u : 0u;
+    const uint32_t few = n >= 128 ? 2u : n >= 64 ? 1u : 0u;
     const bool lone = batch <= few && mlb::panel_fast_fits(m, 1) && mlb::qr_blocked_fits(m, n);
     if (tsqr && !lone) return QrKernel::tsqr;
     if (mid && !mlb::qr_blocked_fits(m, n)) return QrKernel::mid;
