@@ -182,7 +182,6 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     }
     if (small) return QrKernel::small;
     const bool spread = qr_gpu_backend(m, n, batch) == QrBackend::streaming_reduced;
-    if (mid && !spread) return QrKernel::mid;
     // a lone tall thin matrix of 64 columns or more is faster through the blocked QR's cluster panels where
     // those hold its rows (8192 x 128: 0.59 ms against 1.56 ms; 4096 x 64: 0.22 against 0.31; 16384 x 64: 0.37
     // against 0.42), and so are two of 128 columns (1.22 against 1.57; three: 1.8 against 1.57); two of 64 columns
@@ -190,7 +189,12 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     // batch does (16 of 8192 x 128: 4.5 ms against 9.7 ms)
     const uint32_t few = n >= 128 ? 2u : n >= 64 ? 1u : 0u;
     const bool lone = batch <= few && mlb::panel_fast_fits(m, 1) && mlb::qr_blocked_fits(m, n);
-    if (tsqr && !lone) return QrKernel::tsqr;
+    // the tree also takes the tall thin matrices a block could hold (512 to 1024 rows): its blocks of 256 rows
+    // run the panels with a column per lane, which one block of more rows cannot (1024 x 64: 0.21 against 0.50 ms
+    // at any batch up to 64; 512 x 32: 0.09 against 0.15)
+    // (a lone matrix leaves the tree for the blocked QR only, never for one block)
+    if (tsqr && !(lone && (spread || !mid))) return QrKernel::tsqr;
+    if (mid && !spread) return QrKernel::mid;
     if (mid && !mlb::qr_blocked_fits(m, n)) return QrKernel::mid;
     return QrKernel::blocked;
 }

@@ -302,7 +302,9 @@ void tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t
 
 bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc) {
     // reduced or R alone (Q of n columns or none), at most 128 columns, at least two levels' worth of rows
-    return n >= 1 && n <= 128 && m > 1024 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
+    // reduced or R alone (Q of n columns or none), at most 128 columns, at least two blocks of rows and eight times
+    // as tall as wide (640 x 96 is faster in one block; 512 x 64 and 1024 x 128 are faster here)
+    return n >= 1 && n <= 128 && m >= 512 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
 }
 
 void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr) {

@@ -140,7 +140,7 @@ def test_small_square_off_a_16_byte_boundary():
     check(a, q.cpu().numpy(), r.cpu().numpy(), "reduced", r_ref)
 
 
-TALL = [(1025, 8), (1500, 64), (2048, 64), (4096, 16), (5000, 33), (20000, 40), (17000, 24), (9000, 128), (70000, 5)]
+TALL = [(512, 32), (512, 64), (700, 50), (1000, 100), (1024, 128), (1024, 1), (1025, 8), (1500, 64), (2048, 64), (4096, 16), (5000, 33), (20000, 40), (17000, 24), (9000, 128), (70000, 5)]
 
 
 @pytest.mark.parametrize("mode", ["reduced", "r"])
@@ -551,6 +551,9 @@ def test_device_queries():
     assert mlt.qr_kernel(8192, 128, 2) == "blocked" and mlt.qr_kernel(8192, 128, 3) == "tsqr"
     assert mlt.qr_kernel(2048, 32, 2) == "tsqr" and mlt.qr_kernel(2048, 32, 1) == "tsqr" and mlt.qr_kernel(4096, 64, 2) == "tsqr"
     assert mlt.qr_kernel(1 << 20, 32, 1) == "tsqr" and mlt.qr_kernel(65536, 64, 64) == "tsqr"
+    # tall thin matrices of 512 to 1024 rows go to the tree too, unless less than eight times as tall as wide
+    assert mlt.qr_kernel(1024, 64, 16) == "tsqr" and mlt.qr_kernel(512, 32, 1) == "tsqr" and mlt.qr_kernel(640, 96, 16) == "mid"
+    assert mlt.qr_kernel(1024, 128, 1) == "blocked" and mlt.qr_kernel(1024, 64, 16, "complete") == "mid"
     assert mlt.qr_kernel(128, 128, 1) == "mid" and mlt.qr_kernel(4096, 4096, 64) == "blocked"
 
 
