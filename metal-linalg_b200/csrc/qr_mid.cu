@@ -381,47 +381,55 @@ __device__ void build_t(const Smem& s, int ldv, int mp) {
 // reduction a step; measured 4 times as fast as factor_panel on 256 rows). In: the panel in s.Vs.
 // Out as finish_panel's and build_t's: the factored panel in the scratch matrix, the clean V in
 // s.Vs, T in s.Ts. The trailing tile buffer and the partial-sum buffer serve as its scratch.
+template <int RW>      // rows a lane: 32 (up to 256 rows) or 64 (up to 512)
 __device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float* W, size_t ldw, int k0) {
     using namespace cols;
     cols::Smem& cs = *reinterpret_cast<cols::Smem*>(s.Cs);
     static_assert(sizeof(cols::Smem) <= 32 * LDC * sizeof(float), "the tile buffer holds the panel scratch");
     float* pub = s.Zp;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nw = (mp + 31) >> 5;          // the warps that hold rows
-    pair_t x2[16];
+    const int nw = (mp + RW - 1) / RW;          // the warps that hold rows
+    pair_t x2[RW / 2];
     float my_sc = 0.0f;
     if (warp < nw) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const int row0 = warp * 32 + 4 * q;
+        for (int q = 0; q < RW / 4; ++q) {
+            const int row0 = warp * RW + 4 * q;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (row0 < mp) v = *reinterpret_cast<const float4*>(s.Vs + lane * ldv + row0);
             x2[2 * q]     = pack(v.x, v.y);
             x2[2 * q + 1] = pack(v.z, v.w);
         }
-        factor_cols<32, false>(x2, cs, pub, nullptr, my_sc, nw);
+        factor_cols<RW, false>(x2, cs, pub, nullptr, my_sc, nw);
     }
     __syncthreads();
     if (warp == 0) build_t_to(cs, s.Ts, LDZ);
     if (warp < nw) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < RW / 4; ++q) {
             float e[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const int r = 4 * q + t, row = warp * 32 + r;
-                const float raw = warp == 0 ? cs.rows[r][lane] : row_of<32>(x2, r);
+                const int r = 4 * q + t, row = warp * RW + r;
+                // the block's first 32 rows were retired to cs.rows by warp 0; every other row is still in registers
+                const float raw = (warp == 0 && r < 32) ? cs.rows[r & 31][lane] : row_of<RW>(x2, r);
                 const float g = row > lane ? raw * my_sc : raw;      // R, beta on the diagonal, the unit-diagonal reflector below
                 const bool in = lane < jb && row < mp;
                 if (in) W[(size_t)(k0 + row) * ldw + k0 + lane] = g;
                 e[t] = in ? (row < lane ? 0.0f : (row == lane ? 1.0f : g)) : 0.0f;
             }
-            *reinterpret_cast<float4*>(s.Vs + lane * ldv + warp * 32 + 4 * q) = make_float4(e[0], e[1], e[2], e[3]);
+            // (a lane's last rows may lie beyond the column's end in shared memory: ldv follows the matrix's rows)
+            if (warp * RW + 4 * q + 3 < ldv) *reinterpret_cast<float4*>(s.Vs + lane * ldv + warp * RW + 4 * q) = make_float4(e[0], e[1], e[2], e[3]);
         }
     }
     __syncthreads();
 }
 
+// PRW: the most rows a lane holds in a panel factored with a column per lane. The instantiation for 64 (panels
+// of 257 to 512 rows) needs more registers than two blocks a multiprocessor leave and spills; it is launched
+// only for matrices of 257 to 512 rows, where it still wins (512 x 512: 13.1 against 14.2 ms for 296 matrices),
+// so that every other shape runs the instantiation for 32, which does not.
+template <int PRW>
 __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
     extern __shared__ __align__(16) float smem_raw[];
     const Smem s = carve(smem_raw, p.ldv);
@@ -499,7 +507,9 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
             else         load_tile(s.Vs, ldv, W, n, k0, mp, k0, jb, LoadPlain{});
             __syncthreads();
             if (mp <= 256 && p.by_columns) {
-                factor_panel_cols(s, ldv, mp, jb, W, n, k0);
+                factor_panel_cols<32>(s, ldv, mp, jb, W, n, k0);
+            } else if (PRW == 64 && mp <= 512 && p.by_columns) {
+                factor_panel_cols<PRW>(s, ldv, mp, jb, W, n, k0);
             } else {
                 factor_panel(s, ldv, mp, jb);
                 finish_panel(s, ldv, mp, jb, W, n, k0);
@@ -606,16 +616,21 @@ bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
 }
 
 namespace {
+using MidKernel = void (*)(MidParams);
+MidKernel mid_kernel_for(uint32_t m) {
+    return (m > 256 && m <= 512 && mid_by_columns()) ? qr_mid_kernel<64> : qr_mid_kernel<32>;
+}
 uint64_t slot_floats_of(uint32_t m, uint32_t n) {
     const uint32_t K = m < n ? m : n;
     return (((uint64_t)m * n + 3) & ~(uint64_t)3) + (uint64_t)((K + JB - 1) / JB) * 1024;
 }
 uint32_t slots_of(const DeviceContext& ctx, uint32_t m, uint32_t batch) {
     const size_t smem = smem_bytes((int)((m + 31) / 32) * 32 + 4);
-    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    const MidKernel kernel = mid_kernel_for(m);
+    cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                "qr_mid shared memory");
     int per_sm = 0;
-    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NT, smem), "qr_mid occupancy");
     if (per_sm < 1) throw std::runtime_error("qr_mid: the matrix does not fit a thread block");
     return (uint32_t)std::min<uint64_t>(batch, (uint64_t)per_sm * ctx.sm_count);
 }
@@ -645,14 +660,15 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr,
     p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
 
     const size_t smem = smem_bytes(p.ldv);
-    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    const MidKernel kernel = mid_kernel_for(pr.m);
+    cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                "qr_mid shared memory");
     int per_sm = 0;
-    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NT, smem), "qr_mid occupancy");
     if (per_sm < 1) throw std::runtime_error("qr_mid: the matrix does not fit a thread block");
     const uint32_t slots = (uint32_t)std::min<uint64_t>(pr.batch, (uint64_t)per_sm * ctx.sm_count);
     p.ws = o.ws ? o.ws : static_cast<float*>(ctx.workspace(stream, (size_t)slots * p.slot_floats * sizeof(float)));
-    qr_mid_kernel<<<slots, NT, smem, stream>>>(p);
+    kernel<<<slots, NT, smem, stream>>>(p);
     cuda_check(cudaGetLastError(), "qr_mid launch");
 }
 
@@ -730,15 +746,16 @@ void launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& pr) 
                                     " matrix needs " + std::to_string(p.slot_floats * sizeof(float)) +
                                     " bytes of scratch; the built-in scratch holds " +
                                     std::to_string(kStaticScratchFloats * sizeof(float)));
-    cuda_check(cudaFuncSetAttribute(qr_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    const MidKernel kernel = mid_kernel_for(pr.m);
+    cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                "qr_mid shared memory");
     int per_sm = 0;
-    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qr_mid_kernel, NT, smem), "qr_mid occupancy");
+    cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NT, smem), "qr_mid occupancy");
     if (per_sm < 1) throw std::runtime_error("[qr_no_alloc] the matrix does not fit a thread block");
     uint64_t slots = std::min<uint64_t>(pr.batch, (uint64_t)per_sm * sms);
     slots = std::min<uint64_t>(slots, kStaticScratchFloats / p.slot_floats);   // fewer blocks, each looping longer
     p.ws = scratch;
-    qr_mid_kernel<<<(unsigned)slots, NT, smem, stream>>>(p);
+    kernel<<<(unsigned)slots, NT, smem, stream>>>(p);
     cuda_check(cudaGetLastError(), "qr_mid launch");
 }
 

@@ -219,10 +219,11 @@ def test_blocked_fallback_paths(switch):
     assert harness.r_parity(r1, r_ref) <= 1e-4
 
 
-@pytest.mark.parametrize("shape", [(256, 256), (200, 64), (250, 300), (300, 96)])
+@pytest.mark.parametrize("shape", [(256, 256), (200, 64), (250, 300), (300, 96), (476, 64), (257, 40), (512, 512), (450, 500)])
 def test_mid_panel_paths(shape):
-    """The mid kernel's panels of at most 256 rows with a column per lane (the default) and a thread per
-    entry (QR_MID_ROWS=1; panels above 256 rows always) give the same factorisation."""
+    """The mid kernel's panels with a column per lane (the default: 32 rows a lane up to 256 rows, 64 rows a lane
+    in the instantiation for matrices of 257 to 512 rows) and a thread per entry (QR_MID_ROWS=1; panels above
+    512 rows always) give the same factorisation."""
     m, n = shape
     rng = np.random.default_rng(m + n)
     a = rng.standard_normal((5, m, n)).astype(np.float32)
