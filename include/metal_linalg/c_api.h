@@ -125,7 +125,10 @@ const char* metal_linalg_svdvals_backend(uint32_t rows, uint32_t cols, uint32_t 
  * ------------------------------------------------------------------------- */
 
 /* The CUDA stream (a cudaStream_t as a pointer; NULL for the default stream)
- * this thread's calls on device pointers are enqueued on. Thread-local. */
+ * this thread's calls on device pointers are enqueued on. Thread-local, and one
+ * stream for every GPU: a stream belongs to the GPU it was created on, so set it
+ * again before passing pointers that live on another GPU (a stream of the wrong
+ * GPU makes the launch fail with METAL_LINALG_RUNTIME_ERROR). */
 void  metal_linalg_set_stream(void* cuda_stream);
 void* metal_linalg_stream(void);
 
@@ -136,10 +139,31 @@ metal_linalg_status metal_linalg_set_device(int device);
 int                 metal_linalg_device(void);
 int                 metal_linalg_device_count(void);
 
-/* Waits for everything this thread has enqueued on its stream and reports a
- * kernel-side failure (a bounded wait that ran out) that only shows after the
- * work has run. */
+/* Waits for everything this thread has enqueued on its stream. Then reports, as
+ * METAL_LINALG_RUNTIME_ERROR with the GPU, the kind of wait and the last shape
+ * enqueued in the message, a kernel that gave up on one of its bounded waits on
+ * any GPU this library has used since the last report. Such a kernel has
+ * written NaN to the outputs of the matrices concerned, which by itself cannot
+ * be told from a NaN in the input: this call (or the status of a host-pointer
+ * call, which checks before it returns) is where the two differ. The
+ * reference reports a failed GPU command the same way, with the shape
+ * (src/qr_householder.mm:372-377, src/qr_blocked.mm:146-150, src/c_api.cpp:17-35). */
 metal_linalg_status metal_linalg_synchronize(void);
+
+/* No counterpart in the reference (whose buffers are the caller's). The library
+ * keeps scratch memory per (GPU, stream) between calls, as large as the largest
+ * call so far needed (hundreds of MB after a large blocked QR). This frees all
+ * of it, after waiting for every GPU concerned, and stores the bytes freed in
+ * *bytes_freed (may be NULL). Later calls allocate again. Call it after
+ * destroying streams the library has seen, or to hand the memory back. Not to
+ * be called while another thread is inside a call of this library. */
+metal_linalg_status metal_linalg_release_workspaces(uint64_t* bytes_freed);
+
+/* Testing aid, no counterpart in the reference: the next `count` matrices that
+ * the grid-parallel blocked QR factors are treated as if one of its tensor-core
+ * products had given up on a wait at once (NaN outputs, the error at the next
+ * metal_linalg_synchronize). Nothing on the GPU is made to wait, fault or fail. */
+void metal_linalg_inject_wait_failures(int count);
 
 /* ---------------------------------------------------------------------------
  * Device and routing

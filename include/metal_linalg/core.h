@@ -8,6 +8,7 @@
 // Buffers are either all CUDA device pointers on one GPU (the work is enqueued
 // on the calling thread's stream) or all host pointers (staged through the
 // GPU; the call returns when the results are written). See c_api.h.
+#include <cstddef>
 #include <cstdint>
 
 namespace metal_linalg {
@@ -30,7 +31,23 @@ namespace metal_linalg {
     void  set_device(int device);
     int   device();
     int   device_count();
+    // Waits for the calling thread's stream, then throws std::runtime_error if a
+    // kernel on any GPU this library has used gave up on one of its bounded
+    // waits since the last check (the matrices concerned hold NaN). The
+    // reference rethrows a failed command buffer with the shape
+    // (src/qr_householder.mm:372-377, src/qr_blocked.mm:146-150); a CUDA launch
+    // is asynchronous, so here the failure surfaces at this call, or at the end
+    // of a host-pointer call, which waits anyway.
     void  synchronize();
+    // Frees the scratch memory kept per (GPU, stream) between calls, after
+    // waiting for each GPU it touches; returns the bytes freed. The next call
+    // allocates again. For callers that create and destroy streams, or that
+    // need the memory back after one large factorisation.
+    size_t release_workspaces();
+    // Testing aid (no GPU is made to wait or fail): the next `count` matrices
+    // of the grid-parallel blocked QR are treated as if a tensor-core product
+    // had given up on a wait: NaN outputs, and the error at synchronize().
+    void  inject_wait_failures(int count);
 
     // -------------------------------------------------------------------------
     // Routing policy (reference: core.h:45-135, src/qr.mm:231-286)

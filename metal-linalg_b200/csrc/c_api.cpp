@@ -1,6 +1,10 @@
-// The C ABI (include/metal_linalg/c_api.h) over the buffer core: argument checks,
-// and exceptions turned into status codes with the message kept per thread
-// (reference: src/c_api.cpp:15-35,97-124,301-330).
+// The C ABI (include/metal_linalg/c_api.h) over the buffer core. Three things
+// happen here and nowhere else: a call's buffers are checked against the sizes
+// its shape implies, a C++ exception becomes one of the four status codes with
+// its message kept for metal_linalg_last_error(), and the C policy struct is
+// mapped onto the core's. The contract is the reference's (src/c_api.cpp: status
+// per exception class, thread-local message, NULL allowed only for a buffer that
+// would hold nothing); the code is this build's own.
 #include <metal_linalg/c_api.h>
 #include <metal_linalg/core.h>
 
@@ -8,227 +12,266 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <exception>
 #include <new>
 #include <stdexcept>
 #include <string>
 
-using namespace metal_linalg;
+namespace ml = metal_linalg;
 
 namespace {
 
-thread_local std::string g_last_error;
-thread_local std::string g_message;
+// One message per thread; it lives until that thread's next failure.
+thread_local std::string t_error;
+thread_local std::string t_notice;
 
-template <class F>
-metal_linalg_status guarded(F&& f) {
+// The status of the exception in flight, its message recorded.
+metal_linalg_status status_of_current_exception() {
     try {
-        f();
-        return METAL_LINALG_OK;
-    } catch (const std::invalid_argument& e) {
-        g_last_error = e.what();
-        return METAL_LINALG_INVALID_ARGUMENT;
+        throw;
     } catch (const std::bad_alloc&) {
-        g_last_error = "out of memory";
+        t_error = "out of memory";
         return METAL_LINALG_OUT_OF_MEMORY;
-    } catch (const std::exception& e) {
-        g_last_error = e.what();
+    } catch (const std::invalid_argument& bad) {
+        t_error = bad.what();
+        return METAL_LINALG_INVALID_ARGUMENT;
+    } catch (const std::exception& other) {       // CUDA failures, a kernel that gave up on a wait
+        t_error = other.what();
         return METAL_LINALG_RUNTIME_ERROR;
     } catch (...) {
-        g_last_error = "unknown error";
+        t_error = "an exception that is not a std::exception";
         return METAL_LINALG_RUNTIME_ERROR;
     }
 }
 
-void require(bool ok, const char* what) {
-    if (!ok) throw std::invalid_argument(what);
+template <typename Body>
+metal_linalg_status run(Body&& body) noexcept {
+    try {
+        body();
+    } catch (...) {
+        return status_of_current_exception();
+    }
+    return METAL_LINALG_OK;
 }
 
-// Inputs and required outputs may be null only when they hold nothing.
-bool present(const void* p, uint64_t count) { return p != nullptr || count == 0; }
-
-core::QrMode mode_of(metal_linalg_qr_mode mode) {
-    require(mode == METAL_LINALG_QR_REDUCED || mode == METAL_LINALG_QR_R || mode == METAL_LINALG_QR_COMPLETE,
-            "[qr] mode must be METAL_LINALG_QR_REDUCED, _R or _COMPLETE");
-    return mode == METAL_LINALG_QR_R ? core::QrMode::r
-           : mode == METAL_LINALG_QR_COMPLETE ? core::QrMode::complete : core::QrMode::reduced;
+// The same for the queries that return a value and have no status to give: `fallback` on any failure.
+template <typename T, typename Body>
+T query(T fallback, Body&& body) noexcept {
+    try {
+        return body();
+    } catch (...) {
+        status_of_current_exception();
+        return fallback;
+    }
 }
+
+// The buffers of one QR call, with the element counts its shape and mode imply.
+struct QrCall {
+    const char*      who;
+    ml::core::QrMode mode;
+    uint32_t         batch, rows, cols, q_cols, r_rows;
+
+    QrCall(const char* who_, int c_mode, uint32_t b, uint32_t m, uint32_t n) : who(who_), batch(b), rows(m), cols(n) {
+        switch (c_mode) {
+            case METAL_LINALG_QR_REDUCED:  mode = ml::core::QrMode::reduced; break;
+            case METAL_LINALG_QR_R:        mode = ml::core::QrMode::r; break;
+            case METAL_LINALG_QR_COMPLETE: mode = ml::core::QrMode::complete; break;
+            default:
+                throw std::invalid_argument(std::string(who) + " mode must be METAL_LINALG_QR_REDUCED, _R or _COMPLETE");
+        }
+        q_cols = ml::core::qr_q_cols(mode, m, n);
+        r_rows = ml::core::qr_r_rows(mode, m, n);
+    }
+    uint64_t a_count() const { return (uint64_t)batch * rows * cols; }
+    uint64_t q_count() const { return (uint64_t)batch * rows * q_cols; }
+    uint64_t r_count() const { return (uint64_t)batch * r_rows * cols; }
+    // A buffer that holds at least one element has to be there.
+    void need(const void* p, uint64_t count, const char* name) const {
+        if (count != 0 && p == nullptr) throw std::invalid_argument(std::string(who) + " " + name + " is NULL");
+    }
+    void check(const float* a, const float* q, const float* r) const {
+        need(a, a_count(), "a");
+        need(q, q_count(), "q");      // q_count() is 0 for R alone: q is then never looked at
+        need(r, r_count(), "r");
+    }
+};
+
+// The policy's settable fields, C struct member against core struct member.
+struct PolicyField {
+    uint32_t metal_linalg_qr_policy::*c;
+    unsigned ml::QrPolicy::*core;
+    bool     informational;      // reported, never set
+};
+constexpr PolicyField kPolicyFields[] = {
+    {&metal_linalg_qr_policy::m_crossover_small_batch, &ml::QrPolicy::m_crossover_small_batch, false},
+    {&metal_linalg_qr_policy::m_crossover_large_batch, &ml::QrPolicy::m_crossover_large_batch, false},
+    {&metal_linalg_qr_policy::batch_threshold, &ml::QrPolicy::batch_threshold, false},
+    {&metal_linalg_qr_policy::gpu_max_k, &ml::QrPolicy::gpu_max_k, false},
+    {&metal_linalg_qr_policy::gpu_min_batch_times_k, &ml::QrPolicy::gpu_min_batch_times_k, false},
+    {&metal_linalg_qr_policy::gpu_min_batch, &ml::QrPolicy::gpu_min_batch, false},
+    {&metal_linalg_qr_policy::gpu_cores, &ml::QrPolicy::gpu_cores, true},
+    {&metal_linalg_qr_policy::concurrent_matrices, &ml::QrPolicy::concurrent_matrices, true},
+    {&metal_linalg_qr_policy::gpu_large_min_k, &ml::QrPolicy::gpu_large_min_k, false},
+    {&metal_linalg_qr_policy::gpu_large_max_batch, &ml::QrPolicy::gpu_large_max_batch, false},
+    {&metal_linalg_qr_policy::gpu_min_k, &ml::QrPolicy::gpu_min_k, false},
+    {&metal_linalg_qr_policy::share_min_batch, &ml::QrPolicy::share_min_batch, false},
+};
 
 } // namespace
 
 extern "C" {
 
-const char* metal_linalg_last_error(void) { return g_last_error.c_str(); }
+const char* metal_linalg_last_error(void) { return t_error.c_str(); }
 
-metal_linalg_status metal_linalg_qr(const float* a, uint32_t batch, uint32_t rows, uint32_t cols, float* q,
-                                    float* r) {
-    return guarded([&] {
-        const uint64_t k = std::min(rows, cols);
-        require(present(a, (uint64_t)batch * rows * cols), "[qr] a is NULL");
-        require(present(q, (uint64_t)batch * rows * k), "[qr] q is NULL");
-        require(present(r, (uint64_t)batch * k * cols), "[qr] r is NULL");
-        core::qr({a, batch, rows, cols}, q, r);
-    });
-}
+// ---------------------------------------------------------------------------
+// QR
+// ---------------------------------------------------------------------------
 
 metal_linalg_status metal_linalg_qr_with_mode(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
                                               metal_linalg_qr_mode mode, float* q, float* r) {
-    return guarded([&] {
-        const core::QrMode m = mode_of(mode);
-        const uint64_t qc = core::qr_q_cols(m, rows, cols), rr = core::qr_r_rows(m, rows, cols);
-        require(present(a, (uint64_t)batch * rows * cols), "[qr] a is NULL");
-        if (qc) require(present(q, (uint64_t)batch * rows * qc), "[qr] q is NULL");
-        require(present(r, (uint64_t)batch * rr * cols), "[qr] r is NULL");
-        core::qr({a, batch, rows, cols}, qc ? q : nullptr, r, m);
+    return run([&] {
+        const QrCall call("[qr]", (int)mode, batch, rows, cols);
+        call.check(a, q, r);
+        ml::core::qr({a, batch, rows, cols}, call.q_cols ? q : nullptr, r, call.mode);
     });
+}
+
+metal_linalg_status metal_linalg_qr(const float* a, uint32_t batch, uint32_t rows, uint32_t cols, float* q, float* r) {
+    return metal_linalg_qr_with_mode(a, batch, rows, cols, METAL_LINALG_QR_REDUCED, q, r);
 }
 
 metal_linalg_status metal_linalg_qr_no_alloc(const float* a, uint32_t batch, uint32_t rows, uint32_t cols,
                                              metal_linalg_qr_mode mode, float* q, float* r) {
-    return guarded([&] {
-        const core::QrMode m = mode_of(mode);
-        const uint32_t qc = core::qr_q_cols(m, rows, cols), rr = core::qr_r_rows(m, rows, cols);
-        require(present(a, (uint64_t)batch * rows * cols), "[qr_no_alloc] a is NULL");
-        if (qc) require(present(q, (uint64_t)batch * rows * qc), "[qr_no_alloc] q is NULL");
-        require(present(r, (uint64_t)batch * rr * cols), "[qr_no_alloc] r is NULL");
-        if (batch == 0 || rows == 0 || cols == 0) return;   // nothing to factor (and nothing to allocate for it)
+    return run([&] {
+        const QrCall call("[qr_no_alloc]", (int)mode, batch, rows, cols);
+        call.check(a, q, r);
+        if (call.a_count() == 0) return;      // nothing to factor (and nothing to allocate for it)
         const int device = mlb::pointer_device(a);
-        require(device >= 0, "[qr_no_alloc] takes CUDA device pointers only (staging host memory would allocate)");
-        require(mlb::pointer_device(r) == device && (!qc || mlb::pointer_device(q) == device),
-                "[qr_no_alloc] a, q and r must be device pointers on one GPU");
+        if (device < 0)
+            throw std::invalid_argument("[qr_no_alloc] takes CUDA device pointers only (staging host memory would allocate)");
+        if (mlb::pointer_device(r) != device || (call.q_cols && mlb::pointer_device(q) != device))
+            throw std::invalid_argument("[qr_no_alloc] a, q and r must be device pointers on one GPU");
         mlb::QrProblem p{};
-        p.a = a; p.q = qc ? q : nullptr; p.r = r;
-        p.batch = batch; p.m = rows; p.n = cols; p.qc = qc; p.rr = rr;
+        p.a = a; p.q = call.q_cols ? q : nullptr; p.r = r;
+        p.batch = batch; p.m = rows; p.n = cols; p.qc = call.q_cols; p.rr = call.r_rows;
         mlb::launch_qr_mid_static(device, mlb::thread_stream(), p);
     });
 }
 
 uint64_t metal_linalg_qr_no_alloc_scratch_bytes(void) { return mlb::qr_mid_static_capacity_bytes(); }
 
+// ---------------------------------------------------------------------------
+// SVD
+// ---------------------------------------------------------------------------
+
 metal_linalg_status metal_linalg_svd(const float* a, uint32_t batch, uint32_t rows, uint32_t cols, float* u, float* s,
                                      float* vt, uint32_t* info) {
-    return guarded([&] {
-        require(present(a, (uint64_t)batch * rows * cols), "[svd] a is NULL");
-        require(present(s, (uint64_t)batch * std::min(rows, cols)), "[svd] s is NULL");
-        require((u == nullptr) == (vt == nullptr), "[svd] u and vt must both be given or both be NULL");
-        core::svd({a, batch, rows, cols}, u, s, vt, info);
+    return run([&] {
+        const uint64_t k = std::min(rows, cols);
+        if ((uint64_t)batch * rows * cols != 0 && !a) throw std::invalid_argument("[svd] a is NULL");
+        if ((uint64_t)batch * k != 0 && !s) throw std::invalid_argument("[svd] s is NULL");
+        if ((u == nullptr) != (vt == nullptr))
+            throw std::invalid_argument("[svd] u and vt must both be given or both be NULL");
+        ml::core::svd({a, batch, rows, cols}, u, s, vt, info);
     });
 }
+
 const char* metal_linalg_svd_backend(uint32_t rows, uint32_t cols, uint32_t batch) {
-    return svd_backend(rows, cols, batch) == SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+    return query<const char*>("unavailable", [&] {
+        return ml::svd_backend(rows, cols, batch) == ml::SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+    });
 }
 const char* metal_linalg_svdvals_backend(uint32_t rows, uint32_t cols, uint32_t batch) {
-    return svdvals_backend(rows, cols, batch) == SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+    return query<const char*>("unavailable", [&] {
+        return ml::svdvals_backend(rows, cols, batch) == ml::SvdBackend::qr_jacobi ? "qr_jacobi" : "unavailable";
+    });
 }
 
-void  metal_linalg_set_stream(void* cuda_stream) { set_stream(cuda_stream); }
-void* metal_linalg_stream(void) { return stream(); }
+// ---------------------------------------------------------------------------
+// Placement, waiting, memory
+// ---------------------------------------------------------------------------
+
+void  metal_linalg_set_stream(void* cuda_stream) { ml::set_stream(cuda_stream); }
+void* metal_linalg_stream(void) { return ml::stream(); }
 
 metal_linalg_status metal_linalg_set_device(int device) {
-    return guarded([&] { set_device(device); });
+    return run([&] { ml::set_device(device); });
 }
-int metal_linalg_device(void) { return device(); }
-int metal_linalg_device_count(void) { return device_count(); }
+int metal_linalg_device(void) { return ml::device(); }
+int metal_linalg_device_count(void) { return ml::device_count(); }
 
 metal_linalg_status metal_linalg_synchronize(void) {
-    return guarded([&] { synchronize(); });
+    return run([] { ml::synchronize(); });
 }
 
+metal_linalg_status metal_linalg_release_workspaces(uint64_t* bytes_freed) {
+    return run([&] {
+        const size_t freed = ml::release_workspaces();
+        if (bytes_freed) *bytes_freed = freed;
+    });
+}
+
+void metal_linalg_inject_wait_failures(int count) { ml::inject_wait_failures(count); }
+
+// ---------------------------------------------------------------------------
+// Device, host threads, routing
+// ---------------------------------------------------------------------------
+
 const char* metal_linalg_device_name(void) {
-    try {
-        return device_name();
-    } catch (...) {
-        return "";
-    }
+    return query<const char*>("", [] { return ml::device_name(); });
 }
 uint32_t metal_linalg_gpu_core_count(void) {
-    try {
-        return gpu_core_count();
-    } catch (...) {
-        return 0;
-    }
+    return query<uint32_t>(0u, [] { return (uint32_t)ml::gpu_core_count(); });
 }
 
 void        metal_linalg_set_calibration_notices(int) {}
 const char* metal_linalg_calibration_message(const char* decomposition) {
-    g_message.clear();
-    if (!decomposition) return g_message.c_str();
-    try {
-        const std::string source = qr_policy_source();
-        if (std::string(decomposition) == "QR" && source.rfind("default:", 0) == 0)
-            g_message = "metal-linalg: the QR routing table was measured on an NVIDIA B200; " + source;
-    } catch (...) {
+    t_notice.clear();
+    if (decomposition && std::string(decomposition) == "QR") {
+        const std::string source = query<std::string>(std::string(), [] { return std::string(ml::qr_policy_source()); });
+        if (source.compare(0, 8, "default:") == 0)
+            t_notice = "metal-linalg: the QR routing table was measured on an NVIDIA B200; " + source;
     }
-    return g_message.c_str();
+    return t_notice.c_str();
 }
 
-void     metal_linalg_set_cpu_threads(uint32_t n) { set_cpu_threads(n); }
-uint32_t metal_linalg_cpu_threads(void) { return cpu_threads(); }
-void     metal_linalg_set_cpu_only(int on) { set_cpu_only(on != 0); }
-int      metal_linalg_cpu_only(void) { return cpu_only() ? 1 : 0; }
+void     metal_linalg_set_cpu_threads(uint32_t n) { ml::set_cpu_threads(n); }
+uint32_t metal_linalg_cpu_threads(void) { return ml::cpu_threads(); }
+void     metal_linalg_set_cpu_only(int on) { ml::set_cpu_only(on != 0); }
+int      metal_linalg_cpu_only(void) { return ml::cpu_only() ? 1 : 0; }
 
 const char* metal_linalg_qr_backend(uint32_t rows, uint32_t cols, uint32_t batch) {
-    try {
-        return qr_backend(rows, cols, batch) == QrBackend::streaming_reduced ? "streaming_reduced" : "unblocked";
-    } catch (...) {
-        return "unblocked";
-    }
+    return query<const char*>("unblocked", [&] {
+        return ml::qr_backend(rows, cols, batch) == ml::QrBackend::streaming_reduced ? "streaming_reduced" : "unblocked";
+    });
 }
 
 const char* metal_linalg_qr_kernel(uint32_t rows, uint32_t cols, uint32_t batch, metal_linalg_qr_mode mode) {
-    try {
-        return core::qr_kernel_name(core::qr_kernel(rows, cols, batch, mode_of(mode)));
-    } catch (const std::exception& e) {
-        g_last_error = e.what();
-        return "";
-    }
+    return query<const char*>("", [&] {
+        const QrCall call("[qr_kernel]", (int)mode, batch, rows, cols);
+        return ml::core::qr_kernel_name(ml::core::qr_kernel(rows, cols, batch, call.mode));
+    });
 }
 
 metal_linalg_qr_policy metal_linalg_qr_policy_get(void) {
     metal_linalg_qr_policy out{};
-    try {
-        const QrPolicy p = qr_policy();
-        out.m_crossover_small_batch = p.m_crossover_small_batch;
-        out.m_crossover_large_batch = p.m_crossover_large_batch;
-        out.batch_threshold         = p.batch_threshold;
-        out.gpu_max_k               = p.gpu_max_k;
-        out.gpu_min_batch_times_k   = p.gpu_min_batch_times_k;
-        out.gpu_min_batch           = p.gpu_min_batch;
-        out.gpu_cores               = p.gpu_cores;
-        out.concurrent_matrices     = p.concurrent_matrices;
-        out.gpu_large_min_k         = p.gpu_large_min_k;
-        out.gpu_large_max_batch     = p.gpu_large_max_batch;
-        out.gpu_min_k               = p.gpu_min_k;
-        out.share_min_batch         = p.share_min_batch;
-    } catch (...) {
-    }
+    const ml::QrPolicy now = query<ml::QrPolicy>(ml::QrPolicy{}, [] { return ml::qr_policy(); });
+    for (const PolicyField& f : kPolicyFields) out.*f.c = now.*f.core;
     return out;
 }
 
-void metal_linalg_qr_policy_set(const metal_linalg_qr_policy* in) {
-    if (!in) return;
-    try {
-        QrPolicy p = qr_policy();
-        p.m_crossover_small_batch = in->m_crossover_small_batch;
-        p.m_crossover_large_batch = in->m_crossover_large_batch;
-        p.batch_threshold         = in->batch_threshold;
-        p.gpu_max_k               = in->gpu_max_k;
-        p.gpu_min_batch_times_k   = in->gpu_min_batch_times_k;
-        p.gpu_min_batch           = in->gpu_min_batch;
-        p.gpu_large_min_k         = in->gpu_large_min_k;
-        p.gpu_large_max_batch     = in->gpu_large_max_batch;
-        p.gpu_min_k               = in->gpu_min_k;
-        p.share_min_batch         = in->share_min_batch;
-        set_qr_policy(p);
-    } catch (...) {
-    }
+void metal_linalg_qr_policy_set(const metal_linalg_qr_policy* wanted) {
+    if (!wanted) return;
+    run([&] {
+        ml::QrPolicy next = ml::qr_policy();      // the informational fields keep what was detected
+        for (const PolicyField& f : kPolicyFields)
+            if (!f.informational) next.*f.core = wanted->*f.c;
+        ml::set_qr_policy(next);
+    });
 }
 
 const char* metal_linalg_qr_policy_source(void) {
-    try {
-        return qr_policy_source();
-    } catch (...) {
-        return "default:untuned-device";
-    }
+    return query<const char*>("default:untuned-device", [] { return ml::qr_policy_source(); });
 }
 
 } // extern "C"

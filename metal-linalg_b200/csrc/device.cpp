@@ -5,6 +5,7 @@
 #include "runtime.h"
 
 #include <atomic>
+#include <mutex>
 #include <thread>
 
 namespace metal_linalg {
@@ -40,6 +41,20 @@ int   device_count() { return mlb::device_count(); }
 
 void synchronize() {
     mlb::cuda_check(cudaStreamSynchronize(mlb::thread_stream()), "cudaStreamSynchronize");
+    mlb::throw_if_a_kernel_gave_up();
+}
+
+void inject_wait_failures(int count) { mlb::inject_wait_failures(count); }
+
+size_t release_workspaces() {
+    mlb::DeviceContext* all[64];
+    const int n = mlb::created_contexts(all, 64);
+    size_t freed = 0;
+    for (int i = 0; i < n; ++i) {
+        std::lock_guard<std::mutex> lock(all[i]->mutex);
+        freed += all[i]->release_workspaces();
+    }
+    return freed;
 }
 
 } // namespace metal_linalg

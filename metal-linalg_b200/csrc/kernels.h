@@ -99,6 +99,12 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
 
 // Small utilities shared by the launchers.
 void launch_fill_identity(cudaStream_t stream, float* q, uint32_t batch, uint32_t m, uint32_t cols);
+// out (row-major, contiguous float32) = the tensor `in` of element type `dtype` (the order of
+// metal_linalg::Dtype: float32, float64, float16, bfloat16, int8, uint8, int16, int32, int64, bool), of
+// `dims` <= kMaxConvertDims dimensions with the given shape and element strides.
+constexpr int kMaxConvertDims = 8;
+void launch_convert_to_f32(cudaStream_t stream, const void* in, int dtype, const uint32_t* shape, const int64_t* strides,
+                           int dims, float* out);
 
 // The small SVD behind a QR (svd_small.cu): one-sided Jacobi on the k x k factors r [batch, k, k],
 // k <= 128. s [batch, k] descending; with ur non-null also the factors' left vectors ur [batch, k, k]

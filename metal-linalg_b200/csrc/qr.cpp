@@ -202,6 +202,7 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
 void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices& a, float* q, float* r, QrMode mode,
                    int forced /* -1: route */) {
     const mlb::QrProblem p = problem(a, q, r, mode);
+    ctx.last_shape[0] = a.batch; ctx.last_shape[1] = a.rows; ctx.last_shape[2] = a.cols;
     const QrKernel k = forced >= 0 ? (QrKernel)forced : choose(ctx, a.rows, a.cols, a.batch, mode);
     switch (k) {
         case QrKernel::small:   mlb::launch_qr_small(ctx, stream, p); break;
@@ -269,6 +270,10 @@ void run_staged(mlb::DeviceContext& ctx, const Matrices& a, float* q, float* r, 
     }
     mlb::cuda_check(cudaStreamSynchronize(ctx.copy_out), "cudaStreamSynchronize");
     mlb::cuda_check(cudaStreamSynchronize(ctx.compute), "cudaStreamSynchronize");
+    if (const unsigned word = ctx.take_status())      // the call is complete here: a kernel that gave up is an error now
+        throw std::runtime_error("[qr] a kernel gave up on a bounded wait (status " + std::to_string(word) + ") on a batch of " +
+                                 std::to_string(a.batch) + " matrices of " + std::to_string(m) + " x " + std::to_string(n) +
+                                 "; their outputs are NaN");
 }
 
 void run(const Matrices& a, float* q, float* r, QrMode mode, int forced) {

@@ -45,7 +45,8 @@ constexpr int NB  = 32;     // panel width
 
 struct MatInfo {            // per matrix, written by the scan
     unsigned amax_bits;     // bit pattern of the largest magnitude (non-negative floats order as integers)
-    unsigned bad;           // a NaN or an infinity was seen
+    unsigned bad;           // bit 0: a NaN or an infinity was seen; kStatusTensorWait: a tensor-core product gave
+                            // up on a bounded wait. Either way the matrix's outputs are NaN.
 };
 
 __global__ void scan_kernel(const float* a, size_t count, MatInfo* info) {
@@ -79,10 +80,12 @@ __global__ void scale_copy_kernel(const float* a, float* w, uint32_t m, uint32_t
 }
 
 // R [rr][n] = the upper trapezoid of W's first K rows * 2^e, zeros elsewhere; NaN for a non-finite matrix
+// and a wait that ran out during the factorisation is passed on to the context's status word
 __global__ void r_out_kernel(const float* w, uint32_t ldw, float* r, uint32_t rr, uint32_t n, uint32_t K,
-                             const MatInfo* info) {
+                             const MatInfo* info, unsigned* status) {
     const Pow2 up(info_exponent(info));
     const bool bad = info->bad != 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && (info->bad & kStatusTensorWait)) atomicOr(status, (unsigned)kStatusTensorWait);
     const size_t total = (size_t)rr * n;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t row = i / n, c = i % n;
@@ -739,13 +742,13 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         if (e && std::atoi(e) >= 1) nlanes = std::min<uint32_t>(nlanes, (uint32_t)std::atoi(e));
     }
     float* ws_all = static_cast<float*>(ctx.workspace(stream, (size_t)nlanes * off * sizeof(float)));
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;      // the opt-in is recorded per GPU
+    if (once.first(ctx.device)) {
         cuda_check(cudaFuncSetAttribute(reduce_t_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kReduceWideSmem), "reduce_t_wide shared memory");
         cuda_check(cudaFuncSetAttribute(merge_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMergeSmem),
                    "merge_t shared memory");
-        configured = true;
+        once.mark(ctx.device);
     }
     const cudaStream_t caller = stream;
     if (nlanes > 1) {      // the extra lanes start after what the caller's stream holds
@@ -772,6 +775,8 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
 
         cuda_check(cudaMemsetAsync(info, 0, sizeof(MatInfo), stream), "cudaMemsetAsync");
+        if (take_injected_wait_failure())      // a test's stand-in for a wait that ran out: every byte of `bad` = the bit
+            cuda_check(cudaMemsetAsync(&info->bad, (int)kStatusTensorWait, sizeof(unsigned), stream), "cudaMemsetAsync");
         scan_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, (size_t)m * n, info);
         scale_copy_kernel<<<grid_for((size_t)m * n), 256, 0, stream>>>(A, W, m, n, ldw, info);
 
@@ -858,7 +863,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
             cuda_check(cudaEventRecord(ev_panel[0], ps), "cudaEventRecord");
             cuda_check(cudaStreamWaitEvent(us, ev_panel[0], 0), "cudaStreamWaitEvent");
         }
-        r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info);
+        r_out_kernel<<<grid_for((size_t)rr * n), 256, 0, stream>>>(W, ldw, R, rr, n, K, info, ctx.status);
         if (!qc) continue;
 
         if (forward_q) {

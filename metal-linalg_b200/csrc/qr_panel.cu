@@ -732,15 +732,15 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
     TopParams tp{Sl, leaves * 32, Vl, Tl, Bp, panel, ldw, y, ldy, t, jb, mp, Rt};
     if (by_columns) {
-        static const bool configured = [] {
+        static PerDeviceOnce once;      // the opt-in is recorded per GPU
+        if (const int device = current_device(); once.first(device)) {
             // static and dynamic shared memory together pass the 48 KB that need no opt-in
             cuda_check(cudaFuncSetAttribute(panel_top_cols_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             32 * 256 * (int)sizeof(float)), "panel_top_cols shared memory");
             cuda_check(cudaFuncSetAttribute(panel_top_cols_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             32 * 512 * (int)sizeof(float)), "panel_top_cols shared memory");
-            return true;
-        }();
-        (void)configured;
+            once.mark(device);
+        }
         if (rpt == 1) launch_dependent(panel_leaf_cols_kernel<32>, leaves, PT, 0, stream, lp);
         else launch_dependent(panel_leaf_cols_kernel<64>, leaves, PT, 0, stream, lp);
         if (leaves * 32 <= PT) launch_dependent(panel_top_cols_kernel<32>, 1, PT, 32 * 256 * sizeof(float), stream, tp);

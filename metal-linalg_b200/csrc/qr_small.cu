@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, min_blocks(R, C)) qr_small_ker
 }
 
 template <int R, int G, int C, bool Square>
-void launch(cudaStream_t stream, const SmallParams& p, int sm_count) {
+void launch(cudaStream_t stream, const SmallParams& p, int sm_count, int device) {
     constexpr int per_warp = 32 / G;
     constexpr int steps = R < G * C ? R : G * C;
     static const int max_warps = [] {
@@ -158,16 +158,16 @@ void launch(cudaStream_t stream, const SmallParams& p, int sm_count) {
     const uint32_t per_block = per_warp * warps_per_block;
     const uint32_t blocks = (p.batch + per_block - 1) / per_block;
     const size_t smem = (size_t)per_block * slot_floats(R, steps) * sizeof(float);
-    static const bool configured = [] {
+    static PerDeviceOnce once;      // the opt-in is recorded per GPU
+    if (once.first(device)) {
         cuda_check(cudaFuncSetAttribute(qr_small_kernel<R, G, C, Square>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (32 / G) * kMaxWarps * slot_floats(R, steps) * (int)sizeof(float)),
                    "qr_small shared memory");
         cuda_check(cudaFuncSetAttribute(qr_small_kernel<R, G, C, Square>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared),
                    "qr_small shared memory carveout");
-        return true;
-    }();
-    (void)configured;
+        once.mark(device);
+    }
     qr_small_kernel<R, G, C, Square><<<blocks, 32 * warps_per_block, smem, stream>>>(p);
 }
 
@@ -208,9 +208,9 @@ void launch_qr_small(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p
 #define MLB_SMALL(RR, GG, CC)                                                    \
     if (R == RR && G == GG && C == CC) {                                         \
         if constexpr (RR == GG * CC) {                                           \
-            if (square) launch<RR, GG, CC, true>(stream, p, ctx.sm_count);       \
-            else launch<RR, GG, CC, false>(stream, p, ctx.sm_count);             \
-        } else launch<RR, GG, CC, false>(stream, p, ctx.sm_count);               \
+            if (square) launch<RR, GG, CC, true>(stream, p, ctx.sm_count, ctx.device);       \
+            else launch<RR, GG, CC, false>(stream, p, ctx.sm_count, ctx.device);             \
+        } else launch<RR, GG, CC, false>(stream, p, ctx.sm_count, ctx.device);               \
     }
 #define MLB_SMALL_ROWS(RR)                                                                        \
     MLB_SMALL(RR, 8, 1) MLB_SMALL(RR, 16, 1) MLB_SMALL(RR, 32, 1) /* one column a lane */        \

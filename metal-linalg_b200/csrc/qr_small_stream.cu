@@ -42,6 +42,7 @@ struct StreamParams {
     float*       q;      // null: R alone
     float*       r;
     uint32_t     batch;
+    unsigned*    status; // the context's status word: kStatusStreamWait is set by a warp that gives up
 };
 
 constexpr int      kWarps     = 4;            // warps a block; every warp works alone
@@ -138,7 +139,8 @@ __global__ void __launch_bounds__(kWarps * 32, Shape<R, G, C>::kBlocks) qr_small
         parity ^= 1;
         if (!__all_sync(0xffffffffu, arrived)) {
             // give up: NaN in every output this warp still owes, a last bounded wait for the copy
-            // in flight, the stores drained
+            // in flight, the stores drained; the context's status word tells the host
+            if (lane == 0) atomicOr(p.status, (unsigned)kStatusStreamWait);
             for (uint32_t v = u; v < units; v += GW)
                 for (uint32_t i = 0; i < (uint32_t)S::kMats; ++i) {
                     const uint32_t mat = v * S::kMats + i;
@@ -219,7 +221,9 @@ template <int R, int G, int C>
 void launch(const DeviceContext& ctx, cudaStream_t stream, const StreamParams& p) {
     using S = Shape<R, G, C>;
     constexpr size_t smem = (size_t)kWarps * S::kWarpFloats * sizeof(float);
-    static const int blocks_per_sm = [] {
+    static PerDeviceOnce once;                 // the opt-in is recorded per GPU
+    static std::atomic<int> blocks_per_sm{1};  // the same on every GPU of a machine
+    if (once.first(ctx.device)) {
         cuda_check(cudaFuncSetAttribute(qr_small_stream_kernel<R, G, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    "qr_small_stream shared memory");
         cuda_check(cudaFuncSetAttribute(qr_small_stream_kernel<R, G, C>, cudaFuncAttributePreferredSharedMemoryCarveout,
@@ -228,8 +232,9 @@ void launch(const DeviceContext& ctx, cudaStream_t stream, const StreamParams& p
         int n = 0;
         cuda_check(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qr_small_stream_kernel<R, G, C>, kWarps * 32, smem),
                    "qr_small_stream occupancy");
-        return n > 0 ? n : 1;
-    }();
+        blocks_per_sm = n > 0 ? n : 1;
+        once.mark(ctx.device);
+    }
     const uint32_t units  = (p.batch + S::kMats - 1) / S::kMats;
     const uint32_t wanted = (units + kWarps - 1) / kWarps;
     const uint32_t blocks = std::min<uint32_t>(wanted, (uint32_t)(blocks_per_sm * ctx.sm_count));
@@ -261,7 +266,7 @@ bool launch_qr_small_stream(DeviceContext& ctx, cudaStream_t stream, const QrPro
                            (pr.qc ? reinterpret_cast<uintptr_t>(pr.q) : 0);
     if (bits & 15) return false;
     if (pr.batch == 0) return true;
-    const StreamParams p{pr.a, pr.qc ? pr.q : nullptr, pr.r, pr.batch};
+    const StreamParams p{pr.a, pr.qc ? pr.q : nullptr, pr.r, pr.batch, ctx.status};
     if (n == 32) launch<32, 16, 2>(ctx, stream, p);
     else if (n == 16) launch<16, 8, 2>(ctx, stream, p);
     else launch<8, 8, 1>(ctx, stream, p);

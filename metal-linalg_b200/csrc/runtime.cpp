@@ -23,6 +23,12 @@ bool dependent_launches_enabled() {
     return v;
 }
 
+int current_device() {
+    int d = 0;
+    cuda_check(cudaGetDevice(&d), "cudaGetDevice");
+    return d;
+}
+
 int device_count() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess) {
@@ -70,6 +76,8 @@ DeviceContext& context(int device) {
         int least = 0, greatest = 0;   // the panel chain of the blocked QR goes ahead of the bulk updates
         cuda_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
         cuda_check(cudaStreamCreateWithPriority(&c->aux, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        cuda_check(cudaMalloc(&c->status, 256), "cudaMalloc");
+        cuda_check(cudaMemset(c->status, 0, 256), "cudaMemset");
         for (int i = 0; i < 2; ++i) {
             cuda_check(cudaEventCreateWithFlags(&c->ev_panel[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_update[i], cudaEventDisableTiming), "cudaEventCreate");
@@ -118,6 +126,64 @@ void* grown(Workspace& w, int device, size_t bytes) {
 void* DeviceContext::workspace(cudaStream_t stream, size_t bytes) { return grown(workspaces[stream], device, bytes); }
 void* DeviceContext::outer_workspace(cudaStream_t stream, size_t bytes) {
     return grown(outer_workspaces[stream], device, bytes);
+}
+
+size_t DeviceContext::release_workspaces() {
+    DeviceGuard guard(device);
+    cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    size_t freed = 0;
+    for (auto* table : {&workspaces, &outer_workspaces}) {
+        for (auto& entry : *table) {
+            if (entry.second.data) cuda_check(cudaFree(entry.second.data), "cudaFree");
+            freed += entry.second.bytes;
+        }
+        table->clear();
+    }
+    return freed;
+}
+
+unsigned DeviceContext::take_status() {
+    DeviceGuard guard(device);
+    unsigned word = 0;
+    cuda_check(cudaMemcpy(&word, status, sizeof(word), cudaMemcpyDeviceToHost), "cudaMemcpy");
+    if (word) cuda_check(cudaMemset(status, 0, sizeof(word)), "cudaMemset");
+    return word;
+}
+
+void throw_if_a_kernel_gave_up() {
+    DeviceContext* all[64];
+    const int n = created_contexts(all, 64);
+    for (int i = 0; i < n; ++i) {
+        const unsigned word = all[i]->take_status();
+        if (!word) continue;
+        std::string what = "a kernel on GPU " + std::to_string(all[i]->device) + " gave up on a bounded wait (";
+        if (word & kStatusTensorWait) what += "a tensor-core product of the blocked QR";
+        if ((word & kStatusTensorWait) && (word & kStatusStreamWait)) what += ", ";
+        if (word & kStatusStreamWait) what += "a bulk copy of the streaming small-matrix kernel";
+        what += "); the outputs of the matrices concerned are NaN; last QR enqueued there: batch " +
+                std::to_string(all[i]->last_shape[0]) + " of " + std::to_string(all[i]->last_shape[1]) + " x " +
+                std::to_string(all[i]->last_shape[2]);
+        throw std::runtime_error(what);
+    }
+}
+
+int created_contexts(DeviceContext** out, int capacity) {
+    std::lock_guard<std::mutex> lock(g_contexts_mutex);
+    int n = 0;
+    for (auto& c : g_contexts)
+        if (c && n < capacity) out[n++] = c.get();
+    return n;
+}
+
+namespace {
+std::atomic<int> g_injected_wait_failures{0};
+}
+void inject_wait_failures(int count) { g_injected_wait_failures = count > 0 ? count : 0; }
+bool take_injected_wait_failure() {
+    int left = g_injected_wait_failures.load();
+    while (left > 0)
+        if (g_injected_wait_failures.compare_exchange_weak(left, left - 1)) return true;
+    return false;
 }
 
 cudaStream_t thread_stream() { return t_stream; }

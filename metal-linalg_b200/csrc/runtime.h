@@ -5,6 +5,7 @@
 // src/metal_runtime.{h,mm} (buffers, command queues) and src/device.mm.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <map>
@@ -22,14 +23,22 @@ struct Workspace {
     size_t bytes = 0;
 };
 
-// Status words the kernels write: one per stream workspace, in device memory,
-// read back by synchronize(). Non-zero means a bounded wait ran out.
+// What a kernel records when it gives up on a bounded wait: bits of the context's status word
+// (DeviceContext::status, one word of device memory per GPU). The matrices concerned get NaN
+// outputs; take_status() turns the word into an error for the caller.
+enum : unsigned {
+    kStatusTensorWait = 2u,   // an mbarrier wait of a tensor-core product (tc_gemm.cu, tc_gemm2.cu)
+    kStatusStreamWait = 4u,   // an mbarrier wait of the streaming small-matrix kernel (qr_small_stream.cu)
+};
+
 struct DeviceContext {
     int            device      = 0;
     int            sm_count    = 0;
     size_t         smem_optin  = 0;     // bytes of shared memory a block may opt into
     std::string    name;
     std::mutex     mutex;               // held while a call enqueues on this GPU
+    unsigned*      status      = nullptr;   // device word: kStatus* bits set by kernels that gave up on a wait
+    uint32_t       last_shape[3] = {0, 0, 0};   // batch, rows, cols of the last QR enqueued here (for that error's message)
     std::map<cudaStream_t, Workspace> workspaces;
     std::map<cudaStream_t, Workspace> outer_workspaces;   // of a caller of the QR (the SVD), beside the QR's own
     cudaStream_t   copy_in = nullptr, copy_out = nullptr, compute = nullptr;   // host-pointer staging
@@ -54,6 +63,32 @@ struct DeviceContext {
     void* workspace(cudaStream_t stream, size_t bytes);
     // The same for a routine that calls the QR on `stream` and needs scratch that outlives that call.
     void* outer_workspace(cudaStream_t stream, size_t bytes);
+    // Frees every stream's workspace after waiting for the GPU; they are allocated again on demand.
+    // Returns the bytes given back.
+    size_t release_workspaces();
+    // Reads and clears the status word (the caller has synchronised the work it asks about).
+    unsigned take_status();
+};
+
+// Throws std::runtime_error naming the wait and the last shape enqueued if any created context's
+// status word is set (and clears it). The caller has synchronised the work it asks about.
+void throw_if_a_kernel_gave_up();
+
+// The contexts created so far (a context is created by the first call that uses its GPU).
+int created_contexts(DeviceContext** out, int capacity);
+
+// The GPU that is current for the calling thread (every launcher runs under a DeviceGuard).
+int current_device();
+
+// True the first time it is asked about `device` (and again if two threads ask at once, which is
+// harmless for idempotent set-up): for per-GPU set-up of a kernel, such as the opt-in to more than
+// 48 KB of shared memory, which cudaFuncSetAttribute records for the current device only.
+class PerDeviceOnce {
+public:
+    bool first(int device) const { return !((done_.load(std::memory_order_acquire) >> (device & 63)) & 1u); }
+    void mark(int device) { done_.fetch_or((uint64_t)1 << (device & 63), std::memory_order_release); }
+private:
+    std::atomic<uint64_t> done_{0};
 };
 
 int            device_count();
@@ -77,6 +112,12 @@ void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t s
     cfg.numAttrs = dependent_launches_enabled() ? 1 : 0;
     cuda_check(cudaLaunchKernelEx(&cfg, kernel, Params(args)...), "cudaLaunchKernelEx");
 }
+
+// Testing aid: the next `count` matrices that go through the blocked QR behave as if a tensor-core
+// product's bounded wait had run out at once (their products return without touching memory, their
+// outputs are NaN, the context's status word is set). Nothing on the GPU is made to wait or fail.
+void inject_wait_failures(int count);
+bool take_injected_wait_failure();
 
 // The calling thread's stream (device-pointer calls) and device (host-pointer calls).
 cudaStream_t thread_stream();

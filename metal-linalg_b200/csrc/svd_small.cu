@@ -554,14 +554,14 @@ __global__ void __launch_bounds__(32 * kBlockWarps) svd_block_kernel(const SvdSm
 size_t block_smem(uint32_t k, bool vectors) { return (size_t)k * (k | 1u) * sizeof(float) * (vectors ? 2 : 1); }
 
 void launch_block_jacobi(cudaStream_t stream, const SvdSmallParams& p, bool vectors) {
-    static const bool configured = [] {
+    static PerDeviceOnce once;      // the opt-in is recorded per GPU
+    if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(svd_block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)block_smem(128, true)), "svd_block shared memory");
         cuda_check(cudaFuncSetAttribute(svd_block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)block_smem(128, false)), "svd_block shared memory");
-        return true;
-    }();
-    (void)configured;
+        once.mark(device);
+    }
     const uint32_t pairs = (p.k + 1) / 2;
     // with vectors a block fills a multiprocessor's shared memory and takes every warp it may have; the values
     // alone leave room for three blocks, which 16 warps each use better (1024 x 128 x 128: 22 against 25 ms)
@@ -640,12 +640,12 @@ void launch_svd_small(cudaStream_t stream, const float* r, uint32_t batch, uint3
 void launch_svd_left_vectors(cudaStream_t stream, const float* q, const float* ur, float* out, uint32_t batch, uint32_t l,
                              uint32_t k, bool transposed) {
     if (k > 32) {
-        static const bool configured = [] {
+        static PerDeviceOnce once;
+        if (const int device = current_device(); once.first(device)) {
             cuda_check(cudaFuncSetAttribute(svd_left_vectors_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)((128 * 128 + 64 * 129) * sizeof(float))), "svd_left_vectors shared memory");
-            return true;
-        }();
-        (void)configured;
+            once.mark(device);
+        }
         const size_t smem = ((size_t)k * k + 64 * (k + 1)) * sizeof(float);
         for (uint32_t b0 = 0; b0 < batch; b0 += 65535) {      // the batch along y in slices
             const uint32_t nb = batch - b0 < 65535 ? batch - b0 : 65535;

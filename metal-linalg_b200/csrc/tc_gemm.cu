@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool ok = !failed;
-    if (!ok && threadIdx.x == 0) atomicExch(p.error, 1u);
+    if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
     if (ok && tiles > 0 && p.mode == 1) {   // C's tile, a warp a row
         for (uint32_t r = warp; r < out_rows; r += TCT / 32) {
             const float* src = out_tile + (size_t)r * p.ldo + 4 * lane;
@@ -318,11 +318,11 @@ __global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
 constexpr size_t kTcSmem = (2 * STAGE > 128 * CLD * (int)sizeof(float) ? 2 * STAGE : 128 * CLD * (int)sizeof(float)) + 1024;
 
 void configure() {
-    static bool done = false;
-    if (!done) {
+    static PerDeviceOnce once;      // the opt-in is recorded per GPU
+    if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem),
                    "tc_gemm shared memory");
-        done = true;
+        once.mark(device);
     }
 }
 

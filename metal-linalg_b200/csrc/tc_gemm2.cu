@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool ok = !failed;
-    if (!ok && threadIdx.x == 0) atomicExch(p.error, 1u);
+    if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
     if (ok) {   // C's tile, a warp a row
         for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
             const float* src = out_tile + (size_t)r * p.ldc + 4 * lane;
@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool ok = !failed;
-    if (!ok && threadIdx.x == 0) atomicExch(p.error, 1u);
+    if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
     if (ok && tiles > 0) {
         const uint32_t row = 32 * (warp & 3) + lane;
         const uint32_t c_base = 64 * (warp >> 2);
@@ -495,12 +495,12 @@ size_t tc_split_floats(uint32_t extent) { return (size_t)((extent + 127) / 128) 
 // of tc_split_floats(mp) and tc_split_floats(nc) floats).
 void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
                         uint32_t mp, uint32_t kw, uint32_t nc, float* ysp, float* zsp, unsigned* error) {
-    static const bool configured = [] {
+    static PerDeviceOnce once;      // the opt-in is recorded per GPU
+    if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_yz2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYz2Smem),
                    "tc_yz2 shared memory");
-        return true;
-    }();
-    (void)configured;
+        once.mark(device);
+    }
     const uint32_t stages = (kw + KS2 - 1) / KS2, rtiles = (mp + 127) / 128, ctiles = (nc + 127) / 128;
     launch_dependent(split_y_kernel, (rtiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, stages, ysp);
     launch_dependent(split_z_kernel, (ctiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Z, (size_t)ncp, kw, nc, stages, zsp);
@@ -515,12 +515,12 @@ size_t tc_split_t_floats(uint32_t rows) { return (size_t)((rows + 15) / 16) * kP
 // (tc_split_t_floats(mp) floats); chunk_rows a multiple of 16.
 void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp,
                          uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, float* ytsp, unsigned* error) {
-    static const bool configured = [] {
+    static PerDeviceOnce once;
+    if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_ytc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYtc2Smem),
                    "tc_ytc2 shared memory");
-        return true;
-    }();
-    (void)configured;
+        once.mark(device);
+    }
     const uint32_t words = 128 * 4 * ((mp + 15) / 16);
     launch_dependent(split_yt_kernel, (words + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, ytsp);
     Ytc2Params p{ytsp, C, zp, ldc, mp, nc, ncp, chunk_rows, error};

@@ -49,6 +49,8 @@ def _load():
         "metal_linalg_device": (ctypes.c_int, []),
         "metal_linalg_device_count": (ctypes.c_int, []),
         "metal_linalg_synchronize": (ctypes.c_int, []),
+        "metal_linalg_release_workspaces": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint64)]),
+        "metal_linalg_inject_wait_failures": (None, [ctypes.c_int]),
         "metal_linalg_device_name": (ctypes.c_char_p, []),
         "metal_linalg_gpu_core_count": (_u32, []),
         "metal_linalg_set_calibration_notices": (None, [ctypes.c_int]),
@@ -96,6 +98,18 @@ def qr(a, batch, rows, cols, q, r, mode="reduced", stream=None):
     if stream is not None:
         lib.metal_linalg_set_stream(stream)
     check(lib.metal_linalg_qr_with_mode(a, batch, rows, cols, MODES[mode], q, r))
+
+
+def synchronize():
+    """Waits for this thread's stream; raises RuntimeError if a kernel gave up on a bounded wait."""
+    check(lib.metal_linalg_synchronize())
+
+
+def release_workspaces():
+    """Frees the scratch memory the library keeps per (GPU, stream); returns the bytes freed."""
+    freed = ctypes.c_uint64(0)
+    check(lib.metal_linalg_release_workspaces(ctypes.byref(freed)))
+    return freed.value
 
 
 def svd(a, batch, rows, cols, u, s, vt, info=None, stream=None):

@@ -41,9 +41,12 @@ def qr_bytes(m, n, mode="reduced"):
     return 4 * (m * n + m * qc + rr * n)
 
 
-def generate(name, batch=None, rows=None):
-    """The input of configuration `name` as a float32 CPU tensor [batch, M, N].
-    `rows` shortens the tall configuration for tests."""
+def generate(name, batch=None, rows=None, device=None):
+    """The input of configuration `name` as a float32 tensor [batch, M, N] (on the CPU unless
+    `device` is given). `rows` shortens the tall configuration for tests. The random draws always
+    come from the seeded CPU generator; `device` only says where the third configuration's float64
+    orthogonal factors are formed (4096 pairs of 256 x 256 QRs take the host cores half a minute),
+    so its matrices differ from the CPU-built ones in the last bits, not in distribution."""
     default_batch, m, n, _, seed = CONFIGS[name]
     b = default_batch if batch is None else batch
     if rows is not None:
@@ -58,10 +61,11 @@ def generate(name, batch=None, rows=None):
     if name == "c3_256x256_rank224":
         # U diag(s) V^T, U and V the Q factors of N(0,1) matrices (float64), s log-spaced
         # from 1 to 1e-7 with the last 32 exactly zero
-        u = torch.linalg.qr(torch.randn(b, m, m, generator=g, dtype=torch.float64))[0]
-        v = torch.linalg.qr(torch.randn(b, n, n, generator=g, dtype=torch.float64))[0]
+        where = torch.device(device) if device is not None else torch.device("cpu")
+        u = torch.linalg.qr(torch.randn(b, m, m, generator=g, dtype=torch.float64).to(where))[0]
+        v = torch.linalg.qr(torch.randn(b, n, n, generator=g, dtype=torch.float64).to(where))[0]
         k = min(m, n)
-        s = torch.logspace(0.0, -7.0, k, dtype=torch.float64)
+        s = torch.logspace(0.0, -7.0, k, dtype=torch.float64, device=where)
         s[k - max(1, k // 8):] = 0.0
         return ((u[:, :, :k] * s) @ v[:, :, :k].mT).float()
     if name in ("c5a_4096x4096", "c5b_8192x8192"):

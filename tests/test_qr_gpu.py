@@ -268,23 +268,39 @@ def test_blocked_special_matrices():
     assert np.abs(r[1]).max() == 0.0
 
 
-def _gpu_float64_check(a, q, r, mode):
-    """Reconstruction and orthogonality in float64 on the GPU, and R against torch's float64 QR
-    after sign normalisation: for matrices too large for the CPU oracle."""
-    n = a.shape[-1]
-    tol = workloads.tolerance(n)
-    a64, q64, r64 = a.double(), q.double(), r.double()
-    recon = (torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)).max().item()
-    eye = torch.eye(q.shape[-1], device=a.device, dtype=torch.float64)
-    orth = torch.linalg.matrix_norm(q64.mT @ q64 - eye).max().item()
-    assert recon <= tol, f"reconstruction {recon:.3e} > {tol:.3e}"
-    assert orth <= tol, f"orthogonality {orth:.3e} > {tol:.3e}"
+def _gpu_float64_properties(a, q, r, unit=None):
+    """Per-matrix reconstruction and orthogonality in float64 on the GPU, on the unit-scale problem
+    (`unit`: per-matrix scale [batch, 1, 1], or None), for batches and matrices too large for the
+    CPU oracle; R's strict lower triangle exactly zero. Returns (recon_max, orth_max)."""
+    tol = workloads.tolerance(a.shape[-1])
+    recon_max = orth_max = 0.0
+    step = max(1, (1 << 27) // (a.shape[-2] * max(a.shape[-1], q.shape[-1])))      # about 1 GiB of float64 a slice
+    for b0 in range(0, a.shape[0], step):
+        sl = slice(b0, b0 + step)
+        a64, q64, r64 = a[sl].double(), q[sl].double(), r[sl].double()
+        if unit is not None:
+            a64, r64 = a64 / unit[sl], r64 / unit[sl]
+        recon = torch.linalg.matrix_norm(a64 - q64 @ r64) / torch.linalg.matrix_norm(a64)
+        del a64, r64
+        eye = torch.eye(q.shape[-1], device=a.device, dtype=torch.float64)
+        orth = torch.linalg.matrix_norm(q64.mT @ q64 - eye)
+        recon_max, orth_max = max(recon_max, recon.max().item()), max(orth_max, orth.max().item())
+        del q64
+    assert recon_max <= tol, f"reconstruction {recon_max:.3e} > {tol:.3e}"
+    assert orth_max <= tol, f"orthogonality {orth_max:.3e} > {tol:.3e}"
     assert torch.count_nonzero(torch.tril(r, -1)).item() == 0
-    r_ref = torch.linalg.qr(a64, mode="r")[1]
-    k = min(a.shape[-2:])
-    s = torch.sign(torch.diagonal(r64, dim1=-2, dim2=-1)) * torch.sign(torch.diagonal(r_ref, dim1=-2, dim2=-1))
-    diff = (r64[..., :k, :] * s[..., :, None] - r_ref).abs().max().item() / r_ref.abs().max().item()
-    assert diff <= 1e-4, f"R differs from the float64 QR by {diff:.3e}"
+    return recon_max, orth_max
+
+
+def _r_against_reference(a, r):
+    """R against the reference's own CPU QR (src/qr_cpu.mm: LAPACK sgeqrf on all host cores) after sign
+    normalisation; the plain-C restatement where that library was not built."""
+    host = a.cpu().numpy()
+    ref = harness.ref_qr(host, "r")
+    r_ref = ref[1] if ref is not None else harness.oracle_qr(host, "r")[1]
+    par = harness.r_parity(r.cpu().numpy(), r_ref)
+    assert par <= 1e-4, f"R differs from the reference's by {par:.3e}"
+    return par
 
 
 def test_config5a_4096_square():
@@ -292,7 +308,55 @@ def test_config5a_4096_square():
     assert mlt.qr_kernel(4096, 4096, 1) == "blocked"
     q, r = mlt.qr(a)
     torch.cuda.synchronize()
-    _gpu_float64_check(a, q, r, "reduced")
+    _gpu_float64_properties(a, q, r)
+    _r_against_reference(a, r)
+
+
+@pytest.mark.parametrize("tensor", ["1", "0"])
+def test_config5b_8192_square(tensor):
+    """One of configuration 5b's eight 8192 x 8192 matrices (the first of the seeded stream), on the
+    default path (3xTF32 tensor-core products) and on the FP32 FMA fallback (QR_TENSOR=0): reconstruction
+    and orthogonality of the whole 8192 x 8192 Q in float64 against 10 n eps, R against the reference's."""
+    a = workloads.generate("c5b_8192x8192", batch=1).cuda()
+    assert mlt.qr_kernel(8192, 8192, 1) == "blocked"
+    os.environ["QR_TENSOR"] = tensor
+    try:
+        q, r = mlt.qr(a)
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("QR_TENSOR", None)
+    recon, orth = _gpu_float64_properties(a, q, r)
+    par = _r_against_reference(a, r)
+    print(f"8192 x 8192, QR_TENSOR={tensor}: reconstruction {recon:.3e}, orthogonality {orth:.3e} "
+          f"(bound {workloads.tolerance(8192):.3e}), R parity {par:.3e}")
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete"])
+def test_config3_full_batch_properties(mode):
+    """All 4096 rank-224 matrices of configuration 3 (the seeded N(0,1) draws on the CPU, the float64
+    orthogonal factors formed on the GPU): float64 properties of every matrix, R against the oracle on
+    a sample across the batch."""
+    a = workloads.generate("c3_256x256_rank224", device="cuda").cuda()
+    assert a.shape == (4096, 256, 256) and mlt.qr_kernel(256, 256, 4096, mode) == "mid"
+    q, r = mlt.qr(a, mode)
+    torch.cuda.synchronize()
+    _gpu_float64_properties(a, q, r)
+    idx = np.arange(0, a.shape[0], 128)
+    sample = a[idx].cpu().numpy()
+    _, r_ref = harness.oracle_qr(sample, mode)
+    assert harness.r_parity(r[idx].cpu().numpy(), r_ref) <= 1e-4
+
+
+def test_config4_full_batch_properties():
+    """All 64 matrices of 65536 x 64 of configuration 4."""
+    a = workloads.generate("c4_65536x64_tall").cuda()
+    assert mlt.qr_kernel(65536, 64, 64) == "tsqr"
+    q, r = mlt.qr(a)
+    torch.cuda.synchronize()
+    _gpu_float64_properties(a, q, r)
+    idx = [0, 63]
+    _, r_ref = harness.oracle_qr(a[idx].cpu().numpy())
+    assert harness.r_parity(r[idx].cpu().numpy(), r_ref) <= 1e-4
 
 
 def test_mid_kernel_on_small_shapes_agrees_with_small_kernel():
@@ -686,3 +750,81 @@ def test_interop_cuda_array_interface_and_dlpack():
     Q, R = mlt.qr_dlpack(t)
     torch.cuda.synchronize()
     check(a, Q.cpu().numpy(), R.cpu().numpy(), "reduced")
+
+
+# ---------------------------------------------------------------------------
+# Failures that surface, memory that can be given back, a second GPU in one process
+# ---------------------------------------------------------------------------
+
+def test_kernel_that_gives_up_surfaces_as_runtime_error():
+    """A kernel that gives up on a bounded wait writes NaN, which alone cannot be told from a NaN in the
+    input; metal_linalg_synchronize (device pointers) and the call's own status (host pointers) report
+    it as RUNTIME_ERROR with the shape (reference: src/qr_householder.mm:372-377, src/c_api.cpp:17-35).
+    The failure is injected on the host: the blocked QR starts with its give-up word already set, so
+    its tensor-core products return at once. No GPU waits or faults."""
+    lib = _lib.lib
+    a = torch.randn(1, 600, 600, device="cuda")
+    q0, r0 = gpu_qr(a.cpu().numpy(), kernel="blocked")
+    assert lib.metal_linalg_synchronize() == _lib.OK
+    lib.metal_linalg_inject_wait_failures(1)
+    q, r = gpu_qr(a.cpu().numpy(), kernel="blocked")               # device pointers: the call itself cannot know yet
+    assert np.isnan(q).all() and np.isnan(r).all()
+    assert lib.metal_linalg_synchronize() == _lib.RUNTIME_ERROR
+    message = _lib.last_error()
+    assert "gave up" in message and "600 x 600" in message and "tensor-core" in message
+    assert lib.metal_linalg_synchronize() == _lib.OK               # reported once
+    q1, r1 = gpu_qr(a.cpu().numpy(), kernel="blocked")             # and the next call is sound
+    assert np.array_equal(q1, q0) and np.array_equal(r1, r0)
+    # host pointers: the call waits for its results, so its own status carries the failure
+    host = a.cpu().numpy()
+    hq, hr = np.zeros_like(host), np.zeros_like(host)
+    os.environ["QR_KERNEL"] = "blocked"
+    try:
+        lib.metal_linalg_inject_wait_failures(1)
+        status = lib.metal_linalg_qr(host.ctypes.data, 1, 600, 600, hq.ctypes.data, hr.ctypes.data)
+        assert status == _lib.RUNTIME_ERROR and "gave up" in _lib.last_error()
+        assert np.isnan(hq).all() and np.isnan(hr).all()
+        assert lib.metal_linalg_qr(host.ctypes.data, 1, 600, 600, hq.ctypes.data, hr.ctypes.data) == _lib.OK
+    finally:
+        os.environ.pop("QR_KERNEL", None)
+        lib.metal_linalg_inject_wait_failures(0)
+    assert np.array_equal(hr, r0[0:1]) or harness.r_parity(hr, r0) <= 1e-6
+
+
+def test_release_workspaces_gives_memory_back():
+    a = torch.randn(1, 3000, 3000, device="cuda")
+    q, r = mlt.qr(a)                                   # the blocked QR: a workspace of a few hundred MB
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    freed = _lib.release_workspaces()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert freed >= 3000 * 3000 * 4 * 2
+    assert free_after - free_before >= freed // 2      # the driver hands back whole blocks
+    assert _lib.release_workspaces() == 0
+    q2, r2 = mlt.qr(a)                                 # allocates again
+    torch.cuda.synchronize()
+    assert torch.equal(q2, q) and torch.equal(r2, r)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_second_gpu_in_one_process():
+    """Every kernel family on cuda:1 after cuda:0 in ONE process (kernels that opt into more than 48 KB
+    of shared memory do so per GPU): same bits as on cuda:0. `qr_sharded` is that path."""
+    torch.manual_seed(31)
+    cases = [(torch.randn(300, 32, 32), "reduced"), (torch.randn(100, 16, 16), "reduced"),
+             (torch.randn(6, 256, 200), "complete"), (torch.randn(2, 5000, 64), "reduced"),
+             (torch.randn(1, 1500, 1200), "reduced"), (torch.randn(1, 2100, 300), "r")]
+    for a, mode in cases:
+        (q0, r0), (q1, r1) = mlt.qr_sharded([a.to("cuda:0"), a.to("cuda:1")], mode)
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        assert r1.device.index == 1
+        assert torch.equal(r0.cpu(), r1.cpu()), (tuple(a.shape), mode)
+        assert torch.equal(q0.cpu(), q1.cpu()), (tuple(a.shape), mode)
+    a = torch.randn(8, 300, 12)
+    u0, s0, v0 = mlt.svd(a.to("cuda:0"))
+    u1, s1, v1 = mlt.svd(a.to("cuda:1"))
+    assert torch.equal(s0.cpu(), s1.cpu()) and torch.equal(u0.cpu(), u1.cpu())
+    big = torch.randn(4, 400, 128)                     # the block Jacobi and the wide left-vector kernel
+    s0, s1 = mlt.svd(big.to("cuda:0")).S, mlt.svd(big.to("cuda:1")).S
+    assert torch.equal(s0.cpu(), s1.cpu())

@@ -72,3 +72,26 @@ def test_no_alloc_limits_are_refused_with_a_message():
     host = np.zeros((1, 8, 8), np.float32)                        # host memory would need staging buffers
     assert lib.metal_linalg_qr_no_alloc(host.ctypes.data, 1, 8, 8, 0, host.ctypes.data, host.ctypes.data) == _lib.INVALID_ARGUMENT
     assert lib.metal_linalg_qr_no_alloc(None, 0, 8, 8, 0, None, None) == _lib.OK
+
+
+def test_no_alloc_leaves_device_memory_alone():
+    """What the entry point is for: a call changes the GPU's free memory by nothing, where the ordinary
+    entry point, with no workspace left from earlier calls, has to allocate one."""
+    lib = _lib.lib
+    torch.manual_seed(22)
+    a = torch.randn(64, 640, 384, device="cuda")
+    q, r = torch.empty(64, 640, 384, device="cuda"), torch.empty(64, 384, 384, device="cuda")
+    lib.metal_linalg_set_stream(torch.cuda.current_stream().cuda_stream)
+    args = (a.data_ptr(), 64, 640, 384, _lib.MODES["reduced"], q.data_ptr(), r.data_ptr())
+    assert lib.metal_linalg_qr_no_alloc(*args) == _lib.OK, _lib.last_error()      # the first call looks the array up
+    torch.cuda.synchronize()
+    _lib.release_workspaces()                                                      # nothing is kept from earlier tests
+    free0, _ = torch.cuda.mem_get_info()
+    assert lib.metal_linalg_qr_no_alloc(*args) == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"the call changed free device memory by {free0 - free1} bytes"
+    assert lib.metal_linalg_qr_with_mode(*args) == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    free2, _ = torch.cuda.mem_get_info()
+    assert free2 < free1, "the ordinary entry point was expected to allocate its workspace"
