@@ -115,17 +115,36 @@ __device__ __forceinline__ void load_tile(float* dst, int lds, const float* src,
                                           int col0, int ncols, const F& f) {
     const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
     const int nq = (nrows + 3) >> 2;
-    for (int rq = warp; rq < nq; rq += NT / 32) {
-        const int r = rq * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < ncols) {
-            const float* s = src + (size_t)(row0 + r) * ld + col0 + c;
-            if (r + 0 < nrows) v.x = f(s[0], r + 0, c);
-            if (r + 1 < nrows) v.y = f(s[ld], r + 1, c);
-            if (r + 2 < nrows) v.z = f(s[2 * ld], r + 2, c);
-            if (r + 3 < nrows) v.w = f(s[3 * ld], r + 3, c);
+    // A warp's row quads are 8 apart; up to eight of them (a tile of 256 rows) are fetched before the first is
+    // stored, so that the loads of a whole tile are in flight together and the tile costs one trip to L2, not eight.
+    for (int base = warp; base < nq; base += 8 * (NT / 32)) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int r = (base + u * (NT / 32)) * 4;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < ncols && r < nrows) {
+                const float* s = src + (size_t)(row0 + r) * ld + col0 + c;
+                v[u].x = s[0];
+                if (r + 1 < nrows) v[u].y = s[ld];
+                if (r + 2 < nrows) v[u].z = s[2 * ld];
+                if (r + 3 < nrows) v[u].w = s[3 * ld];
+            }
         }
-        *reinterpret_cast<float4*>(dst + c * lds + r) = v;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int rq = base + u * (NT / 32), r = rq * 4;
+            if (rq < nq) {
+                float4 w = v[u];
+                if (c < ncols) {
+                    w.x = f(w.x, r, c);
+                    if (r + 1 < nrows) w.y = f(w.y, r + 1, c);
+                    if (r + 2 < nrows) w.z = f(w.z, r + 2, c);
+                    if (r + 3 < nrows) w.w = f(w.w, r + 3, c);
+                }
+                *reinterpret_cast<float4*>(dst + c * lds + r) = w;
+            }
+        }
     }
 }
 

@@ -708,9 +708,20 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     // up to 4096 rows the whole panel in one cluster launch (QR_PANEL_CLUSTER=0: the tree of row blocks)
     const char* envc = std::getenv("QR_PANEL_CLUSTER");
     if (by_columns && mp <= 4096 && !(envc && envc[0] == '0')) {
-        const uint32_t rw = mp <= 2048 ? 32 : 64;
+        // beyond 2048 rows: 8 blocks of 512 rows (64 rows a lane), or with QR_PANEL_CLUSTER=16 sixteen blocks of
+        // 256 rows (32 rows a lane: half the arithmetic a step, a cluster of the non-portable size)
+        const bool sixteen = mp > 2048 && envc && envc[0] == '1' && envc[1] == '6';
+        const uint32_t rw = (mp <= 2048 || sixteen) ? 32 : 64;
         uint32_t ncta = 1;
-        while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4 or 8 blocks; blocks beyond the rows hold zeros
+        while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4, 8 (or 16) blocks; blocks beyond the rows hold zeros
+        if (ncta > 8) {
+            static PerDeviceOnce once;
+            if (const int device = current_device(); once.first(device)) {
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                           "panel_cluster non-portable cluster size");
+                once.mark(device);
+            }
+        }
         ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb};
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(ncta);
