@@ -105,46 +105,65 @@ struct LoadScaled {
     Pow2 down;
     __device__ __forceinline__ float operator()(float v, int, int) const { return down(v); }
 };
+// a factored panel read as its reflectors: the entries below the diagonal, a unit diagonal, zeros above
+struct LoadReflector {
+    __device__ __forceinline__ float operator()(float v, int r, int c) const { return r > c ? v : (r == c ? 1.0f : 0.0f); }
+};
 
 // Rows [row0, row0 + nrows) x columns [col0, col0 + ncols) of a row-major matrix
 // into dst[c * lds + r], all 32 columns and rows up to the next multiple of four
 // written (zeros outside). A warp reads 32 consecutive floats of four rows and
 // writes one 16-byte word a lane.
+//
+// In two halves, so that a caller can have the next tile's loads in flight while it computes on the current one:
+// tile_fetch issues the loads of up to 256 rows into registers (a warp's row quads are 8 apart: eight of them, all in
+// flight together, so that a tile costs one trip to L2 and not eight), tile_commit writes them to shared memory.
+struct TileRegs {
+    float4 v[8];
+};
+__device__ __forceinline__ void tile_fetch(TileRegs& t, const float* src, size_t ld, int row0, int nrows, int col0,
+                                           int ncols, int quad0) {
+    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int r = (quad0 + warp + u * (NT / 32)) * 4;
+        t.v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < ncols && r < nrows) {
+            const float* s = src + (size_t)(row0 + r) * ld + col0 + c;
+            t.v[u].x = s[0];
+            if (r + 1 < nrows) t.v[u].y = s[ld];
+            if (r + 2 < nrows) t.v[u].z = s[2 * ld];
+            if (r + 3 < nrows) t.v[u].w = s[3 * ld];
+        }
+    }
+}
+template <class F>
+__device__ __forceinline__ void tile_commit(const TileRegs& t, float* dst, int lds, int nrows, int ncols, int quad0, const F& f) {
+    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
+    const int nq = (nrows + 3) >> 2;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int rq = quad0 + warp + u * (NT / 32), r = rq * 4;
+        if (rq < nq) {
+            float4 w = t.v[u];
+            if (c < ncols) {
+                w.x = f(w.x, r, c);
+                if (r + 1 < nrows) w.y = f(w.y, r + 1, c);
+                if (r + 2 < nrows) w.z = f(w.z, r + 2, c);
+                if (r + 3 < nrows) w.w = f(w.w, r + 3, c);
+            }
+            *reinterpret_cast<float4*>(dst + c * lds + r) = w;
+        }
+    }
+}
 template <class F>
 __device__ __forceinline__ void load_tile(float* dst, int lds, const float* src, size_t ld, int row0, int nrows,
                                           int col0, int ncols, const F& f) {
-    const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
     const int nq = (nrows + 3) >> 2;
-    // A warp's row quads are 8 apart; up to eight of them (a tile of 256 rows) are fetched before the first is
-    // stored, so that the loads of a whole tile are in flight together and the tile costs one trip to L2, not eight.
-    for (int base = warp; base < nq; base += 8 * (NT / 32)) {
-        float4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int r = (base + u * (NT / 32)) * 4;
-            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < ncols && r < nrows) {
-                const float* s = src + (size_t)(row0 + r) * ld + col0 + c;
-                v[u].x = s[0];
-                if (r + 1 < nrows) v[u].y = s[ld];
-                if (r + 2 < nrows) v[u].z = s[2 * ld];
-                if (r + 3 < nrows) v[u].w = s[3 * ld];
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int rq = base + u * (NT / 32), r = rq * 4;
-            if (rq < nq) {
-                float4 w = v[u];
-                if (c < ncols) {
-                    w.x = f(w.x, r, c);
-                    if (r + 1 < nrows) w.y = f(w.y, r + 1, c);
-                    if (r + 2 < nrows) w.z = f(w.z, r + 2, c);
-                    if (r + 3 < nrows) w.w = f(w.w, r + 3, c);
-                }
-                *reinterpret_cast<float4*>(dst + c * lds + r) = w;
-            }
-        }
+    for (int quad0 = 0; quad0 < nq; quad0 += 8 * (NT / 32)) {
+        TileRegs t;
+        tile_fetch(t, src, ld, row0, nrows, col0, ncols, quad0);
+        tile_commit(t, dst, lds, nrows, ncols, quad0, f);
     }
 }
 
@@ -255,6 +274,9 @@ __device__ __forceinline__ void gemm_vw(const float* vbase, int ldv, const float
 template <class F>
 __device__ void update_columns(const Smem& s, int ldv, const float* src, size_t lds, const F& f, float* dst,
                                size_t ldd, int row0, int mp, int col_begin, int col_end, bool transposed) {
+    // A matrix of at most 256 rows has one tile a strip: the next strip's tile is then asked into L1 (a row of a tile
+    // is one 128-byte line, a line a thread) while this strip's second product runs.
+    const bool single = mp <= RC;
     for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         const int tw = min(32, col_end - c0);
         float acc[4][4];
@@ -262,7 +284,6 @@ __device__ void update_columns(const Smem& s, int ldv, const float* src, size_t 
         for (int a = 0; a < 4; ++a)
 #pragma unroll
             for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
-        const bool single = mp <= RC;
         for (int r0 = 0; r0 < mp; r0 += RC) {
             const int nr = min(RC, mp - r0);
             __syncthreads();   // the tile buffer is free
@@ -276,6 +297,8 @@ __device__ void update_columns(const Smem& s, int ldv, const float* src, size_t 
         __syncthreads();
         apply_t(s.Ts, s.Zs, s.Ws, transposed);
         __syncthreads();
+        if (single && c0 + 32 < col_end && (int)threadIdx.x < mp)
+            asm volatile("prefetch.global.L1 [%0];" :: "l"(src + (size_t)(row0 + threadIdx.x) * lds + c0 + 32));
         for (int r0 = 0; r0 < mp; r0 += RC) {
             const int nr = min(RC, mp - r0);
             if (!single) {
@@ -475,17 +498,18 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
         if (p.scale) {
             float amax = 0.0f;
             int   bad = 0;
-            if (vec4) {      // 16 bytes a lane, four rows in flight
-                for (int i0 = threadIdx.x / 32; i0 < m; i0 += 4 * (NT / 32))
+            if (vec4) {      // 16 bytes a lane, sixteen rows in flight (the matrix comes from HBM: few round trips)
+                constexpr int kFlight = 16;
+                for (int i0 = threadIdx.x / 32; i0 < m; i0 += kFlight * (NT / 32))
                     for (int j = (threadIdx.x & 31) * 4; j < n; j += 128) {
-                        float4 v[4];
+                        float4 v[kFlight];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
+                        for (int u = 0; u < kFlight; ++u) {
                             const int i = i0 + u * (NT / 32);
                             v[u] = i < m ? *reinterpret_cast<const float4*>(A + (size_t)i * p.lda + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
+                        for (int u = 0; u < kFlight; ++u) {
                             amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v[u].x), fabsf(v[u].y))), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
                             bad |= nonfinite(v[u].x) | nonfinite(v[u].y) | nonfinite(v[u].z) | nonfinite(v[u].w);
                         }
@@ -588,29 +612,8 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
         for (int pi = p.npanels - 1; pi >= 0; --pi) {
             const int k0 = pi * JB, jb = min(JB, K - k0), mp = m - k0;
             __syncthreads();
-            {   // the reflectors back from the scratch matrix: rows relative to the panel
-                const int warp = threadIdx.x >> 5, c = threadIdx.x & 31;
-                const int nq = (mp + 3) >> 2;
-                for (int rq0 = warp; rq0 < nq; rq0 += 2 * (NT / 32)) {      // two words a lane in flight
-                    float e[2][4];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int r = (rq0 + u * (NT / 32)) * 4;
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const int rr = r + t;
-                            e[u][t] = 0.0f;
-                            if (c < jb && rr < mp) e[u][t] = rr > c ? W[(size_t)(k0 + rr) * n + k0 + c] : (rr == c ? 1.0f : 0.0f);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int rq = rq0 + u * (NT / 32);
-                        if (rq < nq)
-                            *reinterpret_cast<float4*>(s.Vs + c * ldv + rq * 4) = make_float4(e[u][0], e[u][1], e[u][2], e[u][3]);
-                    }
-                }
-            }
+            // the reflectors back from the scratch matrix (rows relative to the panel): unit diagonal, zeros above
+            load_tile(s.Vs, ldv, W, n, k0, mp, k0, jb, LoadReflector{});
             for (int i = threadIdx.x; i < 32 * 32; i += NT) s.Ts[(i >> 5) * LDZ + (i & 31)] = Tg[(size_t)pi * 1024 + i];
             __syncthreads();
             update_columns(s, ldv, Q, qc, LoadPlain{}, Q, qc, k0, mp, k0, qc, false);
