@@ -307,7 +307,21 @@ __global__ void __launch_bounds__(1024) reduce_t_narrow_kernel(const float* __re
                                                               float* Z) {
     dependency_wait();
     __shared__ __align__(16) float Zs[128][8];
+    extern __shared__ __align__(16) float dsm_narrow[];
+    float (*Tt)[129] = reinterpret_cast<float (*)[129]>(dsm_narrow);       // Tt[k][i] = op(T)[i][k]
     const uint32_t j0 = blockIdx.x * 8;
+    {   // T into shared memory, sixteen entries a thread, all in flight together (read from global memory entry by
+        // entry inside the product below, every step of its 128 waited for L2)
+        float tv[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) tv[u] = T[threadIdx.x + 1024 * u];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int idx = threadIdx.x + 1024 * u, a = idx >> 7, b = idx & 127;      // T[a][b]
+            if (transposed) Tt[a][b] = tv[u];      // op(T)[i][k] = T[k][i]: Tt[k][i] = T[k][i]
+            else Tt[b][a] = tv[u];                 // op(T)[i][k] = T[i][k]: Tt[k][i] = T[i][k]
+        }
+    }
     {   // 1024 threads, an entry each, eight loads in flight; the chunks are added in order
         const int idx = threadIdx.x;
         const uint32_t k = idx >> 3, j = j0 + (idx & 7);
@@ -333,7 +347,7 @@ __global__ void __launch_bounds__(1024) reduce_t_narrow_kernel(const float* __re
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 8
     for (int k = 0; k < 128; ++k) {
-        const float t = transposed ? T[k * 128 + i] : T[i * 128 + k];
+        const float t = Tt[k][i];
         const float4 z = *reinterpret_cast<const float4*>(&Zs[k][4 * h]);
         acc[0] = fmaf(t, z.x, acc[0]); acc[1] = fmaf(t, z.y, acc[1]);
         acc[2] = fmaf(t, z.z, acc[2]); acc[3] = fmaf(t, z.w, acc[3]);
@@ -443,13 +457,23 @@ __global__ void __launch_bounds__(kMergeThreads) merge_t_kernel(const MergeParam
     float (*X)[33]   = reinterpret_cast<float (*)[33]>(dsm + 2 * 128 * 129);
     const int t = threadIdx.x;
     const int width = 32 * (int)p.panels;
-    for (int idx = t; idx < 128 * 128; idx += kMergeThreads) {
-        const int i = idx >> 7, j = idx & 127;
-        float v = 0.0f;
-        if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) v = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
-        Ta[i][j] = v;
-        // the Gram matrix, already summed over the chunks (gram_sum_kernel)
-        G[i][j] = (p.gram && i < width && j < width && (uint32_t)j < p.gld) ? p.gram[(size_t)i * p.gld + j] : 0.0f;
+    {   // a thread's sixteen entries of each matrix are fetched before the first is stored: one trip to L2, not sixteen
+        constexpr int kPer = 128 * 128 / kMergeThreads;
+        float tv[kPer], gv[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = t + u * kMergeThreads, i = idx >> 7, j = idx & 127;
+            tv[u] = 0.0f;
+            if ((i >> 5) == (j >> 5) && (uint32_t)(i >> 5) < p.panels) tv[u] = p.tp[(size_t)(i >> 5) * 1024 + (i & 31) * 32 + (j & 31)];
+            // the Gram matrix, already summed over the chunks (gram_sum_kernel)
+            gv[u] = (p.gram && i < width && j < width && (uint32_t)j < p.gld) ? p.gram[(size_t)i * p.gld + j] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int idx = t + u * kMergeThreads, i = idx >> 7, j = idx & 127;
+            Ta[i][j] = tv[u];
+            G[i][j] = gv[u];
+        }
     }
     __syncthreads();
     for (uint32_t q = 1; q < p.panels; ++q) {
@@ -481,6 +505,7 @@ bool use_tensor_cores() {
 }
 
 constexpr size_t kReduceWideSmem = (128 * 132 + 128 * 36) * sizeof(float);
+constexpr size_t kReduceNarrowSmem = 128 * 129 * sizeof(float);
 constexpr size_t kMergeSmem = (2 * 128 * 129 + 96 * 33) * sizeof(float);
 
 // C (mp rows, nc columns) <- (I - Y op(T) Y^T) C for an aggregate: Y mp x kw (kw <= 128), T 128 x 128.
@@ -502,7 +527,7 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, ytsp, error);
     else if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
-    if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 1024, 0, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
+    if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 1024, kReduceNarrowSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
     if (split) launch_tc_yz_split(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, ysp, zsp, error);
     else if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
@@ -654,12 +679,148 @@ __global__ void __launch_bounds__(256) inner_apply_kernel(const float* __restric
     }
 }
 
+// The two kernels above in one launch, for panels of at most 8 x 1024 rows: the blocks of a column group (one per
+// 1024 rows) form a thread-block cluster, every block stores its part of Z = Y^T C into the shared memory of all of
+// them (distributed shared memory), and after one cluster barrier each sums the parts in the same fixed order and
+// applies W = T^T Z to its own rows. One launch and no round trip through global memory between the halves.
+constexpr int kInnerCluster = 8;
+
+__device__ __forceinline__ uint32_t inner_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t inner_cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+
+__global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restrict__ Y, size_t ldy, const float* __restrict__ T,
+                                                          float* C, size_t ldc, uint32_t mp, uint32_t jb, uint32_t nc) {
+    dependency_wait();
+    // every block of the cluster has started once this barrier's wait (below, before the remote stores) returns
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    __shared__ float red[8][32 * ICS];
+    __shared__ float parts[kInnerCluster][32 * ICS];      // parts[r]: the part of the cluster's block r, stored by that block
+    __shared__ float Zs[32][ICS], Ws[32][ICS];
+    __shared__ float Ts[32][33];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t rank = inner_cluster_rank(), nblk = inner_cluster_size();
+    const uint32_t c0 = blockIdx.x * ICS, ncb = min((uint32_t)ICS, nc - c0);
+    const uint32_t r_begin = blockIdx.y * IRB, r_end = min(mp, r_begin + IRB);
+    const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
+    float tv[4];                                            // T on its way to shared memory while Z is formed
+#pragma unroll
+    for (int u = 0; u < 4; ++u) tv[u] = T[t + 256 * u];
+    float z[32][ICS];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) z[k][j] = 0.0f;
+    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
+        float y[32], c[ICS];
+        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) c[j] = (uint32_t)j < ncb ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+#pragma unroll
+            for (int j = 0; j < ICS; ++j) z[k][j] = fmaf(y[k], c[j], z[k][j]);
+    }
+#pragma unroll
+    for (int j = 0; j < ICS; ++j) {
+        float pcol[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) pcol[k] = z[k][j];
+#pragma unroll
+        for (int half = 16; half >= 1; half >>= 1) {
+            const bool upper = (lane & half) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float send = upper ? pcol[i] : pcol[i + half];
+                const float keep = upper ? pcol[i + half] : pcol[i];
+                pcol[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+            }
+        }
+        red[warp][lane * ICS + j] = pcol[0];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) Ts[(t + 256 * u) >> 5][(t + 256 * u) & 31] = tv[u];
+    __syncthreads();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (t < 32 * ICS) {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][t];
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&parts[rank][t]);
+        for (uint32_t r = 0; r < nblk; ++r) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(remote), "f"(v) : "memory");
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (t < 32 * ICS) {
+        float v = 0.0f;
+        for (uint32_t r = 0; r < nblk; ++r) v += parts[r][t];      // the same order in every block
+        Zs[t / ICS][t % ICS] = (uint32_t)(t % ICS) < ncb ? v : 0.0f;
+    }
+    __syncthreads();
+    if (t < 32 * ICS) {     // W = T^T Z
+        const int i = t / ICS, j = t % ICS;
+        float v = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) v = fmaf(Ts[k][i], Zs[k][j], v);
+        Ws[i][j] = v;
+    }
+    __syncthreads();
+    float w[32][ICS];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) w[k][j] = Ws[k][j];
+    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
+        float y[32];
+        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
+        float d[ICS];
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) d[j] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+#pragma unroll
+            for (int j = 0; j < ICS; ++j) d[j] = fmaf(y[k], w[k][j], d[j]);
+#pragma unroll
+        for (int j = 0; j < ICS; ++j)
+            if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] -= d[j];
+    }
+}
+
 // zpart: scratch of at least ceil(mp / 1024) * 32 * ((nc + 3) & ~3) floats
 void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T, float* C, size_t ldc, uint32_t mp,
                  uint32_t jb, uint32_t nc, float* zpart) {
     if (nc == 0 || mp == 0) return;
     const uint32_t chunks = (mp + IRB - 1) / IRB, ncp = (nc + 3) & ~3u;
     const dim3 grid((nc + ICS - 1) / ICS, chunks);
+    const char* fused_env = std::getenv("QR_INNER_FUSED");      // QR_INNER_FUSED=0: the two kernels
+    const bool fused = !(fused_env && fused_env[0] == '0');
+    if (fused && chunks <= (uint32_t)kInnerCluster) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = chunks;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = dependent_launches_enabled() ? 2 : 1;
+        cuda_check(cudaLaunchKernelEx(&cfg, inner_fused_kernel, Y, ldy, T, C, ldc, mp, jb, nc), "inner update launch");
+        return;
+    }
     launch_dependent(inner_z_kernel, grid, 256, 0, stream, Y, ldy, C, ldc, mp, jb, nc, zpart, ncp);
     launch_dependent(inner_apply_kernel, grid, 256, 0, stream, Y, ldy, T, C, ldc, mp, jb, nc, zpart, ncp, chunks);
     cuda_check(cudaGetLastError(), "inner update launch");
@@ -748,6 +909,8 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                                         (int)kReduceWideSmem), "reduce_t_wide shared memory");
         cuda_check(cudaFuncSetAttribute(merge_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMergeSmem),
                    "merge_t shared memory");
+        cuda_check(cudaFuncSetAttribute(reduce_t_narrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kReduceNarrowSmem), "reduce_t_narrow shared memory");
         once.mark(ctx.device);
     }
     const cudaStream_t caller = stream;

@@ -29,6 +29,7 @@
 #include "qr_small_steps.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 namespace mlb {
@@ -147,7 +148,10 @@ struct Level {
 // Blocks of 256 rows at every width: the most the block kernel's panels hold with a column per lane. (For 65
 // to 128 columns a level then only halves the rows, but blocks of 512 rows, whose panels go a thread per
 // entry, measured a quarter to a third slower: 16 x 8192 x 128 in 2.24 against 2.99 ms.)
-uint32_t block_rows(uint32_t) { return 256; }
+uint32_t block_rows(uint32_t) {
+    const char* e = std::getenv("QR_TSQR_ROWS");      // for measurements: 256 (default) or 512
+    return e && std::atoi(e) == 512 ? 512u : 256u;
+}
 
 // The levels below the top: each cuts `rows` into blocks of c (the last takes the remainder, < 2c).
 std::vector<Level> plan(uint32_t m, uint32_t n) {
