@@ -220,10 +220,13 @@ void qr_enqueue(mlb::DeviceContext& ctx, cudaStream_t stream, const core::Matric
 
 namespace {
 
-// Host pointers: the batch in chunks through two sets of device buffers, the
-// copy in of chunk i+1 and the copy out of chunk i-1 running beside the
-// kernels of chunk i on the context's three streams.
+// Host pointers: the batch in chunks through three sets of device buffers, the
+// copy in of a later chunk and the copy out of an earlier one running beside the
+// kernels of chunk i on the context's three streams. (With two sets the copy in of
+// chunk i + 1 had to wait for the copy out of chunk i - 1: at two ranks a machine
+// the pipeline then took 1.24 times what its copies alone take.)
 void run_staged(mlb::DeviceContext& ctx, const Matrices& a, float* q, float* r, QrMode mode, int forced) {
+    constexpr int kSets = mlb::DeviceContext::kStagingSets;
     const uint32_t m = a.rows, n = a.cols;
     const size_t qc = core::qr_q_cols(mode, m, n), rr = core::qr_r_rows(mode, m, n);
     const size_t fa = (size_t)m * n, fq = (size_t)m * qc, fr = rr * n;
@@ -239,24 +242,24 @@ void run_staged(mlb::DeviceContext& ctx, const Matrices& a, float* q, float* r, 
     std::lock_guard<std::mutex> lock(ctx.mutex);
     // the staging buffers belong to the copy-in stream's workspace; the kernels'
     // own scratch to the compute stream's
-    float* base = static_cast<float*>(ctx.workspace(ctx.copy_in, 2 * set_floats * sizeof(float)));
-    float* da[2], *dq[2], *dr[2];
-    for (int s = 0; s < 2; ++s) {
+    float* base = static_cast<float*>(ctx.workspace(ctx.copy_in, kSets * set_floats * sizeof(float)));
+    float* da[kSets], *dq[kSets], *dr[kSets];
+    for (int s = 0; s < kSets; ++s) {
         da[s] = base + s * set_floats;
         dq[s] = da[s] + up(chunk * fa);
         dr[s] = dq[s] + up(chunk * fq);
     }
     size_t done = 0;
     for (size_t i = 0; done < a.batch; ++i) {
-        const int s = (int)(i & 1);
+        const int s = (int)(i % kSets);
         const uint32_t count = (uint32_t)std::min<size_t>(chunk, a.batch - done);
         // the set is free once its previous copy out has finished
-        if (i >= 2) mlb::cuda_check(cudaStreamWaitEvent(ctx.copy_in, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
+        if (i >= (size_t)kSets) mlb::cuda_check(cudaStreamWaitEvent(ctx.copy_in, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
         mlb::cuda_check(cudaMemcpyAsync(da[s], a.data + done * fa, count * fa * sizeof(float),
                                         cudaMemcpyHostToDevice, ctx.copy_in), "copy in");
         mlb::cuda_check(cudaEventRecord(ctx.ev_in[s], ctx.copy_in), "cudaEventRecord");
         mlb::cuda_check(cudaStreamWaitEvent(ctx.compute, ctx.ev_in[s], 0), "cudaStreamWaitEvent");
-        if (i >= 2) mlb::cuda_check(cudaStreamWaitEvent(ctx.compute, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
+        if (i >= (size_t)kSets) mlb::cuda_check(cudaStreamWaitEvent(ctx.compute, ctx.ev_out[s], 0), "cudaStreamWaitEvent");
         run_on_device(ctx, ctx.compute, {da[s], count, m, n}, dq[s], dr[s], mode, forced);
         mlb::cuda_check(cudaEventRecord(ctx.ev_done[s], ctx.compute), "cudaEventRecord");
         mlb::cuda_check(cudaStreamWaitEvent(ctx.copy_out, ctx.ev_done[s], 0), "cudaStreamWaitEvent");

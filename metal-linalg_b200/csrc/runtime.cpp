@@ -81,6 +81,8 @@ DeviceContext& context(int device) {
         for (int i = 0; i < 2; ++i) {
             cuda_check(cudaEventCreateWithFlags(&c->ev_panel[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_update[i], cudaEventDisableTiming), "cudaEventCreate");
+        }
+        for (int i = 0; i < DeviceContext::kStagingSets; ++i) {
             cuda_check(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming), "cudaEventCreate");

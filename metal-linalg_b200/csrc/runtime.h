@@ -42,8 +42,8 @@ struct DeviceContext {
     std::map<cudaStream_t, Workspace> workspaces;
     std::map<cudaStream_t, Workspace> outer_workspaces;   // of a caller of the QR (the SVD), beside the QR's own
     cudaStream_t   copy_in = nullptr, copy_out = nullptr, compute = nullptr;   // host-pointer staging
-    cudaEvent_t    ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr},
-                   ev_out[2] = {nullptr, nullptr};
+    static constexpr int kStagingSets = 3;      // device buffer sets of the host-pointer pipeline
+    cudaEvent_t    ev_in[kStagingSets] = {}, ev_done[kStagingSets] = {}, ev_out[kStagingSets] = {};
     // the blocked QR's second stream (trailing updates beside the next panels) and its events
     cudaStream_t   aux = nullptr;
     cudaEvent_t    ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr};
