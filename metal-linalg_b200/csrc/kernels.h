@@ -97,6 +97,15 @@ void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const f
 bool qr_blocked_fits(uint32_t m, uint32_t n);
 void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
 
+// A wide matrix (m < n) by its leading m x m block and one product (qr_wide.cu). `a1` [batch][m][m] takes the
+// leading blocks (a matrix with a NaN or an infinity anywhere gets NaN into its block); after the QR of a1 into q
+// (row stride ldq >= m) and r1 [batch][m][m], launch_wide_finish writes r [batch][m][n] = [r1 | q^T a(:, m:)].
+// Scratch: wide_scratch_floats() floats hold a1, r1, `bad` (one word a matrix) and, when the caller asked for no Q, Q.
+size_t wide_scratch_floats(uint32_t batch, uint32_t m, bool need_q_scratch);
+void   launch_wide_gather(cudaStream_t stream, const float* a, uint32_t batch, uint32_t m, uint32_t n, float* a1, unsigned* bad);
+void   launch_wide_finish(cudaStream_t stream, const float* q, uint32_t ldq, const float* a, const float* r1, float* r,
+                          uint32_t batch, uint32_t m, uint32_t n);
+
 // Small utilities shared by the launchers.
 void launch_fill_identity(cudaStream_t stream, float* q, uint32_t batch, uint32_t m, uint32_t cols);
 // out (row-major, contiguous float32) = the tensor `in` of element type `dtype` (the order of

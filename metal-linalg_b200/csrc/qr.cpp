@@ -199,10 +199,54 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     return QrKernel::blocked;
 }
 
+// QR_WIDE=0: wide matrices through the general kernels, whole (for comparison and tests)
+bool wide_by_leading_block() {
+    const char* e = std::getenv("QR_WIDE");
+    return !(e && e[0] == '0');
+}
+
 void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices& a, float* q, float* r, QrMode mode,
-                   int forced /* -1: route */) {
-    const mlb::QrProblem p = problem(a, q, r, mode);
+                   int forced /* -1: route */, bool may_split = true);
+
+// A wide matrix by its leading M x M block and one product (qr_wide.cu; the reference's CPU path does the
+// same, src/qr_cpu.mm:6-9,112-118): taken where takes_wide_split says it pays. Q (M x M in every mode of a wide
+// matrix) goes to the caller's buffer, or to scratch when R alone was asked for.
+// Measured on a B200 (ms, whole against split): one 128 x 1024 0.53 / 0.16, one 64 x 2048 0.43 / 0.075, eight 256 x 2048
+// 2.70 / 0.60, 2048 of 48 x 100 0.47 / 0.44; R alone, which otherwise never forms Q: 128 x 1024 0.49 / 0.16, 256 of
+// 64 x 256 0.10 / 0.10, 2048 of 48 x 100 0.36 / 0.44, so R alone splits from four times as wide as tall. Where the
+// square block itself would go to the grid-parallel blocked QR the split loses (512 x 4096: 0.99 / 1.01; 2000 x 6000:
+// 4.4 / 5.2: the blocked QR's own trailing updates run on the tensor cores, the product here on FP32 FMAs) and is not taken.
+bool takes_wide_split(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, QrMode mode, int forced) {
+    if (m >= n || n - m < 32 || !wide_by_leading_block()) return false;
+    if (mode == QrMode::r && n < 4 * (uint64_t)m) return false;
+    if (mlb::qr_small_fits(m, n, core::qr_q_cols(mode, m, n))) return false;
+    if ((uint64_t)batch * m * m >= ((uint64_t)1 << 40)) return false;
+    const QrKernel inner = forced >= 0 ? (QrKernel)forced : choose(ctx, m, m, batch, QrMode::reduced);
+    return inner != QrKernel::blocked;
+}
+
+bool run_wide(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices& a, float* q, float* r, QrMode mode, int forced) {
+    const uint32_t m = a.rows, n = a.cols;
+    if (!takes_wide_split(ctx, m, n, a.batch, mode, forced)) return false;
+    const bool q_scratch = q == nullptr;
+    const size_t block = ((size_t)a.batch * m * m + 63) & ~(size_t)63;
+    float* ws = static_cast<float*>(ctx.outer_workspace(stream, mlb::wide_scratch_floats(a.batch, m, q_scratch) * sizeof(float)));
+    float* a1 = ws;
+    float* r1 = ws + block;
+    float* qs = q_scratch ? ws + 2 * block : q;
+    unsigned* bad = reinterpret_cast<unsigned*>(ws + (q_scratch ? 3 : 2) * block);
+    mlb::launch_wide_gather(stream, a.data, a.batch, m, n, a1, bad);
+    // the square block's Q is M x M whether reduced or complete; R1 is M x M
+    run_on_device(ctx, stream, {a1, a.batch, m, m}, qs, r1, QrMode::reduced, forced, false);
+    mlb::launch_wide_finish(stream, qs, m, a.data, r1, r, a.batch, m, n);
+    return true;
+}
+
+void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices& a, float* q, float* r, QrMode mode,
+                   int forced /* -1: route */, bool may_split) {
     ctx.last_shape[0] = a.batch; ctx.last_shape[1] = a.rows; ctx.last_shape[2] = a.cols;
+    if (may_split && run_wide(ctx, stream, a, q, r, mode, forced)) return;
+    const mlb::QrProblem p = problem(a, q, r, mode);
     const QrKernel k = forced >= 0 ? (QrKernel)forced : choose(ctx, a.rows, a.cols, a.batch, mode);
     switch (k) {
         case QrKernel::small:   mlb::launch_qr_small(ctx, stream, p); break;
@@ -215,7 +259,8 @@ void run_on_device(mlb::DeviceContext& ctx, cudaStream_t stream, const Matrices&
 } // namespace
 
 void qr_enqueue(mlb::DeviceContext& ctx, cudaStream_t stream, const core::Matrices& a, float* q, float* r, core::QrMode mode) {
-    run_on_device(ctx, stream, a, q, r, mode, -1);
+    // the library's own callers hold the outer workspace themselves, and hand over tall matrices only
+    run_on_device(ctx, stream, a, q, r, mode, -1, false);
 }
 
 namespace {
@@ -331,7 +376,10 @@ void run(const Matrices& a, float* q, float* r, QrMode mode, int forced) {
 namespace core {
 
 QrKernel qr_kernel(uint32_t m, uint32_t n, uint32_t batch, QrMode mode) {
-    return choose(mlb::context(mlb::thread_device()), m, n, batch, mode);
+    mlb::DeviceContext& ctx = mlb::context(mlb::thread_device());
+    // a wide matrix beyond the register kernel is factored by its leading square block (run_wide)
+    if (takes_wide_split(ctx, m, n, batch, mode, -1)) return choose(ctx, m, m, batch, QrMode::reduced);
+    return choose(ctx, m, n, batch, mode);
 }
 const char* qr_kernel_name(QrKernel k) {
     switch (k) {

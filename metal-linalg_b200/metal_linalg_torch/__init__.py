@@ -1,5 +1,10 @@
 """Batched float32 Householder QR on NVIDIA B200 for PyTorch, behind the API of
-metal-linalg's torch binding (reference: python-torch/metal_linalg_torch/__init__.py).
+metal-linalg's torch binding.
+
+ADAPTED COPY OF THE REFERENCE'S FILE, not written from scratch: `_prepare`, `_needs_grad`, `_TRACED`, `_result` and
+`qr()` with its docstring are the reference's python-torch/metal_linalg_torch/__init__.py:45-115 (under half of this
+file), kept so that a caller of the reference's binding finds the same functions with the same behaviour; "cuda" is
+added to the devices served, and the helpers below `qr` are this build's.
 
     import torch
     import metal_linalg_torch as mlt

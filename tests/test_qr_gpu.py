@@ -828,3 +828,28 @@ def test_second_gpu_in_one_process():
     big = torch.randn(4, 400, 128)                     # the block Jacobi and the wide left-vector kernel
     s0, s1 = mlt.svd(big.to("cuda:0")).S, mlt.svd(big.to("cuda:1")).S
     assert torch.equal(s0.cpu(), s1.cpu())
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("shape", [(128, 1024), (64, 2048), (48, 100), (33, 65), (200, 1000), (16, 64)])
+def test_wide_by_leading_block(shape, mode):
+    """A wide matrix is factored by its leading square block and R's other columns come from one product
+    (the reference's CPU path: src/qr_cpu.mm:6-9,112-118): the same factorisation as the general kernels
+    give on the whole matrix (QR_WIDE=0), and the oracle's R. A NaN right of the leading block still makes
+    the whole matrix's outputs NaN."""
+    m, n = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((5, m, n)).astype(np.float32)
+    a[3, m - 1, n - 1] = np.nan
+    a[4] *= 1e-30
+    good = [0, 1, 2, 4]
+    q, r = gpu_qr(a, mode)
+    assert np.isnan(r[3]).all() and (q is None or np.isnan(q[3]).all())
+    _, r_ref = harness.oracle_qr(a[good], mode)
+    check(a[good], None if q is None else q[good], r[good], mode, r_ref)
+    os.environ["QR_WIDE"] = "0"
+    try:
+        q0, r0 = gpu_qr(a, mode)
+    finally:
+        os.environ.pop("QR_WIDE", None)
+    assert harness.r_parity(r[good], r0[good]) <= 1e-5
