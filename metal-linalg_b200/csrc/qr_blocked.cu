@@ -261,16 +261,49 @@ __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restr
     float (*Tt)[132] = reinterpret_cast<float (*)[132]>(dsm);                // Tt[k][i] = op(T)[i][k]
     float (*Zs)[36]  = reinterpret_cast<float (*)[36]>(dsm + 128 * 132);
     const uint32_t j0 = blockIdx.x * 32;
-    for (int idx = threadIdx.x; idx < 128 * 128; idx += 256) {
-        const int k = idx >> 7, i = idx & 127;
-        Tt[k][i] = transposed ? T[k * 128 + i] : T[i * 128 + k];
+    // Both operands are fetched many loads at a time (sixteen of T; a thread's sixteen entries of four chunks): read
+    // one by one in a loop, every load waited for L2 (37 us a launch at 4096 x 4096, most of it those waits).
+    for (int base = 0; base < 128 * 128; base += 16 * 256) {
+        float tv[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) tv[u] = T[base + threadIdx.x + 256 * u];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int idx = base + threadIdx.x + 256 * u, a = idx >> 7, c = idx & 127;      // T[a][c]
+            if (transposed) Tt[a][c] = tv[u];      // Tt[k][i] = op(T)[i][k] = T[k][i]
+            else Tt[c][a] = tv[u];                 // Tt[k][i] = T[i][k]
+        }
     }
-    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
-        const uint32_t k = idx >> 5, j = j0 + (idx & 31);
-        float sum = 0.0f;
-        if (j < nc)
-            for (uint32_t ch = 0; ch < chunks; ++ch) sum += Zp[((size_t)ch * AG + k) * ncp + j];
-        Zs[k][idx & 31] = sum;
+    {
+        float sum[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) sum[e] = 0.0f;
+        const uint32_t j = j0 + (threadIdx.x & 31);
+        if (j < nc) {
+            const float* src = Zp + (size_t)(threadIdx.x >> 5) * ncp + j;      // entry e: row k = (threadIdx.x >> 5) + 8 e
+            const size_t step = (size_t)AG * ncp;
+            uint32_t ch = 0;
+            for (; ch + 4 <= chunks; ch += 4) {      // the chunks are added in order, four at a time in flight
+                float v[4][16];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[c][e] = src[(size_t)(ch + c) * step + (size_t)8 * e * ncp];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) sum[e] += v[c][e];
+            }
+            for (; ch < chunks; ++ch) {
+                float v[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) v[e] = src[(size_t)ch * step + (size_t)8 * e * ncp];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) sum[e] += v[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) Zs[(threadIdx.x >> 5) + 8 * e][threadIdx.x & 31] = sum[e];
     }
     __syncthreads();
     const int ig = threadIdx.x >> 3, jg = threadIdx.x & 7;

@@ -184,6 +184,18 @@ __global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
     const uint32_t out_rows = p.mode == 0 ? 128u : min(m_valid, 128u);
     const bool out_vec = (p.ldo & 3) == 0 && (reinterpret_cast<size_t>(out_tile) & 15) == 0 && n_valid >= 128;
 
+    // C -= Y Z: the tile of C is fetched now, a warp a row and sixteen rows a warp all in flight, and waits in
+    // registers until the products are done (read row by row afterwards, every row waited for L2)
+    float4 creg[128 / (TCT / 32)];
+    const bool c_early = p.mode == 1 && out_vec;
+    if (c_early) {
+#pragma unroll
+        for (int u = 0; u < 128 / (TCT / 32); ++u) {
+            const uint32_t r = warp + (TCT / 32) * u;
+            creg[u] = r < out_rows ? *reinterpret_cast<const float4*>(out_tile + (size_t)r * p.ldo + 4 * lane)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bars[s])));
@@ -252,7 +264,14 @@ __global__ void __launch_bounds__(TCT, 2) tc_gemm_kernel(const TcParams p) {
     __syncthreads();
     const bool ok = !failed;
     if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
-    if (ok && tiles > 0 && p.mode == 1) {   // C's tile, a warp a row
+    if (ok && tiles > 0 && c_early) {
+#pragma unroll
+        for (int u = 0; u < 128 / (TCT / 32); ++u) {
+            const uint32_t r = warp + (TCT / 32) * u;
+            if (r < out_rows) *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = creg[u];
+        }
+        __syncthreads();
+    } else if (ok && tiles > 0 && p.mode == 1) {   // C's tile, a warp a row
         for (uint32_t r = warp; r < out_rows; r += TCT / 32) {
             const float* src = out_tile + (size_t)r * p.ldo + 4 * lane;
             float4 f = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -144,9 +144,20 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
     float* out_tile = p.c + (size_t)r0 * p.ldc + j0;
     const bool out_vec = (p.ldc & 3) == 0 && (reinterpret_cast<size_t>(out_tile) & 15) == 0 && n_valid == 128;
 
-    // C's tile is read only after the products (its place in shared memory is the slots'): ask for it
-    // to be brought into L2 now, two 128-byte lines a thread, so that the read finds it there
-    if (threadIdx.x / 2 < out_rows) {
+    // C's tile is needed only after the products (its place in shared memory is the slots'), but it is fetched
+    // now, into registers, a warp a row and 16 bytes a lane, sixteen rows a warp all in flight: the loads
+    // complete while one thread issues the products, and the epilogue starts with the tile at hand. (Read row by
+    // row after the products, every row waited for L2: a third of a block's life.) A tile that cannot be read
+    // by whole aligned words is asked into L2 instead and read after the products, entry by entry.
+    float4 creg[128 / (T2 / 32)];
+    if (out_vec) {
+#pragma unroll
+        for (int u = 0; u < 128 / (T2 / 32); ++u) {
+            const uint32_t r = warp + (T2 / 32) * u;
+            creg[u] = r < out_rows ? *reinterpret_cast<const float4*>(out_tile + (size_t)r * p.ldc + 4 * lane)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else if (threadIdx.x / 2 < out_rows) {
         const float* line = out_tile + (size_t)(threadIdx.x / 2) * p.ldc + 64 * (threadIdx.x & 1);
         if (64 * (threadIdx.x & 1) < n_valid) {
             asm volatile("prefetch.global.L2 [%0];" :: "l"(line));
@@ -221,19 +232,23 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
     __syncthreads();
     const bool ok = !failed;
     if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
-    if (ok) {   // C's tile, a warp a row
-        for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
-            const float* src = out_tile + (size_t)r * p.ldc + 4 * lane;
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (out_vec) {
-                f = *reinterpret_cast<const float4*>(src);
-            } else {
+    if (ok) {   // C's tile into shared memory, a warp a row
+        if (out_vec) {
+#pragma unroll
+            for (int u = 0; u < 128 / (T2 / 32); ++u) {
+                const uint32_t r = warp + (T2 / 32) * u;
+                if (r < out_rows) *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = creg[u];
+            }
+        } else {
+            for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
+                const float* src = out_tile + (size_t)r * p.ldc + 4 * lane;
+                float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (4 * lane + 0 < n_valid) f.x = src[0];
                 if (4 * lane + 1 < n_valid) f.y = src[1];
                 if (4 * lane + 2 < n_valid) f.z = src[2];
                 if (4 * lane + 3 < n_valid) f.w = src[3];
+                *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = f;
             }
-            *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = f;
         }
         __syncthreads();
         // warp w reads lanes 32 (w % 4) .. + 31 (its rows of the tile), columns 64 (w / 4) .. + 63
