@@ -57,6 +57,7 @@ struct MidParams {
     int          ldv;
     int          npanels;
     int          by_columns;   // panels of at most 256 rows factored with a column per lane
+    int          pairs;        // ... and two columns a reduction (factor_cols2)
     // matrix index -> (outer, inner) = (mat / inner_count, mat % inner_count) when inner_count > 0:
     // the matrix's buffers then start at outer * *_outer + inner * *_stride
     unsigned     inner_count;
@@ -424,7 +425,7 @@ __device__ void build_t(const Smem& s, int ldv, int mp) {
 // Out as finish_panel's and build_t's: the factored panel in the scratch matrix, the clean V in
 // s.Vs, T in s.Ts. The trailing tile buffer and the partial-sum buffer serve as its scratch.
 template <int RW>      // rows a lane: 32 (up to 256 rows) or 64 (up to 512)
-__device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float* W, size_t ldw, int k0) {
+__device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float* W, size_t ldw, int k0, bool pairs) {
     using namespace cols;
     cols::Smem& cs = *reinterpret_cast<cols::Smem*>(s.Cs);
     static_assert(sizeof(cols::Smem) <= 32 * LDC * sizeof(float), "the tile buffer holds the panel scratch");
@@ -442,7 +443,8 @@ __device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float*
             x2[2 * q]     = pack(v.x, v.y);
             x2[2 * q + 1] = pack(v.z, v.w);
         }
-        factor_cols<RW, false>(x2, cs, pub, nullptr, my_sc, nw);
+        if (pairs) factor_cols2<RW>(x2, cs, pub, my_sc, BlockSync{nw});
+        else factor_cols<RW, false>(x2, cs, pub, nullptr, my_sc, nw);
     }
     __syncthreads();
     if (warp == 0) build_t_to(cs, s.Ts, LDZ);
@@ -550,9 +552,9 @@ __global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
             else         load_tile(s.Vs, ldv, W, n, k0, mp, k0, jb, LoadPlain{});
             __syncthreads();
             if (mp <= 256 && p.by_columns) {
-                factor_panel_cols<32>(s, ldv, mp, jb, W, n, k0);
+                factor_panel_cols<32>(s, ldv, mp, jb, W, n, k0, p.pairs != 0);
             } else if (PRW == 64 && mp <= 512 && p.by_columns) {
-                factor_panel_cols<PRW>(s, ldv, mp, jb, W, n, k0);
+                factor_panel_cols<PRW>(s, ldv, mp, jb, W, n, k0, p.pairs != 0);
             } else {
                 factor_panel(s, ldv, mp, jb);
                 finish_panel(s, ldv, mp, jb, W, n, k0);
@@ -629,6 +631,11 @@ int mid_by_columns() {
     const char* e = std::getenv("QR_MID_ROWS");
     return !(e && e[0] == '1');
 }
+// QR_PANEL_PAIRS=0: panels a column a reduction instead of two (here and in the blocked QR's cluster panels)
+int mid_pairs() {
+    const char* e = std::getenv("QR_PANEL_PAIRS");
+    return !(e && e[0] == '0');
+}
 }
 
 bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
@@ -679,6 +686,7 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& pr,
     p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
     p.npanels = (p.K + JB - 1) / JB;
     p.by_columns = mid_by_columns();
+    p.pairs = mid_pairs();
     p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
 
     const size_t smem = smem_bytes(p.ldv);
@@ -759,6 +767,7 @@ void launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& pr) 
     p.ldv = (int)((pr.m + 31) / 32) * 32 + 4;
     p.npanels = (p.K + JB - 1) / JB;
     p.by_columns = mid_by_columns();
+    p.pairs = mid_pairs();
     p.slot_floats = (((uint64_t)pr.m * pr.n + 3) & ~(uint64_t)3) + (uint64_t)p.npanels * 1024;
     const size_t smem = smem_bytes(p.ldv);
     if (pr.m > 1024 || smem > (size_t)smem_optin)

@@ -573,6 +573,7 @@ struct ClusterPanelParams {
     size_t   ldy;
     float*   t;         // [32][32] out
     uint32_t mp, jb;
+    int      pairs;     // two columns a reduction (factor_cols2)
 };
 
 template <int RW>
@@ -581,7 +582,7 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     dependency_wait();
     __shared__ __align__(16) cols::Smem s;
     __shared__ __align__(16) cols::ClusterShared cs;
-    __shared__ __align__(16) float pub[kWarps * RW];
+    __shared__ __align__(16) float pub[2 * kWarps * RW];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint32_t rank = cluster_rank(), ncta = cluster_size();
     const uint32_t row0 = (rank * kWarps + warp) * RW;
@@ -598,7 +599,8 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     }
     cluster_barrier();          // every block of the cluster is running before any writes into another's shared memory
     float my_sc;
-    factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
+    if (p.pairs) factor_cols2<RW>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});
+    else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
     if (rank == 0 && warp == 0) {
         // T straight to global memory; rows and columns from jb on are zero (their reflectors are the identity)
@@ -722,7 +724,8 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
                 once.mark(device);
             }
         }
-        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb};
+        const char* envp = std::getenv("QR_PANEL_PAIRS");
+        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb, !(envp && envp[0] == '0')};
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(ncta);
         cfg.blockDim = dim3(PT);

@@ -48,6 +48,9 @@ struct Smem {
     float G[32][33];             // G[k][j] = v_k^T v_j for k < j (unit-diagonal reflectors)
     float T[32][33];
     float rows[32][32];          // the block's first 32 rows as they finish: R, and the reflectors' tails below the diagonal
+    // the two-column steps (factor_cols2): partial products with columns j and j + 1, and the two pivot rows, by pair parity
+    float redp[2][kWarps][32], redq[2][kWarps][32];
+    float prow0[2][32], prow1[2][32];
 };
 
 // 1 / x to an ulp or so (x normal)
@@ -79,6 +82,19 @@ struct BlockSync {
         for (int w = 1; w < nw; ++w) d += s.red[buf][w][lane];
         return d;
     }
+    // the same for the two sums of a two-column step
+    __device__ __forceinline__ void exchange2(Smem& s, int buf, int lane, int warp) const {
+        (void)s; (void)buf; (void)lane; (void)warp;
+        step_barrier(32 * nw);
+    }
+    __device__ __forceinline__ void total2(const Smem& s, int buf, int lane, float& p, float& q) const {
+        p = s.redp[buf][0][lane];
+        q = s.redq[buf][0][lane];
+        for (int w = 1; w < nw; ++w) {
+            p += s.redp[buf][w][lane];
+            q += s.redq[buf][w][lane];
+        }
+    }
 };
 
 // ClusterSync: the rows are held by the eight warps of each block of a thread-block CLUSTER (block
@@ -91,6 +107,7 @@ struct BlockSync {
 constexpr int kMaxCluster = 16;
 struct ClusterShared {
     float cred[2][kMaxCluster][32];      // the blocks' sums, by step parity
+    float credp[2][kMaxCluster][32], credq[2][kMaxCluster][32];      // and of the two-column steps, by pair parity
 };
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -133,6 +150,33 @@ struct ClusterSync {
         float d = cs->cred[buf][0][lane];
         for (uint32_t r = 1; r < ncta; ++r) d += cs->cred[buf][r][lane];
         return d;
+    }
+    __device__ __forceinline__ void exchange2(Smem& s, int buf, int lane, int warp) const {
+        step_barrier(32 * kWarps);
+        float dp = s.redp[buf][0][lane], dq = s.redq[buf][0][lane];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) {
+            dp += s.redp[buf][w][lane];
+            dq += s.redq[buf][w][lane];
+        }
+        for (uint32_t r = warp; r < ncta; r += kWarps) {
+            store_to_block(&cs->credp[buf][rank][lane], r, dp);
+            store_to_block(&cs->credq[buf][rank][lane], r, dq);
+            if (rank == 0 && r != 0) {
+                store_to_block(&s.prow0[buf][lane], r, s.prow0[buf][lane]);
+                store_to_block(&s.prow1[buf][lane], r, s.prow1[buf][lane]);
+            }
+        }
+        cluster_barrier();
+    }
+    __device__ __forceinline__ void total2(const Smem& s, int buf, int lane, float& p, float& q) const {
+        (void)s;
+        p = cs->credp[buf][0][lane];
+        q = cs->credq[buf][0][lane];
+        for (uint32_t r = 1; r < ncta; ++r) {
+            p += cs->credp[buf][r][lane];
+            q += cs->credq[buf][r][lane];
+        }
     }
 };
 
@@ -276,6 +320,189 @@ template <int RW, bool Keep>
 __device__ __forceinline__ void factor_cols(pair_t (&x2)[RW / 2], Smem& s, float* pub, float* keep, float& my_sc,
                                             int nw = kWarps) {
     factor_cols<RW, Keep>(x2, s, pub, keep, my_sc, BlockSync{nw});
+}
+
+// One step of a warp that holds ordinary rows (the body of factor_cols' loop for such warps, without Keep).
+template <int RW, typename Sync>
+__device__ __forceinline__ void step_other(pair_t (&x2)[RW / 2], Smem& s, ulonglong2* pj, int j, int lane, int warp,
+                                           const Sync& sync, float& my_sc) {
+    constexpr int NQ = RW / 4;
+    const int buf = j & 1;
+    if (lane == j) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) pj[q] = make_ulonglong2(x2[2 * q], x2[2 * q + 1]);
+    }
+    __syncwarp();
+    ulonglong2 u[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) u[q] = pj[q];
+    {
+        pair_t s2 = mul2(u[0].x, x2[0]), s2b = mul2(u[0].y, x2[1]);
+#pragma unroll
+        for (int q = 1; q < NQ; ++q) {
+            s2  = fma2(u[q].x, x2[2 * q], s2);
+            s2b = fma2(u[q].y, x2[2 * q + 1], s2b);
+        }
+        s.red[buf][warp][lane] = hsum2(s2, s2b);
+    }
+    sync.exchange(s, buf, lane, warp);
+    float v1, alpha;
+    const float  t  = step_reflector(s, j, buf, lane, warp, sync, my_sc, v1, alpha);
+    const pair_t t2 = pack(t, t);
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        x2[2 * q]     = fma2(t2, u[q].x, x2[2 * q]);
+        x2[2 * q + 1] = fma2(t2, u[q].y, x2[2 * q + 1]);
+    }
+}
+
+// The same factorisation with TWO columns a reduction. Before the pair of steps (j, j + 1), lanes j and
+// j + 1 publish their columns below the two pivot rows, every lane takes both products with its own
+// column, and ONE exchange returns, per column k, p_k = a_j^T a_k and q_k = a_(j+1)^T a_k over the rows
+// below the pair; the pivot rows j and j + 1 of every column go round with it. Step j is then what it always
+// was. Step j + 1 acts on columns already changed by step j, a'_k = a_k + t_k u_j, and what it needs of
+// them follows from the same sums: below the pair a'_(j+1)^T a'_k = q_k + t_k p_(j+1) + t_(j+1) p_k +
+// t_(j+1) t_k p_j. Both reflectors are applied as one rank-2 update with the two published columns,
+// a_k += (t_k + t'_k t_(j+1)) a_j + t'_k a_(j+1). A panel is a chain of exchanges (a barrier, or a
+// cluster barrier, and the trips through shared memory around it); this halves the chain.
+//
+// The second column's norm comes out of that formula as a difference, q - (what step j removed): where
+// step j removes nearly all of column j + 1 (the two columns nearly parallel below the diagonal) the
+// difference loses digits, and the reflector built on it would not be orthogonal to rounding. So the pair
+// is taken only where the updated norm keeps at least kPairKeep of the old one; otherwise step j is
+// applied alone and step j + 1 runs as an ordinary step with an exchange of its own. Every thread decides
+// alike: all of them hold the same sums.
+constexpr float kPairKeep = 1.0f / 16.0f;
+
+template <int RW, typename Sync>
+__device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, float* pub, float& my_sc, const Sync& sync) {
+    constexpr int NQ = RW / 4, NP = RW / 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool piv = sync.pivot(warp);
+    const bool lead = sync.leader(warp);
+    ulonglong2* pA = reinterpret_cast<ulonglong2*>(pub) + (size_t)warp * 2 * NQ;      // this warp's pieces of columns j and j + 1
+    ulonglong2* pB = pA + NQ;
+    const pair_t zero2 = pack(0.0f, 0.0f);
+    my_sc = 0.0f;
+#pragma unroll 1
+    for (int it = 0; it < 16; ++it) {
+        const int j = 2 * it, buf = it & 1;
+        // 1. columns j and j + 1 below the pivot pair (the pivot warp's pair 0 holds rows j and j + 1 themselves)
+        if (lane == j || lane == j + 1) {
+            ulonglong2* dst = lane == j ? pA : pB;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) dst[q] = make_ulonglong2((piv && q == 0) ? zero2 : x2[2 * q], x2[2 * q + 1]);
+        }
+        __syncwarp();
+        // 2. both products with this lane's column
+        {
+            pair_t sa = zero2, sa2 = zero2, sb = zero2, sb2 = zero2;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const ulonglong2 ua = pA[q], ub = pB[q];
+                sa  = fma2(ua.x, x2[2 * q], sa);
+                sa2 = fma2(ua.y, x2[2 * q + 1], sa2);
+                sb  = fma2(ub.x, x2[2 * q], sb);
+                sb2 = fma2(ub.y, x2[2 * q + 1], sb2);
+            }
+            s.redp[buf][warp][lane] = hsum2(sa, sa2);
+            s.redq[buf][warp][lane] = hsum2(sb, sb2);
+        }
+        if (piv) {
+            s.prow0[buf][lane] = lo_of(x2[0]);
+            s.prow1[buf][lane] = hi_of(x2[0]);
+        }
+        sync.exchange2(s, buf, lane, warp);
+        float p, q;
+        sync.total2(s, buf, lane, p, q);
+        // 3. step j, and what step j + 1 will see
+        const float r0 = s.prow0[buf][lane], r1 = s.prow1[buf][lane];              // rows j and j + 1 of this lane's column
+        const float alpha = s.prow0[buf][j], e = s.prow1[buf][j];                  // column j's
+        const float f0 = s.prow0[buf][j + 1], f1 = s.prow1[buf][j + 1];            // column j + 1's
+        const float pj = __shfl_sync(0xffffffffu, p, j), pj1 = __shfl_sync(0xffffffffu, p, j + 1);
+        const float qj1 = __shfl_sync(0xffffffffu, q, j + 1);
+        float v1, gneg;
+        fast_reflector(alpha, fmaf(e, e, pj), v1, gneg);
+        const float sv  = fmaf(v1, r0, fmaf(e, r1, p));                            // u_j^T (this lane's column)
+        const float tk  = lane > j ? sv * gneg : 0.0f;
+        const float tj1 = fmaf(v1, f0, fmaf(e, f1, pj1)) * gneg;                   // column j + 1's coefficient, in every lane
+        const float scj = gneg != 0.0f ? recip(v1) : 0.0f;
+        if (lead) {
+            if (lane < j) s.G[lane][j] = sv * my_sc * scj;
+            if (lane == 0) {
+                s.taus[j] = -gneg * v1 * v1;
+                s.sc[j]   = scj;
+            }
+        }
+        if (lane == j) my_sc = scj;
+        const float m1 = fmaf(tk, e, r1);                                          // row j + 1 of this column after step j
+        const float rj = lane > j ? fmaf(tk, v1, r0) : (lane == j ? alpha - v1 : r0);      // row j: final
+        const float alpha1 = fmaf(tj1, e, f1);
+        const float ss1 = fmaf(tj1, fmaf(tj1, pj, 2.0f * pj1), qj1);               // column j + 1's norm below the pair, after step j
+        if (!(ss1 < kPairKeep * qj1)) {
+            // 4a. step j + 1 from the same sums, and both reflectors in one update
+            float v1b, gnegb;
+            fast_reflector(alpha1, ss1, v1b, gnegb);
+            const float s1  = fmaf(tj1 * tk, pj, fmaf(tj1, p, fmaf(tk, pj1, q)));  // a'_(j+1)^T a'_k below the pair
+            const float sv1 = fmaf(v1b, m1, s1);
+            const float t1  = lane > j + 1 ? sv1 * gnegb : 0.0f;
+            const float scj1 = gnegb != 0.0f ? recip(v1b) : 0.0f;
+            if (lead) {
+                if (lane < j + 1) s.G[lane][j + 1] = sv1 * my_sc * scj1;
+                if (lane == 0) {
+                    s.taus[j + 1] = -gnegb * v1b * v1b;
+                    s.sc[j + 1]   = scj1;
+                }
+            }
+            if (lane == j + 1) my_sc = scj1;
+            const float ca = fmaf(t1, tj1, tk);
+            const pair_t a2 = pack(ca, ca), b2 = pack(t1, t1);
+            if (piv) {
+                const float rj1 = lane > j + 1 ? fmaf(t1, v1b, m1) : (lane == j + 1 ? alpha1 - v1b : m1);
+                s.rows[j][lane]     = rj;
+                s.rows[j + 1][lane] = rj1;
+                // the pairs move up one place as the two finished rows leave
+#pragma unroll
+                for (int i = 1; i < 16; ++i) {
+                    const ulonglong2 ua = pA[i / 2], ub = pB[i / 2];
+                    x2[i - 1] = fma2(a2, (i & 1) ? ua.y : ua.x, fma2(b2, (i & 1) ? ub.y : ub.x, x2[i]));
+                }
+                x2[15] = zero2;
+#pragma unroll
+                for (int i = 16; i < NP; ++i) {
+                    const ulonglong2 ua = pA[i / 2], ub = pB[i / 2];
+                    x2[i] = fma2(a2, (i & 1) ? ua.y : ua.x, fma2(b2, (i & 1) ? ub.y : ub.x, x2[i]));
+                }
+            } else {
+#pragma unroll
+                for (int qq = 0; qq < NQ; ++qq) {
+                    const ulonglong2 ua = pA[qq], ub = pB[qq];
+                    x2[2 * qq]     = fma2(a2, ua.x, fma2(b2, ub.x, x2[2 * qq]));
+                    x2[2 * qq + 1] = fma2(a2, ua.y, fma2(b2, ub.y, x2[2 * qq + 1]));
+                }
+            }
+        } else {
+            // 4b. step j alone; step j + 1 as an ordinary step with its own exchange
+            const pair_t a2 = pack(tk, tk);
+            if (piv) {
+#pragma unroll
+                for (int i = 1; i < NP; ++i) {
+                    const ulonglong2 ua = pA[i / 2];
+                    x2[i] = fma2(a2, (i & 1) ? ua.y : ua.x, x2[i]);
+                }
+                x2[0] = pack(rj, m1);          // row j finished (it leaves with row j + 1), row j + 1 the next pivot row
+                step_warp0<RW, 1>(x2, s, pA, it, lane, sync, my_sc);
+            } else {
+#pragma unroll
+                for (int qq = 0; qq < NQ; ++qq) {
+                    const ulonglong2 ua = pA[qq];
+                    x2[2 * qq]     = fma2(a2, ua.x, x2[2 * qq]);
+                    x2[2 * qq + 1] = fma2(a2, ua.y, x2[2 * qq + 1]);
+                }
+                step_other<RW>(x2, s, pA, j + 1, lane, warp, sync, my_sc);
+            }
+        }
+    }
 }
 
 // T from s.G and s.taus (slarft's forward recurrence) by one warp, a row of T per lane, to

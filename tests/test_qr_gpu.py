@@ -196,14 +196,17 @@ def test_blocked_kernel_shapes(shape, mode):
 
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
-                                    "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0"])
+                                    "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
+                                    "QR_PANEL_CLUSTER=16"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
     backward instead of forward, panels with a row per thread instead of a column per lane, ordinary
     launches instead of programmatic dependent ones (QR_NO_PDL is read once per process: it takes
     effect only when set before the first call), panels by the tree of row blocks instead of one
-    cluster launch, tensor-core products that split their operands in every block instead of once."""
+    cluster launch, tensor-core products that split their operands in every block instead of once,
+    panel steps a column a reduction instead of two, the update inside the aggregate in two launches
+    instead of one cluster launch, panel clusters of sixteen blocks."""
     rng = np.random.default_rng(16)
     a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
@@ -234,10 +237,17 @@ def test_mid_panel_paths(shape):
         q1, r1 = gpu_qr(a, "reduced", kernel="mid")
     finally:
         os.environ.pop("QR_MID_ROWS", None)
+    os.environ["QR_PANEL_PAIRS"] = "0"      # a column a reduction instead of two
+    try:
+        q2, r2 = gpu_qr(a, "reduced", kernel="mid")
+    finally:
+        os.environ.pop("QR_PANEL_PAIRS", None)
     check(a, q0, r0, "reduced")
     check(a, q1, r1, "reduced")
+    check(a, q2, r2, "reduced")
     good = [0, 1, 2, 4]
     assert harness.r_parity(r0[good], r1[good]) <= 1e-4
+    assert harness.r_parity(r0[good], r2[good]) <= 1e-4
     _, r_ref = harness.oracle_qr(a[good])
     assert harness.r_parity(r0[good], r_ref) <= 1e-4
 
@@ -853,3 +863,28 @@ def test_wide_by_leading_block(shape, mode):
     finally:
         os.environ.pop("QR_WIDE", None)
     assert harness.r_parity(r[good], r0[good]) <= 1e-5
+
+
+@pytest.mark.parametrize("kernel,shape", [("mid", (300, 96)), ("mid", (256, 64)), ("blocked", (1500, 160)), ("blocked", (3000, 64))])
+def test_panel_pairs_with_nearly_parallel_columns(kernel, shape):
+    """Panels take two columns a reduction and form the second reflector from sums taken before the first was
+    applied; where a column is nearly parallel to the one before it that formula would lose digits, and the
+    pair falls back to two ordinary steps. Columns that repeat, or differ by 1e-3 ... 1e-7, or vanish, exercise
+    both sides of that decision: orthogonality, reconstruction and R against the oracle must hold as everywhere."""
+    m, n = shape
+    rng = np.random.default_rng(m * 3 + n)
+    base = rng.standard_normal((m, n)).astype(np.float64)
+    mats = []
+    for eps in (0.0, 1e-7, 1e-5, 1e-3, 0.3):
+        x = base.copy()
+        x[:, 1::2] = x[:, 0::2][:, : x[:, 1::2].shape[1]] + eps * rng.standard_normal(x[:, 1::2].shape)   # odd columns ~ the even ones
+        mats.append(x)
+    x = base.copy()
+    x[:, 5:9] = 0.0                                  # zero columns: identity reflectors inside pairs
+    mats.append(x)
+    a = np.stack(mats).astype(np.float32)
+    q, r = gpu_qr(a, "reduced", kernel=kernel)
+    check(a, q, r, "reduced")
+    _, r_ref = harness.oracle_qr(a[[3, 4]])
+    assert harness.r_parity(r[[4]], r_ref[[1]]) <= 1e-4          # well conditioned: the usual bound
+    assert harness.r_parity(r[[3]], r_ref[[0]]) <= 2e-3          # column pairs 1e-3 apart: R is determined to about 1e3 eps
