@@ -707,12 +707,15 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     // a column per lane up to 8192 rows; a row per thread beyond, and for both with QR_PANEL_ROWS=1
     const char* env = std::getenv("QR_PANEL_ROWS");
     const bool by_columns = rpt <= 2 && !(env && env[0] == '1');
-    // up to 4096 rows the whole panel in one cluster launch (QR_PANEL_CLUSTER=0: the tree of row blocks)
+    // up to 8192 rows the whole panel in one cluster launch (QR_PANEL_CLUSTER=0: the tree of row blocks)
     const char* envc = std::getenv("QR_PANEL_CLUSTER");
-    if (by_columns && mp <= 4096 && !(envc && envc[0] == '0')) {
+    // panels of 4097 to 8192 rows: a cluster of sixteen blocks of 512 rows (the non-portable size). With two columns a
+    // reduction it beats the tree of row blocks there (8192 x 8192: 35.3 -> 32.6 ms); QR_PANEL_CLUSTER=4096 keeps the tree
+    const bool tall_cluster = !(envc && envc[0] == '4');
+    if (by_columns && (mp <= 4096 || (tall_cluster && mp <= 8192)) && !(envc && envc[0] == '0')) {
         // beyond 2048 rows: 8 blocks of 512 rows (64 rows a lane), or with QR_PANEL_CLUSTER=16 sixteen blocks of
         // 256 rows (32 rows a lane: half the arithmetic a step, a cluster of the non-portable size)
-        const bool sixteen = mp > 2048 && envc && envc[0] == '1' && envc[1] == '6';
+        const bool sixteen = mp > 2048 && mp <= 4096 && envc && envc[0] == '1' && envc[1] == '6';
         const uint32_t rw = (mp <= 2048 || sixteen) ? 32 : 64;
         uint32_t ncta = 1;
         while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4, 8 (or 16) blocks; blocks beyond the rows hold zeros
@@ -720,6 +723,8 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
             static PerDeviceOnce once;
             if (const int device = current_device(); once.first(device)) {
                 cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                           "panel_cluster non-portable cluster size");
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
                            "panel_cluster non-portable cluster size");
                 once.mark(device);
             }
