@@ -65,6 +65,12 @@ void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p)
 size_t tsqr_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, bool want_q);
 void   tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m,
                  uint32_t n, uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws);
+// The tree with the row blocks kept as reflectors (qr_tsqr_vt.cu), which tsqr_core and tsqr_workspace_floats
+// hand over to where tsqr_vt_takes() says so (at most 64 columns; QR_TSQR_VT=0 keeps the older scheme).
+bool   tsqr_vt_takes(uint32_t m, uint32_t n);
+size_t tsqr_vt_workspace_floats(uint32_t m, uint32_t n, uint32_t batch, bool want_q);
+void   tsqr_vt_core(cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m, uint32_t n,
+                    uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws);
 // out_block = q_block * factor for row blocks of n columns (see qr_tsqr.cu).
 void   launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q, uint64_t q_outer, uint64_t q_stride,
                          float* out, uint64_t out_outer, uint64_t out_stride, uint64_t out_ld, const float* up,

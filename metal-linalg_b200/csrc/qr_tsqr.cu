@@ -229,6 +229,7 @@ Layout layout(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, 
 } // namespace
 
 size_t tsqr_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch, bool want_q) {
+    if (tsqr_vt_takes(m, n)) return tsqr_vt_workspace_floats(m, n, batch, want_q);
     return layout(ctx, m, n, batch, want_q).total;
 }
 
@@ -237,6 +238,10 @@ size_t tsqr_workspace_floats(const DeviceContext& ctx, uint32_t m, uint32_t n, u
 void tsqr_core(DeviceContext& ctx, cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m,
                uint32_t n, uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws) {
     if (batch == 0) return;
+    if (tsqr_vt_takes(m, n)) {      // at most 64 columns: the blocks kept as reflectors, Q built once on the way down
+        tsqr_vt_core(stream, a, lda, a_outer, m, n, batch, q, r, r_outer, ws);
+        return;
+    }
     const bool want_q = q != nullptr;
     const Layout L = layout(ctx, m, n, batch, want_q);
     const size_t nl = L.levels.size();
