@@ -61,7 +61,7 @@ __host__ __device__ inline void block_span(unsigned i, unsigned blocks, unsigned
 template <int SETS>
 struct LeafSmem {
     static constexpr int NC = 32 * SETS;
-    float red[2][2 * SETS][kWarps][32];     // by pair parity: each warp's partial products (p, q of its set; p, q of the other)
+    float red[2][kWarps][32][2 * SETS];     // by pair parity: each warp's partial products per lane (p, q of its set; p, q of the other), one word
     float red1[SETS][kWarps][32];           // the same for a column stepped alone
     float prow[2][2][NC];                   // by pair parity: the two pivot rows of every column
     float prow1[NC];
@@ -87,13 +87,14 @@ struct LeafParams {
 
 #define MLB_SEL(u, i) (((i) & 1) ? (u).y : (u).x)
 
-// The 16 pair steps of panel P (columns 32 P ...): xa its own columns' registers, xo the other half's.
-template <int SETS, int P>
-__device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], LeafSmem<SETS>& s, float& my_sc, float& my_sco,
+// piv: this warp holds the panel's pivot rows. The pivot warp and the others run separate copies of the loop (fewer
+// values live in each, no branches on the warp's role) and meet at a named barrier.
+template <int SETS, int P, bool piv>
+__device__ __forceinline__ void leaf_steps(pair_t (&xa)[16], pair_t (&xo)[16], LeafSmem<SETS>& s, float& my_sc, float& my_sco,
                                            const int lane, const int warp) {
     constexpr bool kOth = SETS == 2, kRight = SETS == 2 && P == 0, kLeft = SETS == 2 && P == 1;
     constexpr int  cb = 32 * P, co = kOth ? 32 * (1 - P) : 0;
-    const bool piv = warp == P, lead = warp == kWarps - 1;
+    const bool lead = warp == kWarps - 1;
     ulonglong2* pA = reinterpret_cast<ulonglong2*>(s.pub[warp][0]);
     ulonglong2* pB = reinterpret_cast<ulonglong2*>(s.pub[warp][1]);
     const pair_t zero2 = pack(0.0f, 0.0f);
@@ -126,11 +127,11 @@ __device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], L
                     ob2 = fma2(ub.y, xo[2 * q + 1], ob2);
                 }
             }
-            s.red[buf][0][warp][lane] = hsum2(sa, sa2);
-            s.red[buf][1][warp][lane] = hsum2(sb, sb2);
             if (kOth) {
-                s.red[buf][2 * SETS - 2][warp][lane] = hsum2(oa, oa2);
-                s.red[buf][2 * SETS - 1][warp][lane] = hsum2(ob, ob2);
+                *reinterpret_cast<float4*>(s.red[buf][warp][lane]) =
+                    make_float4(hsum2(sa, sa2), hsum2(sb, sb2), hsum2(oa, oa2), hsum2(ob, ob2));
+            } else {
+                *reinterpret_cast<float2*>(s.red[buf][warp][lane]) = make_float2(hsum2(sa, sa2), hsum2(sb, sb2));
             }
         }
         if (piv) {
@@ -141,15 +142,16 @@ __device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], L
                 s.prow[buf][1][co + lane] = hi_of(xo[0]);
             }
         }
-        __syncthreads();
+        cols::step_barrier(kThreads);
         float p = 0.0f, q = 0.0f, po = 0.0f, qo = 0.0f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-            p += s.red[buf][0][w][lane];
-            q += s.red[buf][1][w][lane];
             if (kOth) {
-                po += s.red[buf][2 * SETS - 2][w][lane];
-                qo += s.red[buf][2 * SETS - 1][w][lane];
+                const float4 v = *reinterpret_cast<const float4*>(s.red[buf][w][lane]);
+                p += v.x; q += v.y; po += v.z; qo += v.w;
+            } else {
+                const float2 v = *reinterpret_cast<const float2*>(s.red[buf][w][lane]);
+                p += v.x; q += v.y;
             }
         }
         // 3. step J, and what step J + 1 will see
@@ -275,7 +277,7 @@ __device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], L
                 s.prow1[cb + lane] = hi_of(xa[0]);
                 if (kOth) s.prow1[co + lane] = hi_of(xo[0]);
             }
-            __syncthreads();
+            cols::step_barrier(kThreads);
             float dd = 0.0f, ddo = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
@@ -332,6 +334,14 @@ __device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], L
             }
         }
     }
+}
+
+// The 16 pair steps of panel P (columns 32 P ...): xa its own columns' registers, xo the other half's.
+template <int SETS, int P>
+__device__ __forceinline__ void leaf_panel(pair_t (&xa)[16], pair_t (&xo)[16], LeafSmem<SETS>& s, float& my_sc, float& my_sco,
+                                           const int lane, const int warp) {
+    if (warp == P) leaf_steps<SETS, P, true>(xa, xo, s, my_sc, my_sco, lane, warp);
+    else leaf_steps<SETS, P, false>(xa, xo, s, my_sc, my_sco, lane, warp);
 }
 
 // T of the 32 reflectors from column `off` on (slarft's forward recurrence), by one warp, a row of T per lane.
@@ -448,29 +458,31 @@ __global__ void __launch_bounds__(kThreads, SETS == 2 ? 2 : 3) tsqr_leaf_kernel(
     }
     __syncthreads();      // s.top, s.G, s.taus and s.sc are complete
 
-    // R (scaled back) and the first rows of V from s.top
-    {
+    // T's diagonal blocks by one warp each; meanwhile the other warps write R (scaled back) and the first rows of V from s.top
+    if (T && warp < SETS) {
+        leaf_build_t<SETS>(s, 32 * warp, lane);
+    } else {
+        const int t0 = T ? t - 32 * SETS : t, nt = T ? kThreads - 32 * SETS : kThreads;
         const Pow2 up(expo);
-        for (int idx = t; idx < n * n; idx += kThreads) {
+        for (int idx = t0; idx < n * n; idx += nt) {
             const int r = idx / n, c = idx % n;
             R[idx] = r <= c ? up(s.top[r][c]) : 0.0f;
         }
         if (V) {
             const int vr = min((unsigned)NC, nrows);
-            for (int idx = t; idx < vr * n; idx += kThreads) {
+            for (int idx = t0; idx < vr * n; idx += nt) {
                 const int r = idx / n, c = idx % n;
                 V[idx] = r > c ? s.top[r][c] * s.sc[c] : (r == c ? 1.0f : 0.0f);
             }
         }
     }
     if (!T) return;
-
-    // T: the diagonal blocks by one warp each, then T12 = -T11 (V1^T V2) T22 by everyone
-    if (warp < SETS) leaf_build_t<SETS>(s, 32 * warp, lane);
     __syncthreads();
+    // T12 = -T11 (V1^T V2) T22 by everyone
     if (SETS == 2) {
         const int r = t >> 3, c0 = 4 * (t & 7);
         float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 8
         for (int k = 0; k < 32; ++k) {          // X = G12 T22 (T22 upper triangular)
             const float g = s.G[r][32 + k];
 #pragma unroll
@@ -480,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, SETS == 2 ? 2 : 3) tsqr_leaf_kernel(
         for (int e = 0; e < 4; ++e) s.X[r][c0 + e] = x[e];
         __syncthreads();
         float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 8
         for (int k = 0; k < 32; ++k) {          // T12 = -T11 X
             const float tv = s.T[r][k];
 #pragma unroll
@@ -501,7 +514,7 @@ __global__ void __launch_bounds__(kThreads, SETS == 2 ? 2 : 3) tsqr_leaf_kernel(
 // ---------------------------------------------------------------------------------------------
 // The way down: Q_block = [B; 0] - V (T (V1^T B)), in place over V.
 
-constexpr int LD = 68;          // leading dimension of the 64 x 64 blocks in shared memory (16-byte rows, 4 banks apart)
+constexpr int LD = 68;          // leading dimension of the blocks in shared memory (16-byte rows, 4 banks apart)
 
 struct DownParams {
     float*       v;             // V in, Q out (rows of n floats): matrix b at v + b * v_outer
@@ -543,6 +556,30 @@ __device__ __forceinline__ void mm64(const float* A, const float* B, pair_t (&ac
     }
 }
 
+// The same for 128 rows of A at once: a thread holds rows 4 rg + a and 64 + 4 rg + a (a < 4), so that a word of B
+// read from shared memory serves eight rows (the shared-memory pipe, not the FMA pipe, is what bounds these loops).
+__device__ __forceinline__ void mm128(const float* A, const float* B, pair_t (&acc)[8][2], int rg, int cg) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a) acc[a][0] = acc[a][1] = pack(0.0f, 0.0f);
+#pragma unroll 2
+    for (int k0 = 0; k0 < 64; k0 += 4) {
+        float4 x[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) x[a] = *reinterpret_cast<const float4*>(A + ((a >> 2) * 64 + 4 * rg + (a & 3)) * LD + k0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(B + (k0 + kk) * LD + 4 * cg);
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                const float xv = kk == 0 ? x[a].x : kk == 1 ? x[a].y : kk == 2 ? x[a].z : x[a].w;
+                const pair_t xx = pack(xv, xv);
+                acc[a][0] = fma2(xx, w.x, acc[a][0]);
+                acc[a][1] = fma2(xx, w.y, acc[a][1]);
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void store_acc(float* dst, const pair_t (&acc)[4][2], int rg, int cg) {
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
@@ -553,23 +590,24 @@ __device__ __forceinline__ void store_acc(float* dst, const pair_t (&acc)[4][2],
     }
 }
 
-// n x n (row-major, contiguous) into a 64 x 64 block, zeros beyond n
-__device__ __forceinline__ void load_square(float* dst, const float* src, int n, int t) {
-    if ((n & 3) == 0 && (reinterpret_cast<size_t>(src) & 15) == 0) {
-        const int nq = n >> 2;
-        for (int idx = t; idx < 64 * 16; idx += kThreads) {
-            const int r = idx >> 4, q = idx & 15;
-            const float4 v = (r < n && q < nq) ? *reinterpret_cast<const float4*>(src + (size_t)r * n + 4 * q)
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4*>(dst + r * LD + 4 * q) = v;
-        }
-    } else {
-        for (int idx = t; idx < 64 * 64; idx += kThreads) {
-            const int r = idx >> 6, c = idx & 63;
-            dst[r * LD + c] = (r < n && c < n) ? src[(size_t)r * n + c] : 0.0f;
+// Four floats of row-major `src` (rows of n floats) at (r, 4 q), zeros outside rows < nr and columns < n
+__device__ __forceinline__ float4 fetch4(const float* src, int n, unsigned nr, unsigned r, int q, bool vec) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nr) {
+        const float* s = src + (size_t)r * n + 4 * q;
+        if (vec) {
+            if (4 * q < n) v = *reinterpret_cast<const float4*>(s);
+        } else {
+            if (4 * q < n) v.x = s[0];
+            if (4 * q + 1 < n) v.y = s[1];
+            if (4 * q + 2 < n) v.z = s[2];
+            if (4 * q + 3 < n) v.w = s[3];
         }
     }
+    return v;
 }
+
+constexpr int kDownSmem = (4 * 64 + 128) * LD * (int)sizeof(float);
 
 __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams p) {
     extern __shared__ __align__(16) float down_sm[];
@@ -577,7 +615,7 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
     float* Ts = Bs + 64 * LD;
     float* Xs = Ts + 64 * LD;            // V1^T B
     float* Ws = Xs + 64 * LD;            // T (V1^T B)
-    float* Vs = Ws + 64 * LD;            // 64 rows of V
+    float* Vs = Ws + 64 * LD;            // 128 rows of V
     const int t = threadIdx.x, rg = t >> 4, cg = t & 15;
     const int n = p.n;
     const unsigned i = blockIdx.x % p.blocks;
@@ -586,58 +624,74 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
     block_span(i, p.blocks, p.rows, p.d, start, nrows);
     float* V = p.v + b * p.v_outer + (size_t)start * n;
     const size_t blk = (size_t)b * p.blocks + i;
-    const bool vec = (n & 3) == 0 && (reinterpret_cast<size_t>(V) & 15) == 0;
+    const float* Bsrc = p.up ? p.up + blk * n * n : nullptr;
+    const float* Tsrc = p.t + blk * n * n;
+    const bool n4 = (n & 3) == 0;
+    const bool vec = n4 && (reinterpret_cast<size_t>(V) & 15) == 0;
+    const bool vecb = n4 && (reinterpret_cast<size_t>(Bsrc) & 15) == 0, vect = n4 && (reinterpret_cast<size_t>(Tsrc) & 15) == 0;
 
-    auto load_rows = [&](unsigned r0) {       // rows r0 ... r0 + 63 of V, zeros beyond the block and beyond n
-        if (vec) {
-            const int nq = n >> 2;
-            for (int idx = t; idx < 64 * 16; idx += kThreads) {
-                const int r = idx >> 4, q = idx & 15;
-                const float4 v = (r0 + r < nrows && q < nq) ? *reinterpret_cast<const float4*>(V + (size_t)(r0 + r) * n + 4 * q)
-                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4*>(Vs + r * LD + 4 * q) = v;
+    {   // B, T and the first 128 rows of V: every load in flight before the first store
+        float4 fb[4], ft[4], fv[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+            if (Bsrc) {
+                fb[k] = fetch4(Bsrc, n, (unsigned)n, (unsigned)r, q, vecb);
+            } else {
+                const int d = r - 4 * q;
+                fb[k] = make_float4(d == 0 && r < n ? 1.f : 0.f, d == 1 && r < n ? 1.f : 0.f, d == 2 && r < n ? 1.f : 0.f,
+                                    d == 3 && r < n ? 1.f : 0.f);
             }
-        } else {
-            for (int idx = t; idx < 64 * 64; idx += kThreads) {
-                const int r = idx >> 6, c = idx & 63;
-                Vs[r * LD + c] = (r0 + r < nrows && c < n) ? V[(size_t)(r0 + r) * n + c] : 0.0f;
-            }
+            ft[k] = fetch4(Tsrc, n, (unsigned)n, (unsigned)r, q, vect);
         }
-    };
-
-    if (p.up) {
-        load_square(Bs, p.up + blk * n * n, n, t);
-    } else {
-        for (int idx = t; idx < 64 * 64; idx += kThreads) {
-            const int r = idx >> 6, c = idx & 63;
-            Bs[r * LD + c] = (r == c && r < n) ? 1.0f : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+            fv[k] = fetch4(V, n, nrows, (unsigned)r, q, vec);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+            *reinterpret_cast<float4*>(Bs + r * LD + 4 * q) = fb[k];
+            *reinterpret_cast<float4*>(Ts + r * LD + 4 * q) = ft[k];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+            *reinterpret_cast<float4*>(Vs + r * LD + 4 * q) = fv[k];
         }
     }
-    load_square(Ts, p.t + blk * n * n, n, t);
-    load_rows(0);
     __syncthreads();
-    pair_t acc[4][2];
-    mm64<true>(Vs, Bs, acc, rg, cg);          // rows of B beyond n are zero, so only V1 = V's first n rows count
-    store_acc(Xs, acc, rg, cg);
+    {
+        pair_t acc[4][2];
+        mm64<true>(Vs, Bs, acc, rg, cg);          // rows of B beyond n are zero, so only V1 = V's first n rows count
+        store_acc(Xs, acc, rg, cg);
+        __syncthreads();
+        mm64<false>(Ts, Xs, acc, rg, cg);
+        store_acc(Ws, acc, rg, cg);
+    }
     __syncthreads();
-    mm64<false>(Ts, Xs, acc, rg, cg);
-    store_acc(Ws, acc, rg, cg);
-    __syncthreads();
-    for (unsigned r0 = 0; r0 < nrows; r0 += 64) {
-        if (r0 != 0) {
-            load_rows(r0);
-            __syncthreads();
-        }
-        mm64<false>(Vs, Ws, acc, rg, cg);
+    for (unsigned r0 = 0; r0 < nrows; r0 += 128) {
+        const bool more = r0 + 128 < nrows;
+        float4 fn[8];       // the next 128 rows, fetched under this product
+        if (more) {
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            const unsigned r = r0 + 4 * rg + a;
+            for (int k = 0; k < 8; ++k) {
+                const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+                fn[k] = fetch4(V, n, nrows, r0 + 128 + (unsigned)r, q, vec);
+            }
+        }
+        pair_t acc[8][2];
+        mm128(Vs, Ws, acc, rg, cg);
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const unsigned r = r0 + (a >> 2) * 64 + 4 * rg + (a & 3);
             if (r >= nrows) continue;
             float o[4];
             unpack(acc[a][0], o[0], o[1]);
             unpack(acc[a][1], o[2], o[3]);
             const int c = 4 * cg;
-            if (r0 == 0) {
+            if (r0 == 0 && a < 4) {
                 const float4 bv = *reinterpret_cast<const float4*>(Bs + (4 * rg + a) * LD + c);
                 o[0] = bv.x - o[0]; o[1] = bv.y - o[1]; o[2] = bv.z - o[2]; o[3] = bv.w - o[3];
             } else {
@@ -652,7 +706,15 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
                     if (c + e < n) dst[e] = o[e];
             }
         }
-        __syncthreads();      // the rows have been read: the next ones may overwrite them
+        if (more) {
+            __syncthreads();      // the rows have been read: the next ones may overwrite them
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
+                *reinterpret_cast<float4*>(Vs + r * LD + 4 * q) = fn[k];
+            }
+            __syncthreads();
+        }
     }
 }
 
@@ -746,9 +808,8 @@ void tsqr_vt_core(cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_
     }
     if (!want_q) return;
     static PerDeviceOnce once;
-    constexpr int down_smem = 5 * 64 * LD * (int)sizeof(float);
     if (const int device = current_device(); once.first(device)) {
-        cuda_check(cudaFuncSetAttribute(tsqr_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, down_smem),
+        cuda_check(cudaFuncSetAttribute(tsqr_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDownSmem),
                    "tsqr_down shared memory");
         once.mark(device);
     }
@@ -761,7 +822,7 @@ void tsqr_vt_core(cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_
         dp.up = l + 1 == nl ? nullptr : ws + L.q_off[l + 1];
         dp.rows = lv.rows; dp.blocks = lv.blocks; dp.d = lv.d;
         dp.n = (int)n;
-        tsqr_down_kernel<<<(unsigned)((uint64_t)batch * lv.blocks), kThreads, down_smem, stream>>>(dp);
+        tsqr_down_kernel<<<(unsigned)((uint64_t)batch * lv.blocks), kThreads, kDownSmem, stream>>>(dp);
         cuda_check(cudaGetLastError(), "tsqr_down launch");
     }
 }
