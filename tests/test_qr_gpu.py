@@ -157,6 +157,50 @@ def test_tsqr_shapes(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
+@pytest.mark.parametrize("mode", ["reduced", "r"])
+@pytest.mark.parametrize("shape", [(513, 64), (520, 64), (1030, 64), (2050, 40), (2700, 48), (769, 3)])
+def test_tsqr_short_last_blocks(shape, mode):
+    """Row counts that leave a last block shorter than the matrix is wide, at the first level ((1030, 64): six rows
+    over four blocks) and at the second ((2700, 48): eleven 48-row factors make 528 rows): the block before it
+    gives up rows, so no block has fewer rows than columns."""
+    m, n = shape
+    rng = np.random.default_rng(3 * m + n)
+    a = rng.standard_normal((3, m, n)).astype(np.float32)
+    q, r = gpu_qr(a, mode, kernel="tsqr")
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
+@pytest.mark.parametrize("shape", [(512, 64), (5000, 33), (4096, 16)])
+def test_tsqr_older_scheme_behind_its_switch(shape):
+    """QR_TSQR_VT=0: blocks through the general block kernel with an explicit Q at every block (the scheme that
+    stays for 65 to 128 columns), with the same results."""
+    m, n = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((2, m, n)).astype(np.float32)
+    os.environ["QR_TSQR_VT"] = "0"
+    try:
+        q, r = gpu_qr(a, "reduced", kernel="tsqr")
+    finally:
+        os.environ.pop("QR_TSQR_VT", None)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
+
+
+def test_tsqr_nearly_parallel_neighbours():
+    """Column pairs that are nearly parallel below the diagonal make the two-column step fall back to two
+    single steps (qr_tsqr_vt.cu, the same rule as qr_panel_cols.cuh); both sides of the rule in one matrix."""
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((4, 2048, 64)).astype(np.float32)
+    a[:, :, 1] = a[:, :, 0] * 1.5 + 1e-2 * a[:, :, 1]          # pair (0, 1) of the first panel
+    a[:, :, 41] = a[:, :, 40] - 1e-2 * a[:, :, 41]             # pair (40, 41) of the second
+    a[:, :, 63] = a[:, :, 62] + 3e-2 * a[:, :, 63]
+    q, r = gpu_qr(a, "reduced", kernel="tsqr")
+    check(a, q, r, "reduced")
+    _, r_ref = harness.oracle_qr(a)
+    assert harness.r_parity(r, r_ref) <= 2e-3                  # columns 1e-2 apart: R's small entries carry the conditioning
+
+
 def test_tsqr_nonfinite_and_constant():
     rng = np.random.default_rng(14)
     a = rng.standard_normal((4, 3000, 48)).astype(np.float32)
