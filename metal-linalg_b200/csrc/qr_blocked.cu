@@ -915,6 +915,10 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
     const size_t o_z = take((size_t)AG * ncp);
     const size_t o_zp2 = take(zp_floats), o_z2 = take((size_t)AG * ncp);   // the second stream's
     const size_t o_ysp = take(tc_split_floats(m)), o_zsp = take(tc_split_floats(ncp)), o_ytsp = take(tc_split_t_floats(m));   // split operands of the wide updates
+    // the inner updates' partial sums where they take two kernels (more than eight chunks of rows, or QR_INNER_FUSED=0): the
+    // chain's own and the look-ahead stream's, which run side by side
+    const size_t inner_floats = (size_t)((m + 1023) / 1024) * 32 * 2 * AG;
+    const size_t o_zi = take(inner_floats), o_zi2 = take(inner_floats);
     const size_t o_info = take(64);
     size_t tsqr_floats = 0;
     for (uint32_t k0 = 0; k0 < K; k0 += NB)
@@ -962,12 +966,14 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         const uint32_t ln = b % nlanes;
         const cudaStream_t stream = ln ? ctx.lane(ln - 1).update : caller;
         const cudaStream_t panel_stream = ln ? ctx.lane(ln - 1).panel : ctx.aux;
+        const cudaStream_t look_stream = ln ? ctx.lane(ln - 1).look : ctx.look;
+        cudaEvent_t* const ev_look = ln ? ctx.lane(ln - 1).ev_look : ctx.ev_look;
         cudaEvent_t* const ev_panel  = ln ? ctx.lane(ln - 1).ev_panel : ctx.ev_panel;
         cudaEvent_t* const ev_update = ln ? ctx.lane(ln - 1).ev_update : ctx.ev_update;
         float* ws = ws_all + (size_t)ln * off;
         float *W = ws + o_w, *Y = ws + o_y, *T = ws + o_t, *Ta = ws + o_ta, *Qp = ws + o_qp, *Rp = ws + o_rp, *Ui = ws + o_ui;
         float *Zp = ws + o_zp, *Z = ws + o_z, *Zp2 = ws + o_zp2, *Z2 = ws + o_z2, *ts = ws + o_ts, *pf = ws + o_pf;
-        float *Ysp = ws + o_ysp, *Zsp = ws + o_zsp, *Ytsp = ws + o_ytsp;
+        float *Ysp = ws + o_ysp, *Zsp = ws + o_zsp, *Ytsp = ws + o_ytsp, *Zi = ws + o_zi, *Zi2 = ws + o_zi2;
         MatInfo* info = reinterpret_cast<MatInfo*>(ws + o_info);
 
         cuda_check(cudaMemsetAsync(info, 0, sizeof(MatInfo), stream), "cudaMemsetAsync");
@@ -1003,8 +1009,26 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // QR_BACKWARD_Q=1 keeps the backward accumulation.
         const bool forward_q = two && qc == m && (nlanes == 1 || m <= 4096) && std::getenv("QR_BACKWARD_Q") == nullptr;
         if (forward_q) launch_fill_identity(us, Q, 1, m, m);
+        // Look-ahead by panels (QR_LOOK_PANELS=0: by aggregates, below): a third stream `ls` keeps the NEXT aggregate's
+        // columns up to date panel by panel (the same inner update, on those 128 columns, as soon as a panel is
+        // factored), builds the aggregate's T and applies the aggregate to the columns of the aggregate after the
+        // next; the wide update on `us` starts beyond those. The chain on `ps` is then panels and their updates
+        // inside the aggregate only: the next aggregate's first panel waits for the last of the third stream's inner
+        // updates, not for the Gram matrix, the merge of the T's and a rank-128 update behind them.
+        // It costs more work in all (four inner updates of 128 columns an aggregate beside the rank-128 update), so it
+        // is for a matrix whose chain of panels is what bounds it: one matrix of at most 4608 rows (one B200, ms, by
+        // panels / by aggregates: 1024^2 1.50 / 1.82, 2048^2 3.39 / 3.98, 4096^2 8.80 / 9.67, 4096 x 1024 2.53 / 2.79;
+        // 5120^2 14.1 / 13.6, 8192^2 37.3 / 33.0, eight 4096^2 53.6 / 39.8). QR_LOOK_PANELS=1 asks for it everywhere.
+        const char* deep_env = std::getenv("QR_LOOK_PANELS");
+        const bool deep = two && (deep_env ? deep_env[0] != '0' : (nlanes == 1 && m <= 4608));
+        const cudaStream_t ls = look_stream;
+        if (deep) cuda_check(cudaStreamWaitEvent(ls, ev_update[1], 0), "cudaStreamWaitEvent");       // the working copy is ready
         for (uint32_t ag = 0; ag < naggs; ++ag) {
             const uint32_t j0 = ag * AG, wa = std::min<uint32_t>(AG, K - j0), ma = m - j0, pans = (wa + NB - 1) / NB;
+            const uint32_t right = n - (j0 + wa);
+            const uint32_t s1 = deep ? std::min<uint32_t>(AG, right) : 0;            // the next aggregate's columns
+            const uint32_t s2 = deep ? std::min<uint32_t>(AG, right - s1) : 0;       // and those of the one after
+            if (deep && ag > 0) cuda_check(cudaStreamWaitEvent(ps, ev_look[1], 0), "cudaStreamWaitEvent");   // this aggregate's columns are complete
             for (uint32_t pp = 0; pp < pans; ++pp) {
                 const uint32_t pi = ag * (AG / NB) + pp, k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
                 if (!slow_panels && panel_fast_fits(mp, jb)) {
@@ -1021,12 +1045,41 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                 if (pp)   // Y is read as one mp x wa matrix by the aggregate's products: zeros above the panel's top
                     cuda_check(cudaMemset2DAsync(Y + (size_t)j0 * ldy + k0, (size_t)ldy * sizeof(float), 0,
                                                  jb * sizeof(float), k0 - j0, ps), "cudaMemset2DAsync");
+                if (deep) {      // the panel's reflector to the next aggregate's columns, beside the chain
+                    cuda_check(cudaEventRecord(ev_look[0], ps), "cudaEventRecord");
+                    cuda_check(cudaStreamWaitEvent(ls, ev_look[0], 0), "cudaStreamWaitEvent");
+                    if (s1)
+                        apply_inner(ls, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024,
+                                    W + (size_t)k0 * ldw + j0 + wa, ldw, mp, jb, s1, Zi2);
+                }
                 const uint32_t inside = j0 + wa - (k0 + jb);   // columns of the aggregate right of the panel
                 if (inside)
                     apply_inner(ps, Y + (size_t)k0 * ldy + k0, ldy, T + (size_t)pi * 1024,
-                                W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside, Zp);
+                                W + (size_t)k0 * ldw + k0 + jb, ldw, mp, jb, inside, Zi);
             }
-            const uint32_t right = n - (j0 + wa);
+            if (deep) {
+                cuda_check(cudaEventRecord(ev_look[1], ls), "cudaEventRecord");      // the next aggregate's columns are complete
+                if (right || qc) {
+                    build_aggregate_t(ls, Y + (size_t)j0 * ldy + j0, ldy, ma, wa, pans, T + (size_t)ag * (AG / NB) * 1024,
+                                      Ta + (size_t)ag * AG * AG, Zp, &info->bad);
+                    cuda_check(cudaEventRecord(ev_look[2], ls), "cudaEventRecord");
+                    cuda_check(cudaStreamWaitEvent(us, ev_look[2], 0), "cudaStreamWaitEvent");
+                }
+                if (s2) {      // the aggregate to the columns of the aggregate after the next, which the previous wide update covered
+                    if (ag > 0) cuda_check(cudaStreamWaitEvent(ls, ev_update[(ag - 1) & 1], 0), "cudaStreamWaitEvent");
+                    apply_aggregate(ls, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                    W + (size_t)j0 * ldw + j0 + wa + s1, ldw, ma, wa, s2, Zp, Z, &info->bad);
+                }
+                if (right > s1 + s2)
+                    apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                    W + (size_t)j0 * ldw + j0 + wa + s1 + s2, ldw, ma, wa, right - s1 - s2, Zp2, Z2, &info->bad,
+                                    Ysp, Zsp, Ytsp);
+                cuda_check(cudaEventRecord(ev_update[ag & 1], us), "cudaEventRecord");
+                if (forward_q)
+                    apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
+                                    Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad, Ysp, Zsp, Ytsp);
+                continue;
+            }
             if (right || qc)
                 build_aggregate_t(ps, Y + (size_t)j0 * ldy + j0, ldy, ma, wa, pans, T + (size_t)ag * (AG / NB) * 1024,
                                   Ta + (size_t)ag * AG * AG, Zp, &info->bad);
@@ -1054,6 +1107,10 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                 apply_aggregate(us, Y + (size_t)j0 * ldy + j0, ldy, Ta + (size_t)ag * AG * AG, true,
                                 Q + (size_t)j0 * m, m, ma, wa, m, Zp2, Z2, &info->bad, Ysp, Zsp, Ytsp);
             }
+        }
+        if (deep) {   // the caller's stream joins the look-ahead stream too
+            cuda_check(cudaEventRecord(ev_look[2], ls), "cudaEventRecord");
+            cuda_check(cudaStreamWaitEvent(us, ev_look[2], 0), "cudaStreamWaitEvent");
         }
         if (two) {   // the caller's stream joins the panel stream
             cuda_check(cudaEventRecord(ev_panel[0], ps), "cudaEventRecord");

@@ -76,6 +76,9 @@ DeviceContext& context(int device) {
         int least = 0, greatest = 0;   // the panel chain of the blocked QR goes ahead of the bulk updates
         cuda_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
         cuda_check(cudaStreamCreateWithPriority(&c->aux, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithPriority(&c->look, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        for (int i = 0; i < DeviceContext::kLookEvents; ++i)
+            cuda_check(cudaEventCreateWithFlags(&c->ev_look[i], cudaEventDisableTiming), "cudaEventCreate");
         cuda_check(cudaMalloc(&c->status, 256), "cudaMalloc");
         cuda_check(cudaMemset(c->status, 0, 256), "cudaMemset");
         for (int i = 0; i < 2; ++i) {
@@ -100,6 +103,9 @@ DeviceContext::Lane& DeviceContext::lane(int i) {
         cuda_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
         cuda_check(cudaStreamCreateWithFlags(&l.update, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaStreamCreateWithPriority(&l.panel, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithPriority(&l.look, cudaStreamNonBlocking, greatest), "cudaStreamCreate");
+        for (int k = 0; k < kLookEvents; ++k)
+            cuda_check(cudaEventCreateWithFlags(&l.ev_look[k], cudaEventDisableTiming), "cudaEventCreate");
         for (int k = 0; k < 2; ++k) {
             cuda_check(cudaEventCreateWithFlags(&l.ev_panel[k], cudaEventDisableTiming), "cudaEventCreate");
             cuda_check(cudaEventCreateWithFlags(&l.ev_update[k], cudaEventDisableTiming), "cudaEventCreate");

@@ -47,11 +47,16 @@ struct DeviceContext {
     // the blocked QR's second stream (trailing updates beside the next panels) and its events
     cudaStream_t   aux = nullptr;
     cudaEvent_t    ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr};
+    // and its third: what the next aggregate's columns need of the current one, beside the chain of panels
+    static constexpr int kLookEvents = 3;       // a panel is factored; the next aggregate's columns are complete; the aggregate's T is built
+    cudaStream_t   look = nullptr;
+    cudaEvent_t    ev_look[kLookEvents] = {};
     // further pairs of streams for a batch of large matrices, factored several at a time (the first
     // matrix of a round runs on the caller's stream and `aux`); created on first use
     struct Lane {
-        cudaStream_t update = nullptr, panel = nullptr;
+        cudaStream_t update = nullptr, panel = nullptr, look = nullptr;
         cudaEvent_t  ev_panel[2] = {nullptr, nullptr}, ev_update[2] = {nullptr, nullptr}, ev_done = nullptr;
+        cudaEvent_t  ev_look[3] = {};
     };
     static constexpr int kExtraLanes = 3;
     Lane           lanes[kExtraLanes];

@@ -241,7 +241,7 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=16"])
+                                    "QR_PANEL_CLUSTER=16", "QR_LOOK_PANELS=0"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
@@ -250,7 +250,7 @@ def test_blocked_fallback_paths(switch):
     effect only when set before the first call), panels by the tree of row blocks instead of one
     cluster launch, tensor-core products that split their operands in every block instead of once,
     panel steps a column a reduction instead of two, the update inside the aggregate in two launches
-    instead of one cluster launch, panel clusters of sixteen blocks."""
+    instead of one cluster launch, panel clusters of sixteen blocks, look-ahead by aggregates instead of by panels."""
     rng = np.random.default_rng(16)
     a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
@@ -263,6 +263,29 @@ def test_blocked_fallback_paths(switch):
     check(a, q1, r1, "reduced")
     assert harness.r_parity(r1, r0) <= 1e-4
     _, r_ref = harness.oracle_qr(a)
+    assert harness.r_parity(r1, r_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
+@pytest.mark.parametrize("shape", [(3, 700, 700), (2, 1000, 420), (2, 400, 1100), (1, 1300, 130), (1, 640, 257)])
+def test_blocked_look_ahead_by_panels(shape, mode):
+    """The look-ahead that keeps the next aggregate's columns up to date panel by panel on a third stream (the default
+    for one matrix of at most 4608 rows; QR_LOOK_PANELS=1 asks for it on a batch, whose matrices run on several sets of
+    streams at once): shapes with two to six aggregates, a last aggregate narrower than 128, one and two columns of
+    the aggregate after the next, wide and tall, against the look-ahead by aggregates and the reference."""
+    b, m, n = shape
+    rng = np.random.default_rng(b * 1000 + m + n)
+    a = rng.standard_normal((b, m, n)).astype(np.float32)
+    os.environ["QR_LOOK_PANELS"] = "0"
+    try:
+        q0, r0 = gpu_qr(a, mode, kernel="blocked")
+        os.environ["QR_LOOK_PANELS"] = "1"
+        q1, r1 = gpu_qr(a, mode, kernel="blocked")
+    finally:
+        os.environ.pop("QR_LOOK_PANELS", None)
+    check(a, q1, r1, mode)
+    assert harness.r_parity(r1, r0) <= 1e-4
+    _, r_ref = harness.oracle_qr(a, mode)
     assert harness.r_parity(r1, r_ref) <= 1e-4
 
 
