@@ -717,6 +717,8 @@ __global__ void __launch_bounds__(256) inner_apply_kernel(const float* __restric
 // them (distributed shared memory), and after one cluster barrier each sums the parts in the same fixed order and
 // applies W = T^T Z to its own rows. One launch and no round trip through global memory between the halves.
 constexpr int kInnerCluster = 8;
+constexpr int kInnerYld = 36;           // floats between a thread's rows of Y in shared memory and the next thread's: 16-byte words, conflict-free
+constexpr size_t kInnerSmem = (size_t)IRB * kInnerYld * sizeof(float);
 
 __device__ __forceinline__ uint32_t inner_cluster_rank() {
     uint32_t r;
@@ -743,6 +745,32 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
     const uint32_t c0 = blockIdx.x * ICS, ncb = min((uint32_t)ICS, nc - c0);
     const uint32_t r_begin = blockIdx.y * IRB, r_end = min(mp, r_begin + IRB);
     const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
+    // Y's rows of this block go to shared memory once, by 16-byte asynchronous copies that are all in flight together
+    // (a thread's own rows: it alone reads them back, so its own wait is all the ordering they need), and serve both
+    // passes; C's entries stay in registers from the first pass to the second. (Read row by row from global memory, in
+    // both passes, the block waited for L2 eight times over.)
+    extern __shared__ __align__(16) float inner_ys[];       // [IRB / 256][256][kInnerYld]
+    float cv[IRB / 256][ICS];
+    if (yvec) {
+#pragma unroll
+        for (int i = 0; i < IRB / 256; ++i) {
+            const uint32_t r = r_begin + t + 256 * i;
+            if (r < r_end) {
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(inner_ys + (size_t)(i * 256 + t) * kInnerYld);
+                const float* src = Y + (size_t)r * ldy;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + 16 * q), "l"(src + 4 * q) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < IRB / 256; ++i) {
+        const uint32_t r = r_begin + t + 256 * i;
+#pragma unroll
+        for (int j = 0; j < ICS; ++j) cv[i][j] = (r < r_end && (uint32_t)j < ncb) ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+    }
     float tv[4];                                            // T on its way to shared memory while Z is formed
 #pragma unroll
     for (int u = 0; u < 4; ++u) tv[u] = T[t + 256 * u];
@@ -751,15 +779,19 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
     for (int k = 0; k < 32; ++k)
 #pragma unroll
         for (int j = 0; j < ICS; ++j) z[k][j] = 0.0f;
-    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
-        float y[32], c[ICS];
-        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
+    if (yvec) asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < ICS; ++j) c[j] = (uint32_t)j < ncb ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+    for (int i = 0; i < IRB / 256; ++i) {
+        const uint32_t r = r_begin + t + 256 * i;
+        if (r < r_end) {
+            float y[32];
+            if (yvec) inner_load_y(y, inner_ys + (size_t)(i * 256 + t) * kInnerYld, true, jb);
+            else inner_load_y(y, Y + (size_t)r * ldy, false, jb);
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
+            for (int k = 0; k < 32; ++k)
 #pragma unroll
-            for (int j = 0; j < ICS; ++j) z[k][j] = fmaf(y[k], c[j], z[k][j]);
+                for (int j = 0; j < ICS; ++j) z[k][j] = fmaf(y[k], cv[i][j], z[k][j]);
+        }
     }
 #pragma unroll
     for (int j = 0; j < ICS; ++j) {
@@ -813,19 +845,24 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
     for (int k = 0; k < 32; ++k)
 #pragma unroll
         for (int j = 0; j < ICS; ++j) w[k][j] = Ws[k][j];
-    for (uint32_t r = r_begin + t; r < r_end; r += 256) {
-        float y[32];
-        inner_load_y(y, Y + (size_t)r * ldy, yvec, jb);
-        float d[ICS];
 #pragma unroll
-        for (int j = 0; j < ICS; ++j) d[j] = 0.0f;
+    for (int i = 0; i < IRB / 256; ++i) {
+        const uint32_t r = r_begin + t + 256 * i;
+        if (r < r_end) {
+            float y[32];
+            if (yvec) inner_load_y(y, inner_ys + (size_t)(i * 256 + t) * kInnerYld, true, jb);
+            else inner_load_y(y, Y + (size_t)r * ldy, false, jb);
+            float d[ICS];
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
+            for (int j = 0; j < ICS; ++j) d[j] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < ICS; ++j) d[j] = fmaf(y[k], w[k][j], d[j]);
+            for (int k = 0; k < 32; ++k)
 #pragma unroll
-        for (int j = 0; j < ICS; ++j)
-            if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] -= d[j];
+                for (int j = 0; j < ICS; ++j) d[j] = fmaf(y[k], w[k][j], d[j]);
+#pragma unroll
+            for (int j = 0; j < ICS; ++j)
+                if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] = cv[i][j] - d[j];
+        }
     }
 }
 
@@ -841,6 +878,7 @@ void apply_inner(cudaStream_t stream, const float* Y, size_t ldy, const float* T
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = kInnerSmem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -948,6 +986,8 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                    "merge_t shared memory");
         cuda_check(cudaFuncSetAttribute(reduce_t_narrow_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kReduceNarrowSmem), "reduce_t_narrow shared memory");
+        cuda_check(cudaFuncSetAttribute(inner_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kInnerSmem),
+                   "inner_fused shared memory");
         once.mark(ctx.device);
     }
     const cudaStream_t caller = stream;
