@@ -1056,11 +1056,12 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // inside the aggregate only: the next aggregate's first panel waits for the last of the third stream's inner
         // updates, not for the Gram matrix, the merge of the T's and a rank-128 update behind them.
         // It costs more work in all (four inner updates of 128 columns an aggregate beside the rank-128 update), so it
-        // is for a matrix whose chain of panels is what bounds it: one matrix of at most 4608 rows (one B200, ms, by
-        // panels / by aggregates: 1024^2 1.50 / 1.82, 2048^2 3.39 / 3.98, 4096^2 8.80 / 9.67, 4096 x 1024 2.53 / 2.79;
-        // 5120^2 14.1 / 13.6, 8192^2 37.3 / 33.0, eight 4096^2 53.6 / 39.8). QR_LOOK_PANELS=1 asks for it everywhere.
+        // is for a matrix whose chain of panels is what bounds it: one matrix of at most 5632 rows, 7168 when no Q is
+        // formed (one B200, ms, by panels / by aggregates: 1024^2 1.38 / 1.73, 2048^2 3.05 / 3.73, 4096^2 7.90 / 9.17,
+        // 5120^2 12.3 / 12.8, 6144^2 17.9 / 17.6 and R alone 13.2 / 14.4, 8192^2 34.1 / 31.7 and R alone 22.1 / 22.1,
+        // eight 4096^2 47.0 / 37.8). QR_LOOK_PANELS=1 asks for it everywhere.
         const char* deep_env = std::getenv("QR_LOOK_PANELS");
-        const bool deep = two && (deep_env ? deep_env[0] != '0' : (nlanes == 1 && m <= 4608));
+        const bool deep = two && (deep_env ? deep_env[0] != '0' : (nlanes == 1 && m <= (qc ? 5632u : 7168u)));
         const cudaStream_t ls = look_stream;
         if (deep) cuda_check(cudaStreamWaitEvent(ls, ev_update[1], 0), "cudaStreamWaitEvent");       // the working copy is ready
         for (uint32_t ag = 0; ag < naggs; ++ag) {
