@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     }
     cluster_barrier();          // every block of the cluster is running before any writes into another's shared memory
     float my_sc;
-    if (p.pairs) factor_cols2<RW>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});
+    if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
     else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
     if (rank == 0 && warp == 0) {
@@ -713,9 +713,10 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
     // reduction it beats the tree of row blocks there (8192 x 8192: 35.3 -> 32.6 ms); QR_PANEL_CLUSTER=4096 keeps the tree
     const bool tall_cluster = !(envc && envc[0] == '4');
     if (by_columns && (mp <= 4096 || (tall_cluster && mp <= 8192)) && !(envc && envc[0] == '0')) {
-        // beyond 2048 rows: 8 blocks of 512 rows (64 rows a lane), or with QR_PANEL_CLUSTER=16 sixteen blocks of
-        // 256 rows (32 rows a lane: half the arithmetic a step, a cluster of the non-portable size)
-        const bool sixteen = mp > 2048 && mp <= 4096 && envc && envc[0] == '1' && envc[1] == '6';
+        // 2049 to 4096 rows: sixteen blocks of 256 rows (32 rows a lane: half the arithmetic and half the shared-memory
+        // reads a step, and registers left to keep the published columns from the products to the update; a cluster of
+        // the non-portable size), or with QR_PANEL_CLUSTER=8 eight blocks of 512 rows (4096 x 4096: 7.67 against 7.86 ms)
+        const bool sixteen = mp > 2048 && mp <= 4096 && !(envc && envc[0] == '8');
         const uint32_t rw = (mp <= 2048 || sixteen) ? 32 : 64;
         uint32_t ncta = 1;
         while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4, 8 (or 16) blocks; blocks beyond the rows hold zeros

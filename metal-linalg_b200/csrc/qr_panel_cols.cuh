@@ -374,7 +374,9 @@ __device__ __forceinline__ void step_other(pair_t (&x2)[RW / 2], Smem& s, ulongl
 // alike: all of them hold the same sums.
 constexpr float kPairKeep = 1.0f / 16.0f;
 
-template <int RW, typename Sync>
+// KeepU: the two published columns stay in registers from the products to the update (4 * RW / 4 more registers) instead
+// of being read from shared memory a second time; the path from shared memory is what bounds a step.
+template <int RW, typename Sync, bool KeepU = false>
 __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, float* pub, float& my_sc, const Sync& sync) {
     constexpr int NQ = RW / 4, NP = RW / 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -387,6 +389,7 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
 #pragma unroll 1
     for (int it = 0; it < 16; ++it) {
         const int j = 2 * it, buf = it & 1;
+        ulonglong2 ka[KeepU ? NQ : 1], kb[KeepU ? NQ : 1];
         // 1. columns j and j + 1 below the pivot pair (the pivot warp's pair 0 holds rows j and j + 1 themselves)
         if (lane == j || lane == j + 1) {
             ulonglong2* dst = lane == j ? pA : pB;
@@ -400,6 +403,10 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
                 const ulonglong2 ua = pA[q], ub = pB[q];
+                if (KeepU) {
+                    ka[q] = ua;
+                    kb[q] = ub;
+                }
                 sa  = fma2(ua.x, x2[2 * q], sa);
                 sa2 = fma2(ua.y, x2[2 * q + 1], sa2);
                 sb  = fma2(ub.x, x2[2 * q], sb);
@@ -464,19 +471,19 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
                 // the pairs move up one place as the two finished rows leave
 #pragma unroll
                 for (int i = 1; i < 16; ++i) {
-                    const ulonglong2 ua = pA[i / 2], ub = pB[i / 2];
+                    const ulonglong2 ua = KeepU ? ka[i / 2] : pA[i / 2], ub = KeepU ? kb[i / 2] : pB[i / 2];
                     x2[i - 1] = fma2(a2, (i & 1) ? ua.y : ua.x, fma2(b2, (i & 1) ? ub.y : ub.x, x2[i]));
                 }
                 x2[15] = zero2;
 #pragma unroll
                 for (int i = 16; i < NP; ++i) {
-                    const ulonglong2 ua = pA[i / 2], ub = pB[i / 2];
+                    const ulonglong2 ua = KeepU ? ka[i / 2] : pA[i / 2], ub = KeepU ? kb[i / 2] : pB[i / 2];
                     x2[i] = fma2(a2, (i & 1) ? ua.y : ua.x, fma2(b2, (i & 1) ? ub.y : ub.x, x2[i]));
                 }
             } else {
 #pragma unroll
                 for (int qq = 0; qq < NQ; ++qq) {
-                    const ulonglong2 ua = pA[qq], ub = pB[qq];
+                    const ulonglong2 ua = KeepU ? ka[qq] : pA[qq], ub = KeepU ? kb[qq] : pB[qq];
                     x2[2 * qq]     = fma2(a2, ua.x, fma2(b2, ub.x, x2[2 * qq]));
                     x2[2 * qq + 1] = fma2(a2, ua.y, fma2(b2, ub.y, x2[2 * qq + 1]));
                 }
@@ -487,7 +494,7 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
             if (piv) {
 #pragma unroll
                 for (int i = 1; i < NP; ++i) {
-                    const ulonglong2 ua = pA[i / 2];
+                    const ulonglong2 ua = KeepU ? ka[i / 2] : pA[i / 2];
                     x2[i] = fma2(a2, (i & 1) ? ua.y : ua.x, x2[i]);
                 }
                 x2[0] = pack(rj, m1);          // row j finished (it leaves with row j + 1), row j + 1 the next pivot row
@@ -495,7 +502,7 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
             } else {
 #pragma unroll
                 for (int qq = 0; qq < NQ; ++qq) {
-                    const ulonglong2 ua = pA[qq];
+                    const ulonglong2 ua = KeepU ? ka[qq] : pA[qq];
                     x2[2 * qq]     = fma2(a2, ua.x, x2[2 * qq]);
                     x2[2 * qq + 1] = fma2(a2, ua.y, x2[2 * qq + 1]);
                 }

@@ -241,7 +241,7 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=16", "QR_LOOK_PANELS=0"])
+                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
@@ -250,7 +250,7 @@ def test_blocked_fallback_paths(switch):
     effect only when set before the first call), panels by the tree of row blocks instead of one
     cluster launch, tensor-core products that split their operands in every block instead of once,
     panel steps a column a reduction instead of two, the update inside the aggregate in two launches
-    instead of one cluster launch, panel clusters of sixteen blocks, look-ahead by aggregates instead of by panels."""
+    instead of one cluster launch, panel clusters of eight blocks of 512 rows instead of sixteen of 256, look-ahead by aggregates instead of by panels."""
     rng = np.random.default_rng(16)
     a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
@@ -264,6 +264,25 @@ def test_blocked_fallback_paths(switch):
     assert harness.r_parity(r1, r0) <= 1e-4
     _, r_ref = harness.oracle_qr(a)
     assert harness.r_parity(r1, r_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("switch", ["", "QR_PANEL_CLUSTER=8", "QR_PANEL_CLUSTER=0", "QR_PANEL_PAIRS=0"])
+def test_blocked_panels_of_2049_to_4096_rows(switch):
+    """Panels of 2049 to 4096 rows: a cluster of sixteen blocks of 256 rows (the default, with the published columns
+    kept in registers between the products and the update), of eight blocks of 512 rows, the tree of row blocks, and
+    the cluster with a column a reduction, all against the reference."""
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((1, 3000, 96)).astype(np.float32)
+    if switch:
+        name, value = switch.split("=")
+        os.environ[name] = value
+    try:
+        q, r = gpu_qr(a, "reduced", kernel="blocked")
+    finally:
+        if switch:
+            os.environ.pop(name, None)
+    _, r_ref = harness.oracle_qr(a)
+    check(a, q, r, "reduced", r_ref)
 
 
 @pytest.mark.parametrize("mode", ["reduced", "complete", "r"])
