@@ -573,7 +573,7 @@ struct ClusterPanelParams {
     size_t   ldy;
     float*   t;         // [32][32] out
     uint32_t mp, jb;
-    int      pairs;     // two columns a reduction (factor_cols2)
+    int      pairs;     // 1: two columns a reduction (factor_cols2); 2: four (factor_cols4); 0: one
 };
 
 template <int RW>
@@ -583,6 +583,9 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     __shared__ __align__(16) cols::Smem s;
     __shared__ __align__(16) cols::ClusterShared cs;
     __shared__ __align__(16) float pub[2 * kWarps * RW];
+    extern __shared__ __align__(16) unsigned char quad_raw[];      // four columns a reduction: QuadShared, then 4 * kWarps * RW floats
+    QuadShared* qs = reinterpret_cast<QuadShared*>(quad_raw);
+    float* pub4 = reinterpret_cast<float*>(quad_raw + sizeof(QuadShared));
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint32_t rank = cluster_rank(), ncta = cluster_size();
     const uint32_t row0 = (rank * kWarps + warp) * RW;
@@ -599,7 +602,8 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     }
     cluster_barrier();          // every block of the cluster is running before any writes into another's shared memory
     float my_sc;
-    if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
+    if (p.pairs == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs});
+    else if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
     else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
     if (rank == 0 && warp == 0) {
@@ -720,6 +724,16 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
         const uint32_t rw = (mp <= 2048 || sixteen) ? 32 : 64;
         uint32_t ncta = 1;
         while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4, 8 (or 16) blocks; blocks beyond the rows hold zeros
+        {
+            static PerDeviceOnce once_smem;      // static and dynamic shared memory together pass the 48 KB that need no opt-in
+            if (const int device = current_device(); once_smem.first(device)) {
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 32 * sizeof(float))), "panel_cluster shared memory");
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 64 * sizeof(float))), "panel_cluster shared memory");
+                once_smem.mark(device);
+            }
+        }
         if (ncta > 8) {
             static PerDeviceOnce once;
             if (const int device = current_device(); once.first(device)) {
@@ -730,11 +744,15 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
                 once.mark(device);
             }
         }
+        // four columns a reduction (QR_PANEL_QUADS=0: two; QR_PANEL_PAIRS=0: one)
         const char* envp = std::getenv("QR_PANEL_PAIRS");
-        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb, !(envp && envp[0] == '0')};
+        const char* envq = std::getenv("QR_PANEL_QUADS");
+        const int pairs = (envp && envp[0] == '0') ? 0 : (envq && envq[0] == '0') ? 1 : 2;
+        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb, pairs};
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(ncta);
         cfg.blockDim = dim3(PT);
+        cfg.dynamicSmemBytes = pairs == 2 ? sizeof(cols::QuadShared) + 4 * cols::kWarps * rw * sizeof(float) : 0;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;

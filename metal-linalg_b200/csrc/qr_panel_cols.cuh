@@ -129,9 +129,53 @@ __device__ __forceinline__ void store_to_block(const float* local, uint32_t rank
                  : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
     asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(remote), "f"(v) : "memory");
 }
+// For the steps of FOUR columns a reduction (factor_cols4): each warp's four partial products per lane as one 16-byte
+// word, the four pivot rows of every column, and the blocks' sums, all by quad parity.
+struct QuadShared {
+    float red4[2][kWarps][32][4];
+    float prow4[2][32][4];
+    float cred4[2][kMaxCluster][32][4];
+};
+__device__ __forceinline__ void store4_to_block(const float* local, uint32_t rank, float4 v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 struct ClusterSync {
     uint32_t       rank, ncta;
     ClusterShared* cs;
+    QuadShared*    qs = nullptr;
+    // the four sums of a four-column step: the block's sums to every block (16 bytes a store), block 0's pivot rows along
+    __device__ __forceinline__ void exchange4(int buf, int lane, int warp) const {
+        step_barrier(32 * kWarps);
+        float4 d = *reinterpret_cast<const float4*>(qs->red4[buf][0][lane]);
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) {
+            const float4 e = *reinterpret_cast<const float4*>(qs->red4[buf][w][lane]);
+            d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+        }
+        for (uint32_t r = warp; r < ncta; r += kWarps) {
+            store4_to_block(qs->cred4[buf][rank][lane], r, d);
+            if (rank == 0 && r != 0)
+                store4_to_block(qs->prow4[buf][lane], r, *reinterpret_cast<const float4*>(qs->prow4[buf][lane]));
+        }
+        cluster_barrier();
+    }
+    __device__ __forceinline__ float4 total4(int buf, int lane) const {
+        // every block's word asked for before the first is added (the loads of a loop over ncta would go one by one);
+        // the order of the additions is the ranks' in every block
+        float4 e[kMaxCluster];
+#pragma unroll
+        for (uint32_t r = 0; r < (uint32_t)kMaxCluster; ++r)
+            e[r] = r < ncta ? *reinterpret_cast<const float4*>(qs->cred4[buf][r][lane]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 d = e[0];
+#pragma unroll
+        for (uint32_t r = 1; r < (uint32_t)kMaxCluster; ++r) {
+            if (r < ncta) { d.x += e[r].x; d.y += e[r].y; d.z += e[r].z; d.w += e[r].w; }
+        }
+        return d;
+    }
     __device__ __forceinline__ bool pivot(int warp) const { return rank == 0 && warp == 0; }
     __device__ __forceinline__ bool leader(int warp) const { return rank == 0 && warp == 0; }
     __device__ __forceinline__ void exchange(Smem& s, int buf, int lane, int warp) const {
@@ -508,6 +552,200 @@ __device__ __forceinline__ void factor_cols2(pair_t (&x2)[RW / 2], Smem& s, floa
                 }
                 step_other<RW>(x2, s, pA, j + 1, lane, warp, sync, my_sc);
             }
+        }
+    }
+}
+
+// The same factorisation with FOUR columns a reduction. Lanes j .. j + 3 publish their columns below the four pivot
+// rows (w_0 .. w_3), every lane takes the four products P_a = w_a^T y with its own column's tail y, and ONE exchange
+// returns them together with the four pivot rows of every column. From then on a column's tail is y + sum_a c_a w_a
+// with four coefficients c (all zero at first), and its entries in the four pivot rows are four numbers b, both held by
+// every thread for its lane's column. Step s (column j + s, whose tail is sum_a d_a w_a, d = e_s + its c) needs only
+//   its norm              d^T G d                       with G = the Gram matrix of the w's (the P's of lanes j .. j + 3)
+//   its product with y'   d^T P + c^T (G d)             for every column
+// and the pivot rows' part, which is explicit; it changes b and c, not the tails. After the four steps the tails take
+// all four reflectors at once, y += sum_a c_a w_a. A panel is a chain of exchanges; this halves it again.
+//
+// As with two columns, a norm that comes out of the Gram matrix as a difference loses digits where the earlier steps
+// of the group removed most of the column: a step is taken from the sums only where its tail keeps at least
+// kQuadKeep of what it was; otherwise the tails are brought up to date with the steps done so far and the rest of the
+// group runs as single steps with an exchange of their own. Every thread of the cluster decides alike.
+constexpr float kQuadKeep = 1.0f / 16.0f;
+
+template <int RW, typename Sync>
+__device__ __forceinline__ void factor_cols4(pair_t (&x2)[RW / 2], Smem& s, float* pub4, float& my_sc, const Sync& sync) {
+    constexpr int NQ = RW / 4, NP = RW / 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool piv = sync.pivot(warp), lead = sync.leader(warp);
+    QuadShared& qs = *sync.qs;
+    ulonglong2* pw = reinterpret_cast<ulonglong2*>(pub4) + (size_t)warp * 4 * NQ;      // this warp's pieces of w_0 .. w_3
+    const pair_t zero2 = pack(0.0f, 0.0f);
+    my_sc = 0.0f;
+#pragma unroll 1
+    for (int it = 0; it < 8; ++it) {
+        const int j = 4 * it, buf = it & 1;
+        // 1. the four columns below the pivot rows (the pivot warp's pairs 0 and 1 hold rows j .. j + 3 themselves)
+        __syncwarp();
+        if (lane >= j && lane < j + 4) {
+            ulonglong2* dst = pw + (lane - j) * NQ;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q)
+                dst[q] = (piv && q == 0) ? make_ulonglong2(zero2, zero2) : make_ulonglong2(x2[2 * q], x2[2 * q + 1]);
+        }
+        __syncwarp();
+        // 2. the four products with this lane's column
+        {
+            pair_t a0 = zero2, a1 = zero2, a2 = zero2, a3 = zero2, e0 = zero2, e1 = zero2, e2 = zero2, e3 = zero2;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const ulonglong2 u0 = pw[q], u1 = pw[NQ + q], u2 = pw[2 * NQ + q], u3 = pw[3 * NQ + q];
+                a0 = fma2(u0.x, x2[2 * q], a0); e0 = fma2(u0.y, x2[2 * q + 1], e0);
+                a1 = fma2(u1.x, x2[2 * q], a1); e1 = fma2(u1.y, x2[2 * q + 1], e1);
+                a2 = fma2(u2.x, x2[2 * q], a2); e2 = fma2(u2.y, x2[2 * q + 1], e2);
+                a3 = fma2(u3.x, x2[2 * q], a3); e3 = fma2(u3.y, x2[2 * q + 1], e3);
+            }
+            *reinterpret_cast<float4*>(qs.red4[buf][warp][lane]) = make_float4(hsum2(a0, e0), hsum2(a1, e1), hsum2(a2, e2), hsum2(a3, e3));
+        }
+        if (piv) *reinterpret_cast<float4*>(qs.prow4[buf][lane]) = make_float4(lo_of(x2[0]), hi_of(x2[0]), lo_of(x2[1]), hi_of(x2[1]));
+        sync.exchange4(buf, lane, warp);
+        float P[4], b[4], c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const float4 t4 = sync.total4(buf, lane);
+            P[0] = t4.x; P[1] = t4.y; P[2] = t4.z; P[3] = t4.w;
+            const float4 b4 = *reinterpret_cast<const float4*>(qs.prow4[buf][lane]);
+            b[0] = b4.x; b[1] = b4.y; b[2] = b4.z; b[3] = b4.w;
+        }
+        float G[4][4];      // G[a][k] = w_a^T w_k
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int k = a; k < 4; ++k) G[a][k] = G[k][a] = __shfl_sync(0xffffffffu, P[a], j + k);
+        // 3. the four steps, from the sums
+        int done = 4;
+        static_for<4>([&](auto sc_) {
+            constexpr int st = decltype(sc_)::value;
+            if (done != 4) return;
+            const int J = j + st;
+            float d[4], bb[4], g[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) d[a] = __shfl_sync(0xffffffffu, c[a], J) + (a == st ? 1.0f : 0.0f);
+#pragma unroll
+            for (int r = st; r < 4; ++r) bb[r] = __shfl_sync(0xffffffffu, b[r], J);
+            float vv = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                g[k] = fmaf(d[0], G[0][k], fmaf(d[1], G[1][k], fmaf(d[2], G[2][k], d[3] * G[3][k])));
+                vv = fmaf(g[k], d[k], vv);
+            }
+            if (st > 0 && !(vv >= kQuadKeep * G[st][st])) {
+                done = st;
+                return;
+            }
+            const float alpha = bb[st];
+            float ssum = fmaxf(vv, 0.0f);
+#pragma unroll
+            for (int r = st + 1; r < 4; ++r) ssum = fmaf(bb[r], bb[r], ssum);
+            float v1, gneg;
+            fast_reflector(alpha, ssum, v1, gneg);
+            float dot = v1 * b[st];
+#pragma unroll
+            for (int r = st + 1; r < 4; ++r) dot = fmaf(bb[r], b[r], dot);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) dot = fmaf(d[a], P[a], fmaf(c[a], g[a], dot));
+            const float t   = lane > J ? dot * gneg : 0.0f;
+            const float scj = gneg != 0.0f ? recip(v1) : 0.0f;
+            if (lead) {
+                if (lane < J) s.G[lane][J] = dot * my_sc * scj;
+                if (lane == 0) {
+                    s.taus[J] = -gneg * v1 * v1;
+                    s.sc[J]   = scj;
+                }
+            }
+            if (lane == J) my_sc = scj;
+            b[st] = lane > J ? fmaf(t, v1, b[st]) : (lane == J ? alpha - v1 : b[st]);
+#pragma unroll
+            for (int r = st + 1; r < 4; ++r) b[r] = fmaf(t, bb[r], b[r]);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) c[a] = fmaf(t, d[a], c[a]);
+        });
+        // 4. the tails take the steps done: y += sum_a c_a w_a (zeros were published for the pivot rows)
+        {
+            const pair_t c0 = pack(c[0], c[0]), c1 = pack(c[1], c[1]), c2 = pack(c[2], c[2]), c3 = pack(c[3], c[3]);
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const ulonglong2 u0 = pw[q], u1 = pw[NQ + q], u2 = pw[2 * NQ + q], u3 = pw[3 * NQ + q];
+                x2[2 * q]     = fma2(c0, u0.x, fma2(c1, u1.x, fma2(c2, u2.x, fma2(c3, u3.x, x2[2 * q]))));
+                x2[2 * q + 1] = fma2(c0, u0.y, fma2(c1, u1.y, fma2(c2, u2.y, fma2(c3, u3.y, x2[2 * q + 1]))));
+            }
+        }
+        // 5. what is left of the group as single steps, each with its own exchange
+        if (done != 4) {
+            static_for<3>([&](auto sc_) {
+                constexpr int st = decltype(sc_)::value + 1;
+                if (st < done) return;
+                const int J = j + st, sb = st & 1;
+                __syncwarp();
+                if (lane == J) {
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q)
+                        pw[q] = (piv && q == 0) ? make_ulonglong2(zero2, zero2) : make_ulonglong2(x2[2 * q], x2[2 * q + 1]);
+                }
+                __syncwarp();
+                {
+                    pair_t a0 = zero2, e0 = zero2;
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) {
+                        const ulonglong2 u0 = pw[q];
+                        a0 = fma2(u0.x, x2[2 * q], a0);
+                        e0 = fma2(u0.y, x2[2 * q + 1], e0);
+                    }
+                    s.red[sb][warp][lane] = hsum2(a0, e0);
+                }
+                if (piv) s.prow[sb][lane] = 0.0f;      // the exchange sends it along; the pivot rows are in b here
+                sync.exchange(s, sb, lane, warp);
+                const float p = sync.total(s, sb, lane);
+                float bb[4];
+#pragma unroll
+                for (int r = st; r < 4; ++r) bb[r] = __shfl_sync(0xffffffffu, b[r], J);
+                const float alpha = bb[st];
+                float ssum = __shfl_sync(0xffffffffu, p, J);
+#pragma unroll
+                for (int r = st + 1; r < 4; ++r) ssum = fmaf(bb[r], bb[r], ssum);
+                float v1, gneg;
+                fast_reflector(alpha, ssum, v1, gneg);
+                float dot = fmaf(v1, b[st], p);
+#pragma unroll
+                for (int r = st + 1; r < 4; ++r) dot = fmaf(bb[r], b[r], dot);
+                const float t   = lane > J ? dot * gneg : 0.0f;
+                const float scj = gneg != 0.0f ? recip(v1) : 0.0f;
+                if (lead) {
+                    if (lane < J) s.G[lane][J] = dot * my_sc * scj;
+                    if (lane == 0) {
+                        s.taus[J] = -gneg * v1 * v1;
+                        s.sc[J]   = scj;
+                    }
+                }
+                if (lane == J) my_sc = scj;
+                b[st] = lane > J ? fmaf(t, v1, b[st]) : (lane == J ? alpha - v1 : b[st]);
+#pragma unroll
+                for (int r = st + 1; r < 4; ++r) b[r] = fmaf(t, bb[r], b[r]);
+                const pair_t t2 = pack(t, t);
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    const ulonglong2 u0 = pw[q];
+                    x2[2 * q]     = fma2(t2, u0.x, x2[2 * q]);
+                    x2[2 * q + 1] = fma2(t2, u0.y, x2[2 * q + 1]);
+                }
+            });
+        }
+        // 6. the four finished rows leave; the pivot warp's pairs move up two places
+        if (piv) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) s.rows[j + r][lane] = b[r];
+#pragma unroll
+            for (int i = 2; i < 16; ++i) x2[i - 2] = x2[i];
+            x2[14] = zero2;
+            x2[15] = zero2;
         }
     }
 }

@@ -241,7 +241,7 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0"])
+                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
@@ -266,7 +266,7 @@ def test_blocked_fallback_paths(switch):
     assert harness.r_parity(r1, r_ref) <= 1e-4
 
 
-@pytest.mark.parametrize("switch", ["", "QR_PANEL_CLUSTER=8", "QR_PANEL_CLUSTER=0", "QR_PANEL_PAIRS=0"])
+@pytest.mark.parametrize("switch", ["", "QR_PANEL_CLUSTER=8", "QR_PANEL_CLUSTER=0", "QR_PANEL_PAIRS=0", "QR_PANEL_QUADS=0"])
 def test_blocked_panels_of_2049_to_4096_rows(switch):
     """Panels of 2049 to 4096 rows: a cluster of sixteen blocks of 256 rows (the default, with the published columns
     kept in registers between the products and the update), of eight blocks of 512 rows, the tree of row blocks, and
