@@ -974,3 +974,43 @@ def test_panel_pairs_with_nearly_parallel_columns(kernel, shape):
     _, r_ref = harness.oracle_qr(a[[3, 4]])
     assert harness.r_parity(r[[4]], r_ref[[1]]) <= 1e-4          # well conditioned: the usual bound
     assert harness.r_parity(r[[3]], r_ref[[0]]) <= 2e-3          # column pairs 1e-3 apart: R is determined to about 1e3 eps
+
+
+@pytest.mark.parametrize("shape", [(1500, 160), (3000, 64), (600, 96)])
+def test_panel_quads_with_nearly_dependent_columns(shape):
+    """The blocked QR's cluster panels take four columns a reduction: every step of a group is formed from sums taken
+    before the group's first step, and a column whose tail the group's earlier steps have nearly removed leaves the
+    group for single steps. Columns that copy an earlier column of their group (the third the first, the fourth the
+    second, all four the same) to 0 ... 0.3, and zero columns inside a group, exercise the first, second and third
+    step's guard."""
+    m, n = shape
+    rng = np.random.default_rng(m + 7 * n)
+    base = rng.standard_normal((m, n)).astype(np.float64)
+    mats = []
+    for eps in (0.0, 1e-6, 1e-3, 0.3):
+        for src, dst in ((0, 2), (1, 3), (0, 1)):
+            x = base.copy()
+            cols = x[:, dst::4].shape[1]
+            x[:, dst::4] = x[:, src::4][:, :cols] + eps * rng.standard_normal((m, cols))
+            mats.append(x)
+        x = base.copy()
+        for d in (1, 2, 3):
+            cols = x[:, d::4].shape[1]
+            x[:, d::4] = x[:, 0::4][:, :cols] + eps * rng.standard_normal((m, cols))
+        mats.append(x)
+    x = base.copy()
+    x[:, 9:11] = 0.0
+    x[:, 20:24] = 0.0
+    mats.append(x)
+    a = np.stack(mats).astype(np.float32)
+    q, r = gpu_qr(a, "reduced", kernel="blocked")
+    check(a, q, r, "reduced")
+    well = [12, 13, 14, 15]                                      # the groups 0.3 apart: the usual bound on R
+    _, r_ref = harness.oracle_qr(a[well])
+    assert harness.r_parity(r[well], r_ref) <= 1e-4
+    os.environ["QR_PANEL_QUADS"] = "0"
+    try:
+        q2, r2 = gpu_qr(a[well], "reduced", kernel="blocked")
+    finally:
+        os.environ.pop("QR_PANEL_QUADS", None)
+    assert harness.r_parity(r[well], r2) <= 1e-4
