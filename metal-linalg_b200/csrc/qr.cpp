@@ -183,11 +183,11 @@ QrKernel choose(mlb::DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t batch,
     if (small) return QrKernel::small;
     const bool spread = qr_gpu_backend(m, n, batch) == QrBackend::streaming_reduced;
     // a lone tall thin matrix of 64 columns or more is faster through the blocked QR's cluster panels where
-    // those hold its rows (8192 x 128: 0.59 ms against 1.56 ms; 4096 x 64: 0.22 against 0.31; 16384 x 64: 0.37
-    // against 0.42), and so are two of 128 columns (1.22 against 1.57; three: 1.8 against 1.57); two of 64 columns
-    // (4096 x 64: 0.43 against 0.31) and any of 32 (16384 x 32: 0.20 against 0.16) go to the tree, as every
-    // batch does (16 of 8192 x 128: 4.5 ms against 9.7 ms)
-    const uint32_t few = n >= 128 ? 2u : n >= 64 ? 1u : 0u;
+    // those hold its rows (8192 x 128: 0.37 ms against 1.43 ms; 4096 x 64: 0.19 against 0.22; 8192 x 64: 0.22
+    // against 0.27), and so are up to four of 128 columns (two: 0.71 against 1.43; four: 1.38 against 1.44); two of
+    // 64 columns (4096 x 64: 0.35 against 0.22) and any of 32 (16384 x 32: 0.21 against 0.15) go to the tree, as
+    // every larger batch does (16 of 8192 x 128: 5.4 ms against 2.1 ms)
+    const uint32_t few = n >= 128 ? 4u : n >= 64 ? 1u : 0u;
     const bool lone = batch <= few && mlb::panel_fast_fits(m, 1) && mlb::qr_blocked_fits(m, n);
     // the tree also takes the tall thin matrices a block could hold (512 to 1024 rows): its blocks of 256 rows
     // run the panels with a column per lane, which one block of more rows cannot (1024 x 64: 0.21 against 0.50 ms

@@ -709,7 +709,7 @@ def test_device_queries():
     assert mlt.qr_kernel(384, 384, 4) == "blocked" and mlt.qr_kernel(192, 192, 1) == "mid"
     assert mlt.qr_kernel(1024, 1024, 16) == "blocked" and mlt.qr_kernel(1024, 1024, 128) == "mid"
     assert mlt.qr_kernel(4096, 64, 1) == "blocked" and mlt.qr_kernel(4096, 64, 16) == "tsqr"
-    assert mlt.qr_kernel(8192, 128, 2) == "blocked" and mlt.qr_kernel(8192, 128, 3) == "tsqr"
+    assert mlt.qr_kernel(8192, 128, 4) == "blocked" and mlt.qr_kernel(8192, 128, 5) == "tsqr"
     assert mlt.qr_kernel(2048, 32, 2) == "tsqr" and mlt.qr_kernel(2048, 32, 1) == "tsqr" and mlt.qr_kernel(4096, 64, 2) == "tsqr"
     assert mlt.qr_kernel(1 << 20, 32, 1) == "tsqr" and mlt.qr_kernel(65536, 64, 64) == "tsqr"
     # tall thin matrices of 512 to 1024 rows go to the tree too, unless less than eight times as tall as wide
