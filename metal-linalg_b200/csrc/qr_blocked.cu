@@ -552,7 +552,9 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const bool tc = use_tensor_cores();
     // a narrow update (the look-ahead's) in short row chunks, so that it still fills the GPU
     const bool narrow = tc && nc <= 256;
-    const uint32_t rows = narrow ? 128u : tc ? 256u : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
+    const char* chunk_env = std::getenv("QR_TC_CHUNK");               // rows a block of the first wide product sums over (a multiple of 256)
+    const uint32_t wide_rows = chunk_env && std::atoi(chunk_env) >= 256 ? (uint32_t)std::atoi(chunk_env) / 256 * 256 : 256u;
+    const uint32_t rows = narrow ? 128u : tc ? wide_rows : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
     const uint32_t chunks = (mp + rows - 1) / rows;
     // QR_TC_SPLIT=0: the products whose blocks split their operands as they load them
     const char* split_env = std::getenv("QR_TC_SPLIT");

@@ -606,9 +606,10 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     else if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
     else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
+    // T straight to global memory by the warp that recorded tau and G; rows and columns from jb on are zero (their
+    // reflectors are the identity). Meanwhile block 0's first warp writes R and the other warps Y.
+    if (rank + 1 == ncta && warp == kWarps - 1) build_t_to(s, p.t, 32);
     if (rank == 0 && warp == 0) {
-        // T straight to global memory; rows and columns from jb on are zero (their reflectors are the identity)
-        build_t_to(s, p.t, 32);
         // the first 32 rows: R into the working copy, the reflectors with a unit diagonal into Y
 #pragma unroll 4
         for (int r = 0; r < 32; ++r) {

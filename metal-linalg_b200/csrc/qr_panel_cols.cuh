@@ -177,7 +177,9 @@ struct ClusterSync {
         return d;
     }
     __device__ __forceinline__ bool pivot(int warp) const { return rank == 0 && warp == 0; }
-    __device__ __forceinline__ bool leader(int warp) const { return rank == 0 && warp == 0; }
+    // every warp of the cluster holds the same sums: the one that records tau, sc and G (and builds T from them at the
+    // end) is the last warp of the last block, which has no pivot rows to look after and none of R to write
+    __device__ __forceinline__ bool leader(int warp) const { return rank + 1 == ncta && warp == kWarps - 1; }
     __device__ __forceinline__ void exchange(Smem& s, int buf, int lane, int warp) const {
         step_barrier(32 * kWarps);
         float d = s.red[buf][0][lane];
