@@ -580,6 +580,9 @@ template <int RW>
 __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanelParams p) {
     using namespace cols;
     dependency_wait();
+    // every block of the cluster must be running before any writes into another's shared memory: arrive now, wait
+    // after the loads, which hide the barrier's latency
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     __shared__ __align__(16) cols::Smem s;
     __shared__ __align__(16) cols::ClusterShared cs;
     __shared__ __align__(16) float pub[2 * kWarps * RW];
@@ -600,7 +603,7 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
         }
         x2[i] = pack(a, b);
     }
-    cluster_barrier();          // every block of the cluster is running before any writes into another's shared memory
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     float my_sc;
     if (p.pairs == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs});
     else if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
@@ -628,7 +631,8 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
             if ((!first || r >= 32) && row < p.mp) p.y[(size_t)row * p.ldy + lane] = row_of<RW>(x2, r) * my_sc;
         }
     }
-    cluster_barrier();          // no block leaves while another could still write into its shared memory
+    // (The last write into another block's shared memory was before the last step's cluster barrier: a block may
+    // leave as soon as its own stores are done.)
 }
 
 struct ApplyParams {
