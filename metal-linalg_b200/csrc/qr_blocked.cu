@@ -552,14 +552,18 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const bool tc = use_tensor_cores();
     // a narrow update (the look-ahead's) in short row chunks, so that it still fills the GPU
     const bool narrow = tc && nc <= 256;
-    const char* chunk_env = std::getenv("QR_TC_CHUNK");               // rows a block of the first wide product sums over (a multiple of 256)
-    const uint32_t wide_rows = chunk_env && std::atoi(chunk_env) >= 256 ? (uint32_t)std::atoi(chunk_env) / 256 * 256 : 256u;
-    const uint32_t rows = narrow ? 128u : tc ? wide_rows : (uint32_t)WCH;   // shorter accumulation chains on the tensor cores
-    const uint32_t chunks = (mp + rows - 1) / rows;
     // QR_TC_SPLIT=0: the products whose blocks split their operands as they load them
     const char* split_env = std::getenv("QR_TC_SPLIT");
     const bool split = tc && !narrow && ysp && zsp && ytsp && !(split_env && split_env[0] == '0');
-    if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, ytsp, error);
+    // rows a tensor-core accumulator sums over (the accumulation truncates: chains are kept short); the split-operand
+    // product's blocks take two such runs of rows each, in two accumulators (QR_TC_PAIR=0: one)
+    const char* chunk_env = std::getenv("QR_TC_CHUNK");
+    const uint32_t sub_rows = chunk_env && std::atoi(chunk_env) >= 256 ? (uint32_t)std::atoi(chunk_env) / 256 * 256 : 256u;
+    const char* pair_env = std::getenv("QR_TC_PAIR");
+    const uint32_t wide_rows = split && !(pair_env && pair_env[0] == '0') ? 2 * sub_rows : sub_rows;
+    const uint32_t rows = narrow ? 128u : tc ? wide_rows : (uint32_t)WCH;
+    const uint32_t chunks = (mp + rows - 1) / rows;
+    if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, sub_rows, ytsp, error);
     else if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
     if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 1024, kReduceNarrowSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);

@@ -232,26 +232,11 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
     __syncthreads();
     const bool ok = !failed;
     if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
-    if (ok) {   // C's tile into shared memory, a warp a row
-        if (out_vec) {
-#pragma unroll
-            for (int u = 0; u < 128 / (T2 / 32); ++u) {
-                const uint32_t r = warp + (T2 / 32) * u;
-                if (r < out_rows) *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = creg[u];
-            }
-        } else {
-            for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
-                const float* src = out_tile + (size_t)r * p.ldc + 4 * lane;
-                float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (4 * lane + 0 < n_valid) f.x = src[0];
-                if (4 * lane + 1 < n_valid) f.y = src[1];
-                if (4 * lane + 2 < n_valid) f.z = src[2];
-                if (4 * lane + 3 < n_valid) f.w = src[3];
-                *reinterpret_cast<float4*>(&Ct[r][4 * lane]) = f;
-            }
-        }
-        __syncthreads();
-        // warp w reads lanes 32 (w % 4) .. + 31 (its rows of the tile), columns 64 (w / 4) .. + 63
+    if (ok) {
+        // The product's tile from tensor memory into shared memory: warp w reads lanes 32 (w % 4) .. + 31 (its rows of the
+        // tile), columns 64 (w / 4) .. + 63, a row per lane, and stores 16-byte words (rows 528 bytes apart: the eight
+        // lanes of a quarter-warp fall into eight different groups of four banks). Entry by entry, subtracting in place,
+        // every access collided four ways.
         const uint32_t row = 32 * (warp & 3) + lane;
         const uint32_t c_base = 64 * (warp >> 2);
 #pragma unroll
@@ -269,22 +254,31 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
                          : "r"(taddr) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < 32; ++c) Ct[row][c0 + c] -= __uint_as_float(v[c]);
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(&Ct[row][c0 + 4 * q]) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (ok) {              // rows of the tile to global memory, a warp a row, 16 bytes a lane
-        for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
-            float* dst = out_tile + (size_t)r * p.ldc + 4 * lane;
-            const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
-            if (out_vec) {
-                *reinterpret_cast<float4*>(dst) = f;
-            } else {
+    if (ok) {              // C's rows minus the product's, to global memory, a warp a row, 16 bytes a lane
+        if (out_vec) {
+#pragma unroll
+            for (int u = 0; u < 128 / (T2 / 32); ++u) {
+                const uint32_t r = warp + (T2 / 32) * u;
+                if (r < out_rows) {
+                    const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
+                    *reinterpret_cast<float4*>(out_tile + (size_t)r * p.ldc + 4 * lane) =
+                        make_float4(creg[u].x - f.x, creg[u].y - f.y, creg[u].z - f.z, creg[u].w - f.w);
+                }
+            }
+        } else {
+            for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
+                float* dst = out_tile + (size_t)r * p.ldc + 4 * lane;
+                const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
                 const float e[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (4 * lane + i < n_valid) dst[i] = e[i];
+                    if (4 * lane + i < n_valid) dst[i] -= e[i];
             }
         }
     }
@@ -332,6 +326,7 @@ struct Ytc2Params {
     float*       zp;       // [chunks][128][ncp]
     size_t       ldc;
     uint32_t     mp, nc, ncp, chunk_rows;
+    uint32_t     sub_tiles;      // 16-row tiles per accumulator: the chunk's first sub_tiles tiles go to the first, the rest to the second
     unsigned*    error;
 };
 
@@ -363,7 +358,9 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" :: "r"(smem_u32(&tmem_base_slot)) : "memory");
+        // two accumulators of 128 columns: a chunk's rows are summed in two halves (the tensor core accumulates with
+        // truncation, so a chain is kept to sub_tiles tiles) and the halves are added once, in the epilogue
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" :: "r"(smem_u32(&tmem_base_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -435,16 +432,18 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
                 for (int h = 0; h < KS2 / 8; ++h) {
                     const uint64_t dah = make_desc2(a_hi + h * 2 * LBO2), dal = make_desc2(a_lo + h * 2 * LBO2);
                     const uint64_t dbh = make_desc_b(b_hi + h * 2 * LBOB), dbl = make_desc_b(b_lo + h * 2 * LBOB);
-                    const uint32_t acc0 = (kt > 0 || h > 0) ? 1u : 0u;
+                    const bool second = kt >= p.sub_tiles;
+                    const uint32_t tmem_acc = tmem_d + (second ? 128u : 0u);
+                    const uint32_t acc0 = ((second ? kt - p.sub_tiles : kt) > 0 || h > 0) ? 1u : 0u;
                     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                                 :: "r"(tmem_d), "l"(dal), "l"(dbh), "r"(kInstrDesc2), "r"(acc0) : "memory");
+                                 :: "r"(tmem_acc), "l"(dal), "l"(dbh), "r"(kInstrDesc2), "r"(acc0) : "memory");
                     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                                 :: "r"(tmem_d), "l"(dah), "l"(dbl), "r"(kInstrDesc2), "r"(1u) : "memory");
+                                 :: "r"(tmem_acc), "l"(dah), "l"(dbl), "r"(kInstrDesc2), "r"(1u) : "memory");
                     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                                 :: "r"(tmem_d), "l"(dah), "l"(dbh), "r"(kInstrDesc2), "r"(1u) : "memory");
+                                 :: "r"(tmem_acc), "l"(dah), "l"(dbh), "r"(kInstrDesc2), "r"(1u) : "memory");
                 }
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -476,8 +475,23 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
                            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                          : "r"(taddr) : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (tiles > p.sub_tiles) {      // the second half's sums
+                uint32_t w[32];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+                               "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15]),
+                               "=r"(w[16]), "=r"(w[17]), "=r"(w[18]), "=r"(w[19]), "=r"(w[20]), "=r"(w[21]), "=r"(w[22]), "=r"(w[23]),
+                               "=r"(w[24]), "=r"(w[25]), "=r"(w[26]), "=r"(w[27]), "=r"(w[28]), "=r"(w[29]), "=r"(w[30]), "=r"(w[31])
+                             : "r"(taddr + 128u) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < 32; ++c) Ct[row][c0 + c] = __uint_as_float(v[c]);
+                for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + __uint_as_float(w[c]));
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)      // 16-byte words: entry by entry the lanes' rows collide four ways
+                *reinterpret_cast<uint4*>(&Ct[row][c0 + 4 * q]) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -497,7 +511,7 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
             }
         }
     }
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" :: "r"(tmem_d) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_d) : "memory");
 }
 
 constexpr size_t kYz2Smem = (size_t)NS2 * STAGE2 + 1024;
@@ -527,9 +541,11 @@ void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const f
 size_t tc_split_t_floats(uint32_t rows) { return (size_t)((rows + 15) / 16) * kPairFloats; }
 
 // Zp[chunk][i][j] = sum over the chunk's rows of Y[r][i] C[r][j] with Y^T split first into ytsp
-// (tc_split_t_floats(mp) floats); chunk_rows a multiple of 16.
+// (tc_split_t_floats(mp) floats); chunk_rows a multiple of 16, at most twice sub_rows (a multiple of 16 too): a block
+// sums its chunk's first sub_rows rows in one accumulator of tensor memory, the rest in a second, and adds the two.
 void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp,
-                         uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, float* ytsp, unsigned* error) {
+                         uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, uint32_t sub_rows, float* ytsp,
+                         unsigned* error) {
     static PerDeviceOnce once;
     if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_ytc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYtc2Smem),
@@ -538,7 +554,7 @@ void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const 
     }
     const uint32_t words = 128 * 4 * ((mp + 15) / 16);
     launch_dependent(split_yt_kernel, (words + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, ytsp);
-    Ytc2Params p{ytsp, C, zp, ldc, mp, nc, ncp, chunk_rows, error};
+    Ytc2Params p{ytsp, C, zp, ldc, mp, nc, ncp, chunk_rows, sub_rows / KS2, error};
     launch_dependent(tc_ytc2_kernel, dim3((nc + 127) / 128, (mp + chunk_rows - 1) / chunk_rows), T2, kYtc2Smem, stream, p);
     cuda_check(cudaGetLastError(), "tc_ytc2 launch");
 }

@@ -241,7 +241,7 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0"])
+                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0", "QR_TC_PAIR=0"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
