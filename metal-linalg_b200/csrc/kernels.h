@@ -55,7 +55,7 @@ void launch_qr_mid(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p, 
 void   launch_qr_mid_static(int device, cudaStream_t stream, const QrProblem& p);
 size_t qr_mid_static_capacity_bytes();
 
-// A tall thin matrix as a tree of row blocks (explicit Q).
+// A tall thin matrix as a tree of row blocks (qr_tsqr.cu; at most 64 columns: qr_tsqr_vt.cu).
 bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc);
 void launch_qr_tsqr(DeviceContext& ctx, cudaStream_t stream, const QrProblem& p);
 

@@ -1,5 +1,8 @@
 // TSQR: a tall thin matrix (m >> n, n <= 128) as a tree of row blocks, for the
-// reduced factorisation and for R alone.
+// reduced factorisation and for R alone. This file holds the entry points and
+// the scheme with an explicit Q at every block, which takes 65 to 128 columns;
+// at most 64 columns go to qr_tsqr_vt.cu (blocks kept as reflectors, Q built
+// once on the way down), to which tsqr_core hands over.
 //
 // It takes the place of the reference's TSQR panel kernels bd_tsqr_leaf /
 // bd_tsqr_top / bd_tsqr_rebuild (shaders/Svd_Bidiag.metal:583-869; host side
