@@ -752,30 +752,33 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
     const uint32_t r_begin = blockIdx.y * IRB, r_end = min(mp, r_begin + IRB);
     const bool yvec = (ldy & 3) == 0 && jb == 32 && (reinterpret_cast<size_t>(Y) & 15) == 0;
     // Y's rows of this block go to shared memory once, by 16-byte asynchronous copies that are all in flight together
-    // (a thread's own rows: it alone reads them back, so its own wait is all the ordering they need), and serve both
-    // passes; C's entries stay in registers from the first pass to the second. (Read row by row from global memory, in
-    // both passes, the block waited for L2 eight times over.)
-    extern __shared__ __align__(16) float inner_ys[];       // [IRB / 256][256][kInnerYld]
+    // (eight consecutive lanes a row: whole 128-byte lines; a lane a row asked for every line eight times over), and
+    // serve both passes; C's entries stay in registers from the first pass to the second. (Read row by row from global
+    // memory, in both passes, the block waited for L2 eight times over.)
+    extern __shared__ __align__(16) float inner_ys[];       // [IRB][kInnerYld]: row r_begin + i at i * kInnerYld
     float cv[IRB / 256][ICS];
     if (yvec) {
-#pragma unroll
-        for (int i = 0; i < IRB / 256; ++i) {
-            const uint32_t r = r_begin + t + 256 * i;
+#pragma unroll 8
+        for (int i = 0; i < IRB * 8 / 256; ++i) {
+            const uint32_t idx = t + 256 * i, rl = idx >> 3, q = idx & 7, r = r_begin + rl;
             if (r < r_end) {
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(inner_ys + (size_t)(i * 256 + t) * kInnerYld);
-                const float* src = Y + (size_t)r * ldy;
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + 16 * q), "l"(src + 4 * q) : "memory");
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(inner_ys + (size_t)rl * kInnerYld + 4 * q);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(Y + (size_t)r * ldy + 4 * q) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    const bool cvec = (ldc & 3) == 0 && ncb == (uint32_t)ICS && ICS == 4 && (reinterpret_cast<size_t>(C + c0) & 15) == 0;
 #pragma unroll
     for (int i = 0; i < IRB / 256; ++i) {
         const uint32_t r = r_begin + t + 256 * i;
+        if (cvec) {
+            const float4 f = r < r_end ? *reinterpret_cast<const float4*>(C + (size_t)r * ldc + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+            cv[i][0] = f.x; cv[i][1] = f.y; cv[i][2] = f.z; cv[i][3] = f.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < ICS; ++j) cv[i][j] = (r < r_end && (uint32_t)j < ncb) ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+            for (int j = 0; j < ICS; ++j) cv[i][j] = (r < r_end && (uint32_t)j < ncb) ? C[(size_t)r * ldc + c0 + j] : 0.0f;
+        }
     }
     float tv[4];                                            // T on its way to shared memory while Z is formed
 #pragma unroll
@@ -785,7 +788,10 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
     for (int k = 0; k < 32; ++k)
 #pragma unroll
         for (int j = 0; j < ICS; ++j) z[k][j] = 0.0f;
-    if (yvec) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (yvec) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();      // a row's eight words came from eight threads
+    }
 #pragma unroll
     for (int i = 0; i < IRB / 256; ++i) {
         const uint32_t r = r_begin + t + 256 * i;
@@ -865,9 +871,14 @@ __global__ void __launch_bounds__(256) inner_fused_kernel(const float* __restric
             for (int k = 0; k < 32; ++k)
 #pragma unroll
                 for (int j = 0; j < ICS; ++j) d[j] = fmaf(y[k], w[k][j], d[j]);
+            if (cvec) {
+                *reinterpret_cast<float4*>(C + (size_t)r * ldc + c0) =
+                    make_float4(cv[i][0] - d[0], cv[i][1] - d[1], cv[i][2] - d[2], cv[i][3] - d[3]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < ICS; ++j)
-                if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] = cv[i][j] - d[j];
+                for (int j = 0; j < ICS; ++j)
+                    if ((uint32_t)j < ncb) C[(size_t)r * ldc + c0 + j] = cv[i][j] - d[j];
+            }
         }
     }
 }
