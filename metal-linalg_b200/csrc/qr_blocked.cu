@@ -1073,12 +1073,13 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
         // inside the aggregate only: the next aggregate's first panel waits for the last of the third stream's inner
         // updates, not for the Gram matrix, the merge of the T's and a rank-128 update behind them.
         // It costs more work in all (four inner updates of 128 columns an aggregate beside the rank-128 update), so it
-        // is for a matrix whose chain of panels is what bounds it: one matrix of at most 5632 rows, 7168 when no Q is
-        // formed (one B200, ms, by panels / by aggregates: 1024^2 1.38 / 1.73, 2048^2 3.05 / 3.73, 4096^2 7.90 / 9.17,
-        // 5120^2 12.3 / 12.8, 6144^2 17.9 / 17.6 and R alone 13.2 / 14.4, 8192^2 34.1 / 31.7 and R alone 22.1 / 22.1,
-        // eight 4096^2 47.0 / 37.8). QR_LOOK_PANELS=1 asks for it everywhere.
+        // is for a matrix whose chain of panels is what bounds it: one matrix of at most 6144 rows, or whose wide
+        // updates are light (no Q to accumulate, or at most 4096 columns of A and Q). One B200, ms, by panels / by
+        // aggregates: 1024^2 1.19 / 1.55, 2048^2 2.53 / 3.23, 4096^2 6.61 / 7.64, 5120^2 10.5 / 11.2, 6144^2 15.5 / 15.6,
+        // 8192^2 30.2 / 28.7 but R alone 17.9 / 19.3 and 8192 x 2048 5.63 / 6.01; eight 4096^2 42.0 / 35.1.
+        // QR_LOOK_PANELS=1 asks for it everywhere, =0 nowhere.
         const char* deep_env = std::getenv("QR_LOOK_PANELS");
-        const bool deep = two && (deep_env ? deep_env[0] != '0' : (nlanes == 1 && m <= (qc ? 5632u : 7168u)));
+        const bool deep = two && (deep_env ? deep_env[0] != '0' : (nlanes == 1 && (m <= 6144 || qc == 0 || std::max(n, qc) <= 4096)));
         const cudaStream_t ls = look_stream;
         if (deep) cuda_check(cudaStreamWaitEvent(ls, ev_update[1], 0), "cudaStreamWaitEvent");       // the working copy is ready
         for (uint32_t ag = 0; ag < naggs; ++ag) {
