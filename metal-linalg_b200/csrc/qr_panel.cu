@@ -576,7 +576,9 @@ struct ClusterPanelParams {
     int      pairs;     // 1: two columns a reduction (factor_cols2); 2: four (factor_cols4); 0: one
 };
 
-template <int RW>
+// MODE: the columns a reduction (0: one, 1: two, 2: four), a kernel each: one kernel holding all three was larger and
+// slower on every path.
+template <int RW, int MODE>
 __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanelParams p) {
     using namespace cols;
     dependency_wait();
@@ -605,8 +607,8 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     }
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     float my_sc;
-    if (p.pairs == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs});
-    else if (p.pairs) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
+    if constexpr (MODE == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs});
+    else if constexpr (MODE == 1) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
     else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
     // T straight to global memory by the warp that recorded tau and G; rows and columns from jb on are zero (their
@@ -730,22 +732,19 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
         uint32_t ncta = 1;
         while (ncta * 8 * rw < mp) ncta *= 2;       // 1, 2, 4, 8 (or 16) blocks; blocks beyond the rows hold zeros
         {
-            static PerDeviceOnce once_smem;      // static and dynamic shared memory together pass the 48 KB that need no opt-in
-            if (const int device = current_device(); once_smem.first(device)) {
-                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 32 * sizeof(float))), "panel_cluster shared memory");
-                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 64 * sizeof(float))), "panel_cluster shared memory");
-                once_smem.mark(device);
-            }
-        }
-        if (ncta > 8) {
-            static PerDeviceOnce once;
+            static PerDeviceOnce once;      // per GPU: the four-column kernels' static and dynamic shared memory together pass the
+                                            // 48 KB that need no opt-in; sixteen blocks are a cluster of the non-portable size
             if (const int device = current_device(); once.first(device)) {
-                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
-                           "panel_cluster non-portable cluster size");
-                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<64>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
-                           "panel_cluster non-portable cluster size");
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 32 * sizeof(float))), "panel_cluster shared memory");
+                cuda_check(cudaFuncSetAttribute(panel_cluster_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(sizeof(cols::QuadShared) + 4 * cols::kWarps * 64 * sizeof(float))), "panel_cluster shared memory");
+                const auto big = [](auto kernel) {
+                    cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                               "panel_cluster non-portable cluster size");
+                };
+                big(panel_cluster_kernel<32, 0>); big(panel_cluster_kernel<32, 1>); big(panel_cluster_kernel<32, 2>);
+                big(panel_cluster_kernel<64, 0>); big(panel_cluster_kernel<64, 1>); big(panel_cluster_kernel<64, 2>);
                 once.mark(device);
             }
         }
@@ -768,8 +767,10 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = dependent_launches_enabled() ? 2 : 1;
-        if (rw == 32) cuda_check(cudaLaunchKernelEx(&cfg, panel_cluster_kernel<32>, cp), "panel_cluster launch");
-        else cuda_check(cudaLaunchKernelEx(&cfg, panel_cluster_kernel<64>, cp), "panel_cluster launch");
+        using Kernel = void (*)(ClusterPanelParams);
+        static const Kernel kernels[2][3] = {{panel_cluster_kernel<32, 0>, panel_cluster_kernel<32, 1>, panel_cluster_kernel<32, 2>},
+                                             {panel_cluster_kernel<64, 0>, panel_cluster_kernel<64, 1>, panel_cluster_kernel<64, 2>}};
+        cuda_check(cudaLaunchKernelEx(&cfg, kernels[rw == 64][pairs], cp), "panel_cluster launch");
         return;
     }
     LeafParams lp{panel, ldw, mp, jb, lr, Vl, Tl, Sl};
