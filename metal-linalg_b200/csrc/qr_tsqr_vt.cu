@@ -526,12 +526,13 @@ struct DownParams {
 };
 
 // acc (rows 4 rg ..., columns 4 cg ... of a 64 x 64 product, a thread of 256) = op(A) B for A, B in shared memory
+// (k_from: op(A)'s rows 4 rg ... are zero left of it: V1^T and T are upper triangular, so a thread starts at its own rows)
 template <bool TA>
-__device__ __forceinline__ void mm64(const float* A, const float* B, pair_t (&acc)[4][2], int rg, int cg) {
+__device__ __forceinline__ void mm64(const float* A, const float* B, pair_t (&acc)[4][2], int rg, int cg, int k_from = 0) {
 #pragma unroll
     for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = pack(0.0f, 0.0f);
 #pragma unroll 2
-    for (int k0 = 0; k0 < 64; k0 += 4) {
+    for (int k0 = k_from; k0 < 64; k0 += 4) {
         float4 x[4];
         if (TA) {
 #pragma unroll
@@ -664,10 +665,10 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
     __syncthreads();
     {
         pair_t acc[4][2];
-        mm64<true>(Vs, Bs, acc, rg, cg);          // rows of B beyond n are zero, so only V1 = V's first n rows count
+        mm64<true>(Vs, Bs, acc, rg, cg, 4 * rg);  // rows of B beyond n are zero, so only V1 = V's first n rows count
         store_acc(Xs, acc, rg, cg);
         __syncthreads();
-        mm64<false>(Ts, Xs, acc, rg, cg);
+        mm64<false>(Ts, Xs, acc, rg, cg, 4 * rg);
         store_acc(Ws, acc, rg, cg);
     }
     __syncthreads();
