@@ -557,25 +557,31 @@ __device__ __forceinline__ void mm64(const float* A, const float* B, pair_t (&ac
     }
 }
 
-// The same for 128 rows of A at once: a thread holds rows 4 rg + a and 64 + 4 rg + a (a < 4), so that a word of B
-// read from shared memory serves eight rows (the shared-memory pipe, not the FMA pipe, is what bounds these loops).
-__device__ __forceinline__ void mm128(const float* A, const float* B, pair_t (&acc)[8][2], int rg, int cg) {
+// The large product: 256 rows of A at once, a thread 8 rows (8 rg ...) x 8 columns (4 cg ... and 32 + 4 cg ...): a word
+// of B read from shared memory serves eight rows and a word of A eight columns (the path from shared memory into the
+// registers, not the FMA pipe, is what bounds these loops: 16 words for 128 packed FMAs here, 8 for 32 in mm64).
+__device__ __forceinline__ void mm256(const float* A, const float* B, pair_t (&acc)[8][4], int rg, int cg) {
 #pragma unroll
-    for (int a = 0; a < 8; ++a) acc[a][0] = acc[a][1] = pack(0.0f, 0.0f);
-#pragma unroll 2
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int h = 0; h < 4; ++h) acc[a][h] = pack(0.0f, 0.0f);
+#pragma unroll 1
     for (int k0 = 0; k0 < 64; k0 += 4) {
         float4 x[8];
 #pragma unroll
-        for (int a = 0; a < 8; ++a) x[a] = *reinterpret_cast<const float4*>(A + ((a >> 2) * 64 + 4 * rg + (a & 3)) * LD + k0);
+        for (int a = 0; a < 8; ++a) x[a] = *reinterpret_cast<const float4*>(A + (8 * rg + a) * LD + k0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-            const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(B + (k0 + kk) * LD + 4 * cg);
+            const ulonglong2 w0 = *reinterpret_cast<const ulonglong2*>(B + (k0 + kk) * LD + 4 * cg);
+            const ulonglong2 w1 = *reinterpret_cast<const ulonglong2*>(B + (k0 + kk) * LD + 32 + 4 * cg);
 #pragma unroll
             for (int a = 0; a < 8; ++a) {
                 const float xv = kk == 0 ? x[a].x : kk == 1 ? x[a].y : kk == 2 ? x[a].z : x[a].w;
                 const pair_t xx = pack(xv, xv);
-                acc[a][0] = fma2(xx, w.x, acc[a][0]);
-                acc[a][1] = fma2(xx, w.y, acc[a][1]);
+                acc[a][0] = fma2(xx, w0.x, acc[a][0]);
+                acc[a][1] = fma2(xx, w0.y, acc[a][1]);
+                acc[a][2] = fma2(xx, w1.x, acc[a][2]);
+                acc[a][3] = fma2(xx, w1.y, acc[a][3]);
             }
         }
     }
@@ -613,10 +619,10 @@ constexpr int kDownSmem = (4 * 64 + 128) * LD * (int)sizeof(float);
 __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams p) {
     extern __shared__ __align__(16) float down_sm[];
     float* Bs = down_sm;                 // B, zeros beyond n
-    float* Ts = Bs + 64 * LD;
+    float* Ws = Bs + 64 * LD;            // T (V1^T B)
+    float* Vs = Ws + 64 * LD;            // V's rows 0 .. 127, and behind them, once T and V1^T B are done with, rows 128 .. 255
+    float* Ts = Vs + 128 * LD;
     float* Xs = Ts + 64 * LD;            // V1^T B
-    float* Ws = Xs + 64 * LD;            // T (V1^T B)
-    float* Vs = Ws + 64 * LD;            // 128 rows of V
     const int t = threadIdx.x, rg = t >> 4, cg = t & 15;
     const int n = p.n;
     const unsigned i = blockIdx.x % p.blocks;
@@ -662,6 +668,14 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
             *reinterpret_cast<float4*>(Vs + r * LD + 4 * q) = fv[k];
         }
     }
+    float4 fn[8];       // rows 128 .. 255 of V, fetched under the two small products
+    if (nrows > 128) {
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8) {
+            const int idx = t + kThreads * q8, r = idx >> 4, q = idx & 15;
+            fn[q8] = fetch4(V, n, nrows, 128u + (unsigned)r, q, vec);
+        }
+    }
     __syncthreads();
     {
         pair_t acc[4][2];
@@ -672,49 +686,44 @@ __global__ void __launch_bounds__(kThreads, 2) tsqr_down_kernel(const DownParams
         store_acc(Ws, acc, rg, cg);
     }
     __syncthreads();
-    for (unsigned r0 = 0; r0 < nrows; r0 += 128) {
-        const bool more = r0 + 128 < nrows;
-        float4 fn[8];       // the next 128 rows, fetched under this product
-        if (more) {
+    // V's rows 128 .. 255 take T's and X's place (fetched under the two small products)
+    if (nrows > 128) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
-                fn[k] = fetch4(V, n, nrows, r0 + 128 + (unsigned)r, q, vec);
-            }
+        for (int q8 = 0; q8 < 8; ++q8) {
+            const int idx = t + kThreads * q8, r = idx >> 4, q = idx & 15;
+            *reinterpret_cast<float4*>(Ts + r * LD + 4 * q) = fn[q8];
         }
-        pair_t acc[8][2];
-        mm128(Vs, Ws, acc, rg, cg);
+        __syncthreads();
+    }
+    {
+        const int rg8 = t >> 3, cg8 = t & 7;
+        pair_t acc[8][4];
+        mm256(Vs, Ws, acc, rg8, cg8);
 #pragma unroll
         for (int a = 0; a < 8; ++a) {
-            const unsigned r = r0 + (a >> 2) * 64 + 4 * rg + (a & 3);
+            const unsigned r = 8 * rg8 + a;
             if (r >= nrows) continue;
-            float o[4];
-            unpack(acc[a][0], o[0], o[1]);
-            unpack(acc[a][1], o[2], o[3]);
-            const int c = 4 * cg;
-            if (r0 == 0 && a < 4) {
-                const float4 bv = *reinterpret_cast<const float4*>(Bs + (4 * rg + a) * LD + c);
-                o[0] = bv.x - o[0]; o[1] = bv.y - o[1]; o[2] = bv.z - o[2]; o[3] = bv.w - o[3];
-            } else {
-                o[0] = -o[0]; o[1] = -o[1]; o[2] = -o[2]; o[3] = -o[3];
-            }
-            float* dst = V + (size_t)r * n + c;
-            if (vec && c + 3 < n) {
-                *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
-            } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (c + e < n) dst[e] = o[e];
-            }
-        }
-        if (more) {
-            __syncthreads();      // the rows have been read: the next ones may overwrite them
+            for (int h = 0; h < 2; ++h) {
+                float o[4];
+                unpack(acc[a][2 * h], o[0], o[1]);
+                unpack(acc[a][2 * h + 1], o[2], o[3]);
+                const int c = 32 * h + 4 * cg8;
+                if (r < 64) {
+                    const float4 bv = *reinterpret_cast<const float4*>(Bs + r * LD + c);
+                    o[0] = bv.x - o[0]; o[1] = bv.y - o[1]; o[2] = bv.z - o[2]; o[3] = bv.w - o[3];
+                } else {
+                    o[0] = -o[0]; o[1] = -o[1]; o[2] = -o[2]; o[3] = -o[3];
+                }
+                float* dst = V + (size_t)r * n + c;
+                if (vec && c + 3 < n) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int idx = t + kThreads * k, r = idx >> 4, q = idx & 15;
-                *reinterpret_cast<float4*>(Vs + r * LD + 4 * q) = fn[k];
+                    for (int e = 0; e < 4; ++e)
+                        if (c + e < n) dst[e] = o[e];
+                }
             }
-            __syncthreads();
         }
     }
 }
