@@ -316,6 +316,10 @@ bool qr_tsqr_fits(const DeviceContext& ctx, uint32_t m, uint32_t n, uint32_t qc)
     // reduced or R alone (Q of n columns or none), at most 128 columns, at least two levels' worth of rows
     // reduced or R alone (Q of n columns or none), at most 128 columns, at least two blocks of rows and eight times
     // as tall as wide (640 x 96 is faster in one block; 512 x 64 and 1024 x 128 are faster here)
+    // with at most 64 columns the blocks are kept as reflectors (qr_tsqr_vt.cu), and one such block, or two, already beats
+    // the general block kernel where a block of 256 rows is filled to three quarters (16384 of 256 x 64: 4.4 against
+    // 5.9 ms; 8192 of 500 x 48: 6.3 against 10.6; 16384 of 200 x 40: 4.2 against 5.3; but 16384 of 128 x 64: 4.3 against 3.7)
+    if (n >= 1 && n <= 64 && m >= 192 && m >= 3 * n && (qc == 0 || qc == n) && tsqr_vt_takes(m, n)) return true;
     return n >= 1 && n <= 128 && m >= 512 && m >= 8 * n && (qc == 0 || qc == n) && qr_mid_fits(ctx, 1024, n);
 }
 

@@ -783,14 +783,14 @@ void launch_leaf(cudaStream_t stream, const LeafParams& lp, uint64_t grid) {
 
 bool tsqr_vt_takes(uint32_t m, uint32_t n) {
     const char* e = std::getenv("QR_TSQR_VT");
-    return n >= 1 && n <= 64 && m > (uint32_t)kBlockRows && !(e && e[0] == '0');
+    return n >= 1 && n <= 64 && m >= n && !(e && e[0] == '0');      // (at most 256 rows: one block, no tree)
 }
 
 size_t tsqr_vt_workspace_floats(uint32_t m, uint32_t n, uint32_t batch, bool want_q) {
     return vt_layout(m, n, batch, want_q).total;
 }
 
-// Thin QR of `batch` matrices of m x n (n <= 64, m > 256) read with row stride lda and matrix stride a_outer:
+// Thin QR of `batch` matrices of m x n (n <= 64, m >= n) read with row stride lda and matrix stride a_outer:
 // q [batch][m][n] contiguous (null: R alone), r [batch] n x n at stride r_outer.
 void tsqr_vt_core(cudaStream_t stream, const float* a, uint32_t lda, uint64_t a_outer, uint32_t m, uint32_t n,
                   uint32_t batch, float* q, float* r, uint64_t r_outer, float* ws) {

@@ -171,6 +171,21 @@ def test_tsqr_short_last_blocks(shape, mode):
     check(a, q, r, mode, r_ref)
 
 
+@pytest.mark.parametrize("mode", ["reduced", "r"])
+@pytest.mark.parametrize("shape", [(256, 64), (192, 64), (200, 40), (255, 33), (384, 64), (500, 48), (300, 7), (257, 64), (511, 1)])
+def test_tsqr_one_and_two_blocks(shape, mode):
+    """With at most 64 columns a matrix of 192 to 511 rows goes to the tree of blocks kept as reflectors too: one block
+    (no tree at all) up to 256 rows, two beyond (257 x 64: a second block of one row takes 63 from the first)."""
+    m, n = shape
+    assert mlt.qr_kernel(m, n, 64, mode) == "tsqr" and mlt.qr_kernel(m, n, 1, mode) == "tsqr"
+    rng = np.random.default_rng(5 * m + n)
+    a = rng.standard_normal((5, m, n)).astype(np.float32)
+    a[3] *= 1e-20
+    q, r = gpu_qr(a, mode)
+    _, r_ref = harness.oracle_qr(a, mode)
+    check(a, q, r, mode, r_ref)
+
+
 @pytest.mark.parametrize("shape", [(512, 64), (5000, 33), (4096, 16)])
 def test_tsqr_older_scheme_behind_its_switch(shape):
     """QR_TSQR_VT=0: blocks through the general block kernel with an explicit Q at every block (the scheme that
@@ -716,6 +731,10 @@ def test_device_queries():
     assert mlt.qr_kernel(1024, 64, 16) == "tsqr" and mlt.qr_kernel(512, 32, 1) == "tsqr" and mlt.qr_kernel(640, 96, 16) == "mid"
     assert mlt.qr_kernel(1024, 128, 1) == "blocked" and mlt.qr_kernel(1024, 64, 16, "complete") == "mid"
     assert mlt.qr_kernel(128, 128, 1) == "mid" and mlt.qr_kernel(4096, 4096, 64) == "blocked"
+    # at most 64 columns and at least 192 rows (three times the columns): the tree of blocks kept as reflectors, even as one block
+    assert mlt.qr_kernel(256, 64, 1000) == "tsqr" and mlt.qr_kernel(200, 40, 8) == "tsqr" and mlt.qr_kernel(384, 64, 1) == "tsqr"
+    assert mlt.qr_kernel(128, 64, 1000) == "mid" and mlt.qr_kernel(191, 40, 8) == "mid" and mlt.qr_kernel(256, 65, 8) == "mid"
+    assert mlt.qr_kernel(256, 64, 8, "complete") == "mid"
 
 
 # ---------------------------------------------------------------------------
