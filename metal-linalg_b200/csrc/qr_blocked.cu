@@ -559,8 +559,12 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     // product's blocks take two such runs of rows each, in two accumulators (QR_TC_PAIR=0: one)
     const char* chunk_env = std::getenv("QR_TC_CHUNK");
     const uint32_t sub_rows = chunk_env && std::atoi(chunk_env) >= 256 ? (uint32_t)std::atoi(chunk_env) / 256 * 256 : 256u;
+    // ... where that still leaves two waves of blocks (two a multiprocessor): at 4096 x 4096 the halved grid is a single
+    // wave of longer blocks and the product takes 37 instead of 29 us
     const char* pair_env = std::getenv("QR_TC_PAIR");
-    const uint32_t wide_rows = split && !(pair_env && pair_env[0] == '0') ? 2 * sub_rows : sub_rows;
+    const bool pair = split && (pair_env ? pair_env[0] != '0'
+                                         : (uint64_t)((mp + 2 * sub_rows - 1) / (2 * sub_rows)) * ((nc + 127) / 128) >= 4 * 148);
+    const uint32_t wide_rows = pair ? 2 * sub_rows : sub_rows;
     const uint32_t rows = narrow ? 128u : tc ? wide_rows : (uint32_t)WCH;
     const uint32_t chunks = (mp + rows - 1) / rows;
     if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, sub_rows, ytsp, error);
