@@ -96,7 +96,7 @@ size_t tc_split_floats(uint32_t extent);
 size_t tc_split_t_floats(uint32_t rows);
 void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp,
                          uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, uint32_t sub_rows, float* ytsp,
-                         unsigned* error);
+                         unsigned* error, float* ysp = nullptr);
 void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
                         uint32_t mp, uint32_t kw, uint32_t nc, float* ysp, float* zsp, unsigned* error);
 

@@ -32,6 +32,7 @@
 // read it as a plain matrix.
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_split.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -253,9 +254,11 @@ __global__ void __launch_bounds__(256) ytc_wide_kernel(const float* __restrict__
 
 // Z[i][j] = sum_k op(T)[i][k] (sum_chunks Zp[chunk][k][j]), T 128 x 128. Grid ceil(nc / 32).
 // Dynamic shared memory: op(T) transposed [128][132] and the summed chunks [128][36].
+// zsp non-null: the result goes out split into its tf32 parts, in the layout the second product's bulk copies fetch
+// (the stages of its kw rows), instead of as Z: a thread holds four consecutive rows of four columns, a word each.
 __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restrict__ Zp, uint32_t chunks, uint32_t nc,
                                                             uint32_t ncp, const float* __restrict__ T, int transposed,
-                                                            float* Z) {
+                                                            float* Z, float* zsp, uint32_t kw) {
     dependency_wait_only();
     extern __shared__ __align__(16) float dsm[];
     float (*Tt)[132] = reinterpret_cast<float (*)[132]>(dsm);                // Tt[k][i] = op(T)[i][k]
@@ -322,6 +325,19 @@ __global__ void __launch_bounds__(256) reduce_t_wide_kernel(const float* __restr
         for (int a = 0; a < 4; ++a)
 #pragma unroll
             for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(tv[a], zv[b], acc[a][b]);
+    }
+    if (zsp) {
+        const uint32_t stages = (kw + tcsplit::kStageK - 1) / tcsplit::kStageK, k0 = 4 * ig;
+        if (k0 < tcsplit::kStageK * stages) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t j = j0 + 4 * jg + b;
+                const float v[4] = {k0 < kw ? acc[0][b] : 0.0f, k0 + 1 < kw ? acc[1][b] : 0.0f, k0 + 2 < kw ? acc[2][b] : 0.0f,
+                                    k0 + 3 < kw ? acc[3][b] : 0.0f};      // rows from kw on are zero
+                if (j < nc) tcsplit::store_word(zsp, stages, j, (uint32_t)ig, v);
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int a = 0; a < 4; ++a)
@@ -567,12 +583,13 @@ void apply_aggregate(cudaStream_t stream, const float* Y, size_t ldy, const floa
     const uint32_t wide_rows = pair ? 2 * sub_rows : sub_rows;
     const uint32_t rows = narrow ? 128u : tc ? wide_rows : (uint32_t)WCH;
     const uint32_t chunks = (mp + rows - 1) / rows;
-    if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, sub_rows, ytsp, error);
+    if (split) launch_tc_ytc_split(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, sub_rows, ytsp, error, ysp);      // both splits of Y
     else if (tc) launch_tc_ytc(stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp, rows, error);
     else launch_dependent(ytc_wide_kernel, dim3((nc + 127) / 128, chunks), 256, 0, stream, Y, ldy, C, ldc, mp, kw, nc, zp, ncp);
     if (narrow) launch_dependent(reduce_t_narrow_kernel, (nc + 7) / 8, 1024, kReduceNarrowSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z);
-    if (split) launch_tc_yz_split(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, ysp, zsp, error);
+    else launch_dependent(reduce_t_wide_kernel, (nc + 31) / 32, 256, kReduceWideSmem, stream, zp, chunks, nc, ncp, T, transposed ? 1 : 0, z,
+                          split ? zsp : (float*)nullptr, kw);
+    if (split) launch_tc_yz_split(stream, (const float*)nullptr, ldy, (const float*)nullptr, ncp, C, ldc, mp, kw, nc, ysp, zsp, error);
     else if (tc) launch_tc_yz(stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc, error);
     else launch_dependent(yz_wide_kernel, dim3((nc + 127) / 128, (mp + 127) / 128), 256, 0, stream, Y, ldy, z, ncp, C, ldc, mp, kw, nc);
     cuda_check(cudaGetLastError(), "aggregate reflector launch");

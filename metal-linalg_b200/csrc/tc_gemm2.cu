@@ -27,22 +27,25 @@
 // become NaN) and the block leaves without touching C.
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_split.cuh"
 
 namespace mlb {
 
 namespace {
 
 constexpr int      T2     = 256;                  // threads
-constexpr int      KS2    = 16;                   // K values a stage
-constexpr int      TILE2  = 128 * KS2 * 4;        // bytes of a 128 x 16 tf32 operand tile (8 KB)
+constexpr int      KS2    = tcsplit::kStageK;     // K values a stage
+constexpr int      TILE2  = tcsplit::kTileBytes;  // bytes of a 128 x 16 tf32 operand tile (8 KB)
 constexpr int      HALF2  = 2 * TILE2;            // hi and lo of one operand
 constexpr int      STAGE2 = 2 * HALF2;            // A hi, A lo, B hi, B lo (32 KB)
 constexpr int      NS2    = 3;                    // stages in flight
-constexpr int      LBO2   = 128 * 16;             // bytes between the 16-byte K words of a tile
-constexpr int      SBO2   = 128;                  // bytes between groups of eight rows
+constexpr int      LBO2   = tcsplit::kLbo;        // bytes between the 16-byte K words of a tile
+constexpr int      SBO2   = tcsplit::kSbo;        // bytes between groups of eight rows
 constexpr int      CLD2   = 132;                  // leading dimension of C's tile in shared memory
 constexpr uint32_t kSpin2 = 1u << 22;
-constexpr uint32_t kPairFloats = HALF2 / 4;       // floats of a (tile, stage): hi then lo
+constexpr uint32_t kPairFloats = tcsplit::kPairFloats;       // floats of a (tile, stage): hi then lo
+using tcsplit::split4;
+using tcsplit::word_offset;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -62,23 +65,6 @@ __device__ __forceinline__ bool wait_barrier2(uint32_t bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
-}
-
-__device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& lo) {
-    float h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t b;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(v[i]));
-        h[i] = __uint_as_float(b);
-        l[i] = v[i] - h[i];
-    }
-    hi = make_float4(h[0], h[1], h[2], h[3]);
-    lo = make_float4(l[0], l[1], l[2], l[3]);
-}
-// float offset of the word (mn, four K values from 4 * kq) inside a (tile, stage)'s hi part
-__device__ __forceinline__ uint32_t word_offset(uint32_t mn, uint32_t kq) {
-    return kq * (LBO2 / 4) + (mn >> 3) * (SBO2 / 4) + (mn & 7) * 4;
 }
 
 // A thread a word: row r of Y, columns 4 q ... 4 q + 3. Rows from mp on and columns from kw on are zero.
@@ -306,6 +292,34 @@ __global__ void __launch_bounds__(256) split_yt_kernel(const float* __restrict__
     *reinterpret_cast<float4*>(dst + TILE2 / 4) = lo;
 }
 
+// Both splits of Y in one launch (the two products of an update need one each): the first blocks_t blocks do
+// split_yt_kernel's work, the rest split_y_kernel's.
+__global__ void __launch_bounds__(256) split_y_both_kernel(const float* __restrict__ Y, size_t ldy, uint32_t mp, uint32_t kw,
+                                                           uint32_t stages, float* __restrict__ ysp, float* __restrict__ ytsp,
+                                                           uint32_t blocks_t) {
+    dependency_wait_only();
+    float v[4];
+    if (blockIdx.x < blocks_t) {
+        const uint32_t idx = blockIdx.x * 256 + threadIdx.x;
+        const uint32_t c = idx & 127, q = idx >> 7;               // q: group of four rows
+        if (q >= 4 * ((mp + 15) / 16)) return;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (4 * q + i < mp && c < kw) ? Y[(size_t)(4 * q + i) * ldy + c] : 0.0f;
+        float4 hi, lo;
+        split4(v, hi, lo);
+        float* dst = ytsp + (size_t)(q / 4) * kPairFloats + word_offset(c, q % 4);
+        *reinterpret_cast<float4*>(dst) = hi;
+        *reinterpret_cast<float4*>(dst + TILE2 / 4) = lo;
+    } else {
+        const uint32_t idx = (blockIdx.x - blocks_t) * 256 + threadIdx.x;
+        const uint32_t q = idx % (4 * stages), r = idx / (4 * stages);
+        if (r >= (mp + 127) / 128 * 128) return;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (r < mp && 4 * q + i < kw) ? Y[(size_t)r * ldy + 4 * q + i] : 0.0f;
+        tcsplit::store_word(ysp, stages, r, q, v);
+    }
+}
+
 // B tiles written by threads: padded one word per K column so that the stores do not collide
 constexpr int LBOB  = 16 * 128 + 16;
 constexpr int TILEB = (KS2 / 4) * LBOB;           // bytes of one 128 x 16 thread-written tile
@@ -521,7 +535,8 @@ constexpr size_t kYz2Smem = (size_t)NS2 * STAGE2 + 1024;
 size_t tc_split_floats(uint32_t extent) { return (size_t)((extent + 127) / 128) * 8 * kPairFloats; }
 
 // C[r][j] -= sum_k Y[r][k] Z[k][j], k < kw <= 128, with Y and Z split first into ysp and zsp (scratch
-// of tc_split_floats(mp) and tc_split_floats(nc) floats).
+// of tc_split_floats(mp) and tc_split_floats(nc) floats). Z null: zsp holds Z's split already (its
+// producer wrote it: tc_split.cuh), for the stages of kw; Y null: ysp holds Y's (launch_tc_ytc_split made it).
 void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const float* Z, uint32_t ncp, float* C, size_t ldc,
                         uint32_t mp, uint32_t kw, uint32_t nc, float* ysp, float* zsp, unsigned* error) {
     static PerDeviceOnce once;      // the opt-in is recorded per GPU
@@ -531,8 +546,8 @@ void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const f
         once.mark(device);
     }
     const uint32_t stages = (kw + KS2 - 1) / KS2, rtiles = (mp + 127) / 128, ctiles = (nc + 127) / 128;
-    launch_dependent(split_y_kernel, (rtiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, stages, ysp);
-    launch_dependent(split_z_kernel, (ctiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Z, (size_t)ncp, kw, nc, stages, zsp);
+    if (Y) launch_dependent(split_y_kernel, (rtiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, stages, ysp);
+    if (Z) launch_dependent(split_z_kernel, (ctiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Z, (size_t)ncp, kw, nc, stages, zsp);
     Yz2Params p{ysp, zsp, C, ldc, mp, nc, stages, error};
     launch_dependent(tc_yz2_kernel, dim3(ctiles, rtiles), T2, kYz2Smem, stream, p);
     cuda_check(cudaGetLastError(), "tc_yz2 launch");
@@ -545,15 +560,21 @@ size_t tc_split_t_floats(uint32_t rows) { return (size_t)((rows + 15) / 16) * kP
 // sums its chunk's first sub_rows rows in one accumulator of tensor memory, the rest in a second, and adds the two.
 void launch_tc_ytc_split(cudaStream_t stream, const float* Y, size_t ldy, const float* C, size_t ldc, uint32_t mp,
                          uint32_t kw, uint32_t nc, float* zp, uint32_t ncp, uint32_t chunk_rows, uint32_t sub_rows, float* ytsp,
-                         unsigned* error) {
+                         unsigned* error, float* ysp) {
     static PerDeviceOnce once;
     if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_ytc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYtc2Smem),
                    "tc_ytc2 shared memory");
         once.mark(device);
     }
-    const uint32_t words = 128 * 4 * ((mp + 15) / 16);
-    launch_dependent(split_yt_kernel, (words + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, ytsp);
+    const uint32_t words = 128 * 4 * ((mp + 15) / 16), blocks_t = (words + 255) / 256;
+    if (ysp) {      // the second product's split of Y in the same launch
+        const uint32_t stages = (kw + KS2 - 1) / KS2, rtiles = (mp + 127) / 128;
+        launch_dependent(split_y_both_kernel, blocks_t + (rtiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Y, ldy, mp, kw,
+                         stages, ysp, ytsp, blocks_t);
+    } else {
+        launch_dependent(split_yt_kernel, blocks_t, 256, 0, stream, Y, ldy, mp, kw, ytsp);
+    }
     Ytc2Params p{ytsp, C, zp, ldc, mp, nc, ncp, chunk_rows, sub_rows / KS2, error};
     launch_dependent(tc_ytc2_kernel, dim3((nc + 127) / 128, (mp + chunk_rows - 1) / chunk_rows), T2, kYtc2Smem, stream, p);
     cuda_check(cudaGetLastError(), "tc_ytc2 launch");
