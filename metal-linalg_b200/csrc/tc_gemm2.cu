@@ -29,6 +29,8 @@
 #include "kernels.h"
 #include "tc_split.cuh"
 
+#include <cstdlib>
+
 namespace mlb {
 
 namespace {
@@ -271,6 +273,193 @@ __global__ void __launch_bounds__(T2, 2) tc_yz2_kernel(const Yz2Params p) {
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" :: "r"(tmem_d) : "memory");
 }
 
+
+// The same product on TWO column tiles a block (128 x 256 of C): a stage is Y's tile and both of Z's, so Y's tile is
+// fetched once for the two (three quarters of the operand bytes of two single-tile blocks), the prologue (barriers,
+// tensor memory) is paid once, and the accumulators are two runs of 128 columns of tensor memory. Two slots of 48 KB.
+constexpr int NSP    = 2;                     // slots of the pair kernel
+constexpr int STAGEP = 3 * HALF2;             // Y hi, lo; Z hi, lo of the first tile; of the second (48 KB)
+
+__global__ void __launch_bounds__(T2, 2) tc_yz2_pair_kernel(const Yz2Params p) {
+    dependency_wait_only();
+    extern __shared__ __align__(1024) char smem[];
+    __shared__ __align__(8) unsigned long long full[NSP], freed[NSP];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t ct = 2 * blockIdx.x, rt = blockIdx.y, j0 = ct * 128, r0 = rt * 128;
+    const bool two = j0 + 128 < p.nc;            // the second column tile exists
+    if (threadIdx.x == 0) failed = *reinterpret_cast<volatile unsigned*>(p.error) != 0;
+    __syncthreads();
+    if (failed) return;   // an earlier block or launch gave up: do nothing (the same answer for the whole block)
+
+    const uint32_t out_rows = min(p.mp - r0, 128u), stages = p.stages;
+    float (*Ct)[CLD2] = reinterpret_cast<float (*)[CLD2]>(smem);      // takes the slots' place once the products are done
+    float* out_tile = p.c + (size_t)r0 * p.ldc + j0;
+    const bool aligned = (p.ldc & 3) == 0 && (reinterpret_cast<size_t>(out_tile) & 15) == 0;
+    const uint32_t n_valid0 = min(p.nc - j0, 128u), n_valid1 = two ? min(p.nc - j0 - 128, 128u) : 0u;
+
+    // The first tile of C into registers now (a warp a row, 16 bytes a lane, sixteen rows a warp in flight); the second
+    // is asked into L2 and read when the first has gone out.
+    float4 creg[128 / (T2 / 32)];
+    if (aligned && n_valid0 == 128) {
+#pragma unroll
+        for (int u = 0; u < 128 / (T2 / 32); ++u) {
+            const uint32_t r = warp + (T2 / 32) * u;
+            creg[u] = r < out_rows ? *reinterpret_cast<const float4*>(out_tile + (size_t)r * p.ldc + 4 * lane)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (threadIdx.x / 2 < out_rows) {
+        const float* line = out_tile + (size_t)(threadIdx.x / 2) * p.ldc + 128 + 64 * (threadIdx.x & 1);
+        if (64 * (threadIdx.x & 1) < n_valid1) {
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(line));
+            if (64 * (threadIdx.x & 1) + 32 < n_valid1) asm volatile("prefetch.global.L2 [%0];" :: "l"(line + 32));
+        }
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSP; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&full[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&freed[s])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {            // 2 x 128 columns of tensor memory for the two 128 x 128 float32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" :: "r"(smem_u32(&tmem_base_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_base_slot;
+
+    if (threadIdx.x == 0) {
+        const float* ya = p.ysp + (size_t)rt * stages * kPairFloats;
+        const float* zb = p.zsp + (size_t)ct * stages * kPairFloats;
+        const float* zb1 = zb + (size_t)stages * kPairFloats;
+        const uint32_t stage_bytes = two ? (uint32_t)STAGEP : (uint32_t)(2 * HALF2);
+        auto request = [&](uint32_t s) {      // stage s into its slot: Y's hi and lo, Z's hi and lo of each tile
+            const uint32_t slot = s % NSP, base = smem_u32(smem + slot * STAGEP), bar = smem_u32(&full[slot]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(stage_bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         :: "r"(base), "l"(ya + (size_t)s * kPairFloats), "r"((uint32_t)HALF2), "r"(bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         :: "r"(base + HALF2), "l"(zb + (size_t)s * kPairFloats), "r"((uint32_t)HALF2), "r"(bar) : "memory");
+            if (two)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             :: "r"(base + 2 * HALF2), "l"(zb1 + (size_t)s * kPairFloats), "r"((uint32_t)HALF2), "r"(bar) : "memory");
+        };
+        int bad = 0;
+        for (uint32_t s = 0; s < stages && s < (uint32_t)NSP; ++s) request(s);
+        for (uint32_t s = 0; s < stages && !bad; ++s) {
+            const uint32_t slot = s % NSP, parity = (s / NSP) & 1;
+            if (!wait_barrier2(smem_u32(&full[slot]), parity)) { bad = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = smem_u32(smem + slot * STAGEP), a_lo = a_hi + TILE2;
+#pragma unroll
+            for (int tile = 0; tile < 2; ++tile) {
+                if (tile == 1 && !two) break;
+                const uint32_t b_hi = a_hi + (1 + tile) * HALF2, b_lo = b_hi + TILE2, tmem_acc = tmem_d + 128u * tile;
+#pragma unroll
+                for (int h = 0; h < KS2 / 8; ++h) {
+                    const uint32_t koff = h * 2 * LBO2;             // two 16-byte words of K an instruction
+                    const uint64_t dah = make_desc2(a_hi + koff), dal = make_desc2(a_lo + koff);
+                    const uint64_t dbh = make_desc2(b_hi + koff), dbl = make_desc2(b_lo + koff);
+                    const uint32_t acc0 = (s > 0 || h > 0) ? 1u : 0u;
+                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                 " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                                 :: "r"(tmem_acc), "l"(dal), "l"(dbh), "r"(kInstrDesc2), "r"(acc0) : "memory");
+                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                 " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                                 :: "r"(tmem_acc), "l"(dah), "l"(dbl), "r"(kInstrDesc2), "r"(1u) : "memory");
+                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                 " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                                 :: "r"(tmem_acc), "l"(dah), "l"(dbh), "r"(kInstrDesc2), "r"(1u) : "memory");
+                }
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                         :: "r"(smem_u32(&freed[slot])) : "memory");
+            if (s + NSP < stages) {       // the slot is free when these products have completed
+                if (!wait_barrier2(smem_u32(&freed[slot]), parity)) { bad = 1; break; }
+                request(s + NSP);
+            }
+        }
+        if (bad) failed = 1;
+    }
+    // every product has completed when the last commit has arrived
+    if (stages > 0) {
+        const uint32_t last = stages - 1;
+        if (!wait_barrier2(smem_u32(&freed[last % NSP]), (last / NSP) & 1)) failed = 1;
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool ok = !failed;
+    if (!ok && threadIdx.x == 0) atomicOr(p.error, (unsigned)kStatusTensorWait);
+#pragma unroll 1
+    for (int tile = 0; tile < 2; ++tile) {
+        if (tile == 1 && !two) break;
+        const uint32_t n_valid = tile ? n_valid1 : n_valid0;
+        float* out = out_tile + 128 * tile;
+        const bool out_vec = aligned && n_valid == 128;
+        if (tile == 1 && out_vec) {        // the second tile of C, asked into L2 at the start
+#pragma unroll
+            for (int u = 0; u < 128 / (T2 / 32); ++u) {
+                const uint32_t r = warp + (T2 / 32) * u;
+                creg[u] = r < out_rows ? *reinterpret_cast<const float4*>(out + (size_t)r * p.ldc + 4 * lane)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (ok) {      // the product's tile from tensor memory into shared memory, a row per lane, 16-byte stores
+            const uint32_t row = 32 * (warp & 3) + lane;
+            const uint32_t c_base = 64 * (warp >> 2);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t c0 = c_base + 32 * half;
+                uint32_t v[32];
+                const uint32_t taddr = tmem_d + 128u * tile + ((32u * (warp & 3)) << 16) + c0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    *reinterpret_cast<uint4*>(&Ct[row][c0 + 4 * q]) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (ok) {              // C's rows minus the product's, to global memory, a warp a row, 16 bytes a lane
+            if (out_vec) {
+#pragma unroll
+                for (int u = 0; u < 128 / (T2 / 32); ++u) {
+                    const uint32_t r = warp + (T2 / 32) * u;
+                    if (r < out_rows) {
+                        const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
+                        *reinterpret_cast<float4*>(out + (size_t)r * p.ldc + 4 * lane) =
+                            make_float4(creg[u].x - f.x, creg[u].y - f.y, creg[u].z - f.z, creg[u].w - f.w);
+                    }
+                }
+            } else {
+                for (uint32_t r = warp; r < out_rows; r += T2 / 32) {
+                    float* dst = out + (size_t)r * p.ldc + 4 * lane;
+                    const float4 f = *reinterpret_cast<const float4*>(&Ct[r][4 * lane]);
+                    const float e[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (4 * lane + i < n_valid) dst[i] -= e[i];
+                }
+            }
+        }
+        __syncthreads();      // the tile in shared memory has been read: the second may take its place
+    }
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_d) : "memory");
+}
 
 // ---------------------------------------------------------------------------
 // Zp[chunk][i][j] = sum over the chunk's rows r of Y[r][i] C[r][j]
@@ -529,6 +718,7 @@ __global__ void __launch_bounds__(T2, 2) tc_ytc2_kernel(const Ytc2Params p) {
 }
 
 constexpr size_t kYz2Smem = (size_t)NS2 * STAGE2 + 1024;
+constexpr size_t kYz2PairSmem = (size_t)NSP * STAGEP + 1024;
 
 } // namespace
 
@@ -543,13 +733,19 @@ void launch_tc_yz_split(cudaStream_t stream, const float* Y, size_t ldy, const f
     if (const int device = current_device(); once.first(device)) {
         cuda_check(cudaFuncSetAttribute(tc_yz2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYz2Smem),
                    "tc_yz2 shared memory");
+        cuda_check(cudaFuncSetAttribute(tc_yz2_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kYz2PairSmem),
+                   "tc_yz2_pair shared memory");
         once.mark(device);
     }
     const uint32_t stages = (kw + KS2 - 1) / KS2, rtiles = (mp + 127) / 128, ctiles = (nc + 127) / 128;
     if (Y) launch_dependent(split_y_kernel, (rtiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Y, ldy, mp, kw, stages, ysp);
     if (Z) launch_dependent(split_z_kernel, (ctiles * 128 * 4 * stages + 255) / 256, 256, 0, stream, Z, (size_t)ncp, kw, nc, stages, zsp);
     Yz2Params p{ysp, zsp, C, ldc, mp, nc, stages, error};
-    launch_dependent(tc_yz2_kernel, dim3(ctiles, rtiles), T2, kYz2Smem, stream, p);
+    // two column tiles a block where that still leaves two waves of blocks (QR_TC_YZ_PAIR=0/1: never / always)
+    const char* pair_env = std::getenv("QR_TC_YZ_PAIR");
+    const bool pair = pair_env ? pair_env[0] != '0' : (uint64_t)((ctiles + 1) / 2) * rtiles >= 4 * 148;
+    if (pair) launch_dependent(tc_yz2_pair_kernel, dim3((ctiles + 1) / 2, rtiles), T2, kYz2PairSmem, stream, p);
+    else launch_dependent(tc_yz2_kernel, dim3(ctiles, rtiles), T2, kYz2Smem, stream, p);
     cuda_check(cudaGetLastError(), "tc_yz2 launch");
 }
 

@@ -256,7 +256,8 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0", "QR_TC_PAIR=0"])
+                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0", "QR_TC_PAIR=0", "QR_TC_PAIR=1",
+                                    "QR_TC_YZ_PAIR=1"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
     the tensor cores, one stream instead of look-ahead, the general tree for every panel, Q accumulated
@@ -265,7 +266,8 @@ def test_blocked_fallback_paths(switch):
     effect only when set before the first call), panels by the tree of row blocks instead of one
     cluster launch, tensor-core products that split their operands in every block instead of once,
     panel steps a column a reduction instead of two, the update inside the aggregate in two launches
-    instead of one cluster launch, panel clusters of eight blocks of 512 rows instead of sixteen of 256, look-ahead by aggregates instead of by panels."""
+    instead of one cluster launch, panel clusters of eight blocks of 512 rows instead of sixteen of 256, the wide products' blocks with one or two accumulators and one or two column tiles whatever the
+    size, look-ahead by aggregates instead of by panels."""
     rng = np.random.default_rng(16)
     a = rng.standard_normal((1, 900, 900)).astype(np.float32)
     q0, r0 = gpu_qr(a, "reduced", kernel="blocked")
