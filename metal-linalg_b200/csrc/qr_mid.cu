@@ -248,24 +248,24 @@ __device__ __forceinline__ void gemm_vw(const float* vbase, int ldv, const float
     const int tcq = ((threadIdx.x >> 3) & 3) + 4 * ((threadIdx.x >> 5) & 1);
     const int trb = threadIdx.x >> 6;
     for (int rq = trq + 8 * trb; rq < nq; rq += 32) {
-        float4 c[4];
+        ulonglong2 cp[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) c[b] = *reinterpret_cast<const float4*>(cbase + (4 * tcq + b) * ldc + 4 * rq);
+        for (int b = 0; b < 4; ++b) cp[b] = *reinterpret_cast<const ulonglong2*>(cbase + (4 * tcq + b) * ldc + 4 * rq);
 #pragma unroll 8
         for (int i = 0; i < 32; ++i) {
             const float4 v = *reinterpret_cast<const float4*>(vbase + i * ldv + 4 * rq);
             const float4 w = *reinterpret_cast<const float4*>(Ws + i * LDZ + 4 * tcq);
-            c[0].x = fmaf(-v.x, w.x, c[0].x); c[0].y = fmaf(-v.y, w.x, c[0].y);
-            c[0].z = fmaf(-v.z, w.x, c[0].z); c[0].w = fmaf(-v.w, w.x, c[0].w);
-            c[1].x = fmaf(-v.x, w.y, c[1].x); c[1].y = fmaf(-v.y, w.y, c[1].y);
-            c[1].z = fmaf(-v.z, w.y, c[1].z); c[1].w = fmaf(-v.w, w.y, c[1].w);
-            c[2].x = fmaf(-v.x, w.z, c[2].x); c[2].y = fmaf(-v.y, w.z, c[2].y);
-            c[2].z = fmaf(-v.z, w.z, c[2].z); c[2].w = fmaf(-v.w, w.z, c[2].w);
-            c[3].x = fmaf(-v.x, w.w, c[3].x); c[3].y = fmaf(-v.y, w.w, c[3].y);
-            c[3].z = fmaf(-v.z, w.w, c[3].z); c[3].w = fmaf(-v.w, w.w, c[3].w);
+            // packed: rows (x, y) and (z, w) of V's word are pairs as they lie; W's entry goes into both halves, negated
+            const ulonglong2 vv = *reinterpret_cast<const ulonglong2*>(&v);
+            const small::pair_t w0 = small::pack(-w.x, -w.x), w1 = small::pack(-w.y, -w.y), w2 = small::pack(-w.z, -w.z),
+                                w3 = small::pack(-w.w, -w.w);
+            cp[0].x = small::fma2(vv.x, w0, cp[0].x); cp[0].y = small::fma2(vv.y, w0, cp[0].y);
+            cp[1].x = small::fma2(vv.x, w1, cp[1].x); cp[1].y = small::fma2(vv.y, w1, cp[1].y);
+            cp[2].x = small::fma2(vv.x, w2, cp[2].x); cp[2].y = small::fma2(vv.y, w2, cp[2].y);
+            cp[3].x = small::fma2(vv.x, w3, cp[3].x); cp[3].y = small::fma2(vv.y, w3, cp[3].y);
         }
 #pragma unroll
-        for (int b = 0; b < 4; ++b) *reinterpret_cast<float4*>(cbase + (4 * tcq + b) * ldc + 4 * rq) = c[b];
+        for (int b = 0; b < 4; ++b) *reinterpret_cast<ulonglong2*>(cbase + (4 * tcq + b) * ldc + 4 * rq) = cp[b];
     }
 }
 
