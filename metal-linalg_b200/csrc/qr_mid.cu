@@ -473,8 +473,10 @@ __device__ void factor_panel_cols(const Smem& s, int ldv, int mp, int jb, float*
 // of 257 to 512 rows) needs more registers than two blocks a multiprocessor leave and spills; it is launched
 // only for matrices of 257 to 512 rows, where it still wins (512 x 512: 13.1 against 14.2 ms for 296 matrices),
 // so that every other shape runs the instantiation for 32, which does not.
-template <int PRW>
-__global__ void __launch_bounds__(NT, 2) qr_mid_kernel(const MidParams p) {
+// MB: the blocks a multiprocessor the registers are held to. Beyond about 330 rows the shared memory leaves room for one
+// block only, and holding the instantiation for 64 to two blocks' registers made it spill 2 KB a thread for nothing.
+template <int PRW, int MB = 2>
+__global__ void __launch_bounds__(NT, MB) qr_mid_kernel(const MidParams p) {
     extern __shared__ __align__(16) float smem_raw[];
     const Smem s = carve(smem_raw, p.ldv);
     const int m = p.m, n = p.n, K = p.K, ldv = p.ldv;
@@ -647,7 +649,15 @@ bool qr_mid_fits(const DeviceContext& ctx, uint32_t m, uint32_t n) {
 namespace {
 using MidKernel = void (*)(MidParams);
 MidKernel mid_kernel_for(uint32_t m) {
-    return (m > 256 && m <= 512 && mid_by_columns()) ? qr_mid_kernel<64> : qr_mid_kernel<32>;
+    if (!(m > 256 && m <= 512 && mid_by_columns())) return qr_mid_kernel<32>;
+    // two blocks a multiprocessor only where their shared memory fits its 228 KB twice (1 KB a block is the system's)
+    static const size_t fixed = [] {
+        cudaFuncAttributes attr{};
+        cuda_check(cudaFuncGetAttributes(&attr, qr_mid_kernel<64, 2>), "qr_mid attributes");
+        return attr.sharedSizeBytes + 1024;
+    }();
+    const bool two = 2 * (smem_bytes((int)((m + 31) / 32) * 32 + 4) + fixed) <= 228 * 1024;
+    return two ? qr_mid_kernel<64, 2> : qr_mid_kernel<64, 1>;
 }
 uint64_t slot_floats_of(uint32_t m, uint32_t n) {
     const uint32_t K = m < n ? m : n;
