@@ -78,11 +78,11 @@ void   launch_tsqr_apply(DeviceContext& ctx, cudaStream_t stream, const float* q
 
 // A panel of the blocked QR (mp x jb, jb <= 32, mp <= 16384) to compact-WY form in three launches
 // (qr_panel.cu): its R into the working copy's upper triangle, Y (unit lower trapezoidal) into y,
-// T into t[32][32].
+// T into t[32][32]. A wait inside it that ran out sets kStatusTensorWait in *bad (where given).
 bool   panel_fast_fits(uint32_t mp, uint32_t jb);
 size_t panel_fast_workspace_floats(uint32_t mp);
 void   panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t mp, uint32_t jb, float* y, size_t ldy,
-                         float* t, float* ws);
+                         float* t, float* ws, unsigned* bad = nullptr);
 
 // The rank-128 products of the blocked QR on the tcgen05 tensor cores, 3xTF32 (tc_gemm.cu).
 // `error` is set non-zero if a bounded wait inside the kernel ran out.

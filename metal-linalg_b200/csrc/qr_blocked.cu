@@ -1113,7 +1113,7 @@ void launch_qr_blocked(DeviceContext& ctx, cudaStream_t stream, const QrProblem&
                 const uint32_t pi = ag * (AG / NB) + pp, k0 = pi * NB, jb = std::min<uint32_t>(NB, K - k0), mp = m - k0;
                 if (!slow_panels && panel_fast_fits(mp, jb)) {
                     panel_factor_fast(ps, W + (size_t)k0 * ldw + k0, ldw, mp, jb, Y + (size_t)k0 * ldy + k0, ldy,
-                                      T + (size_t)pi * 1024, pf);
+                                      T + (size_t)pi * 1024, pf, &info->bad);
                 } else {   // taller than the register-resident panel kernels take: the general tree
                     tsqr_core(ctx, ps, W + (size_t)k0 * ldw + k0, ldw, 0, mp, jb, 1, Qp, Rp, 0, ts);
                     ReconParams rp{Qp, Rp, W, Y, T + (size_t)pi * 1024, Ui, ldw, ldy, k0, jb};

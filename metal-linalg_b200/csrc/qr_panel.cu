@@ -574,6 +574,8 @@ struct ClusterPanelParams {
     float*   t;         // [32][32] out
     uint32_t mp, jb;
     int      pairs;     // 1: two columns a reduction (factor_cols2); 2: four (factor_cols4); 0: one
+    int      post;      // four columns a reduction: the sums posted to mbarriers (cols::ClusterSync::post)
+    unsigned* bad;      // where a wait that ran out is recorded (may be null)
 };
 
 // MODE: the columns a reduction (0: one, 1: two, 2: four), a kernel each: one kernel holding all three was larger and
@@ -582,14 +584,17 @@ template <int RW, int MODE>
 __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanelParams p) {
     using namespace cols;
     dependency_wait();
-    // every block of the cluster must be running before any writes into another's shared memory: arrive now, wait
-    // after the loads, which hide the barrier's latency
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     __shared__ __align__(16) cols::Smem s;
     __shared__ __align__(16) cols::ClusterShared cs;
     __shared__ __align__(16) float pub[2 * kWarps * RW];
     extern __shared__ __align__(16) unsigned char quad_raw[];      // four columns a reduction: QuadShared, then 4 * kWarps * RW floats
     QuadShared* qs = reinterpret_cast<QuadShared*>(quad_raw);
+    if constexpr (MODE == 2) {
+        if (threadIdx.x == 0) ClusterSync::init_posts(qs);
+    }
+    // every block of the cluster must be running (and its mbarriers set up) before any writes into another's shared
+    // memory: arrive now, wait after the loads, which hide the barrier's latency
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     float* pub4 = reinterpret_cast<float*>(quad_raw + sizeof(QuadShared));
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint32_t rank = cluster_rank(), ncta = cluster_size();
@@ -607,7 +612,7 @@ __global__ void __launch_bounds__(PT, 1) panel_cluster_kernel(const ClusterPanel
     }
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     float my_sc;
-    if constexpr (MODE == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs});
+    if constexpr (MODE == 2) factor_cols4<RW>(x2, s, pub4, my_sc, ClusterSync{rank, ncta, &cs, qs, p.post, p.bad});
     else if constexpr (MODE == 1) factor_cols2<RW, ClusterSync, RW == 32>(x2, s, pub, my_sc, ClusterSync{rank, ncta, &cs});      // 32 rows a lane leave the registers for it
     else factor_cols<RW, false>(x2, s, pub, nullptr, my_sc, ClusterSync{rank, ncta, &cs});
     __syncthreads();
@@ -707,7 +712,7 @@ size_t panel_fast_workspace_floats(uint32_t mp) {
 // The panel at `panel` (mp x jb, row stride ldw, inside the working copy) to compact-WY form: its R
 // (S R) into the working copy's upper triangle, Y into `y` (row stride ldy), T into t[32][32].
 void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t mp, uint32_t jb, float* y, size_t ldy,
-                       float* t, float* ws) {
+                       float* t, float* ws, unsigned* bad) {
     const int rpt = rows_per_thread(mp);
     const uint32_t lr = PT * rpt, leaves = (mp + lr - 1) / lr;
     float* Vl = ws;
@@ -752,7 +757,9 @@ void panel_factor_fast(cudaStream_t stream, float* panel, size_t ldw, uint32_t m
         const char* envp = std::getenv("QR_PANEL_PAIRS");
         const char* envq = std::getenv("QR_PANEL_QUADS");
         const int pairs = (envp && envp[0] == '0') ? 0 : (envq && envq[0] == '0') ? 1 : 2;
-        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb, pairs};
+        // the sums of four columns posted to mbarriers (QR_PANEL_POST=0: stored, then the cluster's barrier)
+        const char* envs = std::getenv("QR_PANEL_POST");
+        ClusterPanelParams cp{panel, ldw, y, ldy, t, mp, jb, pairs, !(envs && envs[0] == '0'), bad};
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(ncta);
         cfg.blockDim = dim3(PT);

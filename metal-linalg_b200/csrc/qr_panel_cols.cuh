@@ -135,6 +135,7 @@ struct QuadShared {
     float red4[2][kWarps][32][4];
     float prow4[2][32][4];
     float cred4[2][kMaxCluster][32][4];
+    unsigned long long arrived[2];      // mbarriers, by quad parity: a quad's words have all arrived (ClusterSync::post)
 };
 __device__ __forceinline__ void store4_to_block(const float* local, uint32_t rank, float4 v) {
     uint32_t remote;
@@ -142,18 +143,65 @@ __device__ __forceinline__ void store4_to_block(const float* local, uint32_t ran
                  : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// The same store as an asynchronous one that counts its 16 bytes on the mbarrier at `bar` of the receiving block
+__device__ __forceinline__ void post4_to_block(const float* local, const unsigned long long* bar, uint32_t rank, float4 v) {
+    uint32_t remote, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(rbar) : "r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 :: "r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(rbar) : "memory");
+}
+constexpr unsigned kPostPolls = 1u << 18;       // polls of a quad's mbarrier before the block gives up on it
 struct ClusterSync {
     uint32_t       rank, ncta;
     ClusterShared* cs;
     QuadShared*    qs = nullptr;
+    // post: a quad's sums travel as asynchronous stores that count their bytes on an mbarrier of the receiving block,
+    // and every block waits on its own mbarrier instead of the cluster's barrier (whose round trip was a third of a
+    // quad's time with sixteen blocks). A block sends quad q + 1 only after all its threads have read quad q, and
+    // nobody sends quad q + 2 before it has that, so two buffers are enough. A wait that runs out sets `bad`.
+    int            post = 0;
+    unsigned*      bad = nullptr;
+    // the mbarriers, before the cluster barrier that opens the kernel (one thread of the block)
+    __device__ __forceinline__ static void init_posts(QuadShared* q) {
+        for (int b = 0; b < 2; ++b)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"((uint32_t)__cvta_generic_to_shared(&q->arrived[b])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     // the four sums of a four-column step: the block's sums to every block (16 bytes a store), block 0's pivot rows along
-    __device__ __forceinline__ void exchange4(int buf, int lane, int warp) const {
+    __device__ __forceinline__ void exchange4(int buf, int lane, int warp, int it) const {
         step_barrier(32 * kWarps);
         float4 d = *reinterpret_cast<const float4*>(qs->red4[buf][0][lane]);
 #pragma unroll
         for (int w = 1; w < kWarps; ++w) {
             const float4 e = *reinterpret_cast<const float4*>(qs->red4[buf][w][lane]);
             d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+        }
+        if (post) {
+            const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&qs->arrived[buf]);
+            if (warp == 0 && lane == 0) {      // what this block will receive: 512 bytes a block, and block 0's pivot rows
+                const uint32_t bytes = ncta * 512u + (rank != 0 ? 512u : 0u);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+            }
+            for (uint32_t r = warp; r < ncta; r += kWarps) {
+                post4_to_block(qs->cred4[buf][rank][lane], &qs->arrived[buf], r, d);
+                if (rank == 0 && r != 0)
+                    post4_to_block(qs->prow4[buf][lane], &qs->arrived[buf], r, *reinterpret_cast<const float4*>(qs->prow4[buf][lane]));
+            }
+            const uint32_t parity = (uint32_t)(it >> 1) & 1u;
+            uint32_t ok = 0;
+            for (unsigned polls = 0; polls < kPostPolls && !ok; ++polls) {
+                asm volatile("{\n\t.reg .pred p;\n\t"
+                             "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+                // once a wait has run out somewhere, the others give up soon: the factorisation is lost already
+                if (!ok && (polls & 1023u) == 1023u && bad && (*reinterpret_cast<volatile unsigned*>(bad) & 2u)) break;
+            }
+            if (!ok && bad && lane == 0) atomicOr(bad, 2u);      // kStatusTensorWait: the outputs become NaN, the status word says why
+            return;
         }
         for (uint32_t r = warp; r < ncta; r += kWarps) {
             store4_to_block(qs->cred4[buf][rank][lane], r, d);
@@ -609,7 +657,7 @@ __device__ __forceinline__ void factor_cols4(pair_t (&x2)[RW / 2], Smem& s, floa
             *reinterpret_cast<float4*>(qs.red4[buf][warp][lane]) = make_float4(hsum2(a0, e0), hsum2(a1, e1), hsum2(a2, e2), hsum2(a3, e3));
         }
         if (piv) *reinterpret_cast<float4*>(qs.prow4[buf][lane]) = make_float4(lo_of(x2[0]), hi_of(x2[0]), lo_of(x2[1]), hi_of(x2[1]));
-        sync.exchange4(buf, lane, warp);
+        sync.exchange4(buf, lane, warp, it);
         float P[4], b[4], c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         {
             const float4 t4 = sync.total4(buf, lane);

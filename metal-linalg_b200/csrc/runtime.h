@@ -27,7 +27,7 @@ struct Workspace {
 // (DeviceContext::status, one word of device memory per GPU). The matrices concerned get NaN
 // outputs; take_status() turns the word into an error for the caller.
 enum : unsigned {
-    kStatusTensorWait = 2u,   // an mbarrier wait of a tensor-core product (tc_gemm.cu, tc_gemm2.cu)
+    kStatusTensorWait = 2u,   // an mbarrier wait of a tensor-core product (tc_gemm.cu, tc_gemm2.cu) or of a panel's cluster (qr_panel_cols.cuh)
     kStatusStreamWait = 4u,   // an mbarrier wait of the streaming small-matrix kernel (qr_small_stream.cu)
 };
 

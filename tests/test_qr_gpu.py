@@ -256,7 +256,7 @@ def test_blocked_kernel_shapes(shape, mode):
 
 @pytest.mark.parametrize("switch", ["QR_TENSOR=0", "QR_NO_LOOKAHEAD=1", "QR_PANEL_TREE=1", "QR_BACKWARD_Q=1", "QR_PANEL_ROWS=1",
                                     "QR_NO_PDL=1", "QR_PANEL_CLUSTER=0", "QR_TC_SPLIT=0", "QR_PANEL_PAIRS=0", "QR_INNER_FUSED=0",
-                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0", "QR_TC_PAIR=0", "QR_TC_PAIR=1",
+                                    "QR_PANEL_CLUSTER=8", "QR_LOOK_PANELS=0", "QR_PANEL_QUADS=0", "QR_PANEL_POST=0", "QR_TC_PAIR=0", "QR_TC_PAIR=1",
                                     "QR_TC_YZ_PAIR=1"])
 def test_blocked_fallback_paths(switch):
     """The blocked QR's alternatives give the same factorisation: the FP32 FMA products instead of
@@ -283,11 +283,13 @@ def test_blocked_fallback_paths(switch):
     assert harness.r_parity(r1, r_ref) <= 1e-4
 
 
-@pytest.mark.parametrize("switch", ["", "QR_PANEL_CLUSTER=8", "QR_PANEL_CLUSTER=0", "QR_PANEL_PAIRS=0", "QR_PANEL_QUADS=0"])
+@pytest.mark.parametrize("switch", ["", "QR_PANEL_CLUSTER=8", "QR_PANEL_CLUSTER=0", "QR_PANEL_PAIRS=0", "QR_PANEL_QUADS=0",
+                                    "QR_PANEL_POST=0"])
 def test_blocked_panels_of_2049_to_4096_rows(switch):
     """Panels of 2049 to 4096 rows: a cluster of sixteen blocks of 256 rows (the default, with the published columns
-    kept in registers between the products and the update), of eight blocks of 512 rows, the tree of row blocks, and
-    the cluster with a column a reduction, all against the reference."""
+    kept in registers between the products and the update, the sums of four columns posted to mbarriers), of eight
+    blocks of 512 rows, the tree of row blocks, the cluster with a column a reduction, and the cluster's own barrier
+    for the sums, all against the reference."""
     rng = np.random.default_rng(31)
     a = rng.standard_normal((1, 3000, 96)).astype(np.float32)
     if switch:
