@@ -723,7 +723,7 @@ def test_device_queries():
     assert mlt.qr_policy_source().startswith(("tuned:", "env:", "user"))
     assert mlt.calibration_status() == ""
     assert mlt.qr_kernel(32, 32, 1000) == "small" and mlt.qr_kernel(256, 256, 4096) == "mid"
-    # the measured routing: one matrix is spread over the grid from sqrt(M k) of 220, a batch later
+    # the measured routing: one matrix is spread over the grid from sqrt(M k) of 240, a batch later
     assert mlt.qr_kernel(512, 512, 1) == "blocked" and mlt.qr_kernel(512, 512, 32) == "mid"
     assert mlt.qr_kernel(384, 384, 4) == "blocked" and mlt.qr_kernel(192, 192, 1) == "mid"
     assert mlt.qr_kernel(1024, 1024, 16) == "blocked" and mlt.qr_kernel(1024, 1024, 128) == "mid"
