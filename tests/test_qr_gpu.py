@@ -932,7 +932,8 @@ def test_second_gpu_in_one_process():
     torch.manual_seed(31)
     cases = [(torch.randn(300, 32, 32), "reduced"), (torch.randn(100, 16, 16), "reduced"),
              (torch.randn(6, 256, 200), "complete"), (torch.randn(2, 5000, 64), "reduced"),
-             (torch.randn(1, 1500, 1200), "reduced"), (torch.randn(1, 2100, 300), "r")]
+             (torch.randn(1, 1500, 1200), "reduced"), (torch.randn(1, 2100, 300), "r"),
+             (torch.randn(4, 450, 300), "reduced"), (torch.randn(1, 3000, 160), "reduced")]
     for a, mode in cases:
         (q0, r0), (q1, r1) = mlt.qr_sharded([a.to("cuda:0"), a.to("cuda:1")], mode)
         torch.cuda.synchronize(0)
