@@ -70,8 +70,11 @@ def test_random_shapes(seed):
             orth = torch.linalg.matrix_norm(q64.mT @ q64 - eye).max().item()
             if not recon <= tol:
                 msg.append(f"reconstruction {recon:.2e} > {tol:.2e}")
-            if not orth <= tol:
-                msg.append(f"orthogonality {orth:.2e} > {tol:.2e}")
+            # a float32 Q of c columns is off by about 0.3 sqrt(c) eps from rounding its entries alone (the exact Q of
+            # 1833 x 1, rounded: 1.5e-6), which passes 10 n eps for a complete Q of one or two columns
+            floor = 0.5 * q.shape[-1] ** 0.5 * EPS
+            if not orth <= max(tol, floor):
+                msg.append(f"orthogonality {orth:.2e} > {max(tol, floor):.2e}")
         else:
             g = a64.mT @ a64
             d = (torch.linalg.matrix_norm(r64.mT @ r64 - g) / torch.linalg.matrix_norm(g).clamp_min(1e-300)).max().item()

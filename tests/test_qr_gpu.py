@@ -925,6 +925,29 @@ def test_release_workspaces_gives_memory_back():
     assert torch.equal(q2, q) and torch.equal(r2, r)
 
 
+@pytest.mark.parametrize("shape", [(3, 1833, 1), (2, 3000, 2), (1, 2500, 15)])
+def test_complete_q_of_a_few_columns(shape):
+    """A complete Q of thousands of rows from one to a few columns. The bound on orthogonality, 10 n eps, is a few ulps
+    here, and an m x m float32 matrix cannot keep it beyond about a thousand rows whatever the algorithm (the exact Q
+    of 1833 x 1 rounded to float32: 1.5e-6 against 1.2e-6; the reference's CPU path: 1.5e-6): the kernels are held to
+    the bound or to the reference's own figure on the same input plus a tenth, whichever is larger."""
+    b, m, n = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((b, m, n)).astype(np.float32)
+    q, r = gpu_qr(a, "complete")
+    assert mlt.qr_kernel(m, n, b, "complete") == "blocked"
+    q_ref, r_ref = harness.oracle_qr(a, "complete")
+    tol = workloads.tolerance(n)
+    eye = np.eye(m)
+    for k in range(b):
+        q64, ref64 = q[k].astype(np.float64), q_ref[k].astype(np.float64)
+        orth, orth_ref = np.linalg.norm(q64.T @ q64 - eye), np.linalg.norm(ref64.T @ ref64 - eye)
+        assert orth <= max(tol, 1.1 * orth_ref), (orth, orth_ref, tol)
+        a64 = a[k].astype(np.float64)
+        assert np.linalg.norm(a64 - q64 @ r[k].astype(np.float64)) / np.linalg.norm(a64) <= tol
+    assert harness.r_parity(r, r_ref) <= 1e-4
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
 def test_second_gpu_in_one_process():
     """Every kernel family on cuda:1 after cuda:0 in ONE process (kernels that opt into more than 48 KB
